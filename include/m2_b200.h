@@ -1,0 +1,197 @@
+/*
+ * m2_b200 -- C ABI of the B200 (sm_100a) kernels behind the M2-BERT sequence mixer and
+ * BlockdiagLinear GLU MLP forward path.
+ *
+ * Conventions
+ *   - plain C: pointers, sizes and strides only; no framework types.
+ *   - every pointer marked "device" is caller-owned device memory of the CURRENT device;
+ *     the library never allocates or frees device memory in these calls (the one
+ *     exception is a per-device cache of constant twiddle tables built on first use).
+ *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*).
+ *   - return value: M2_OK or an m2_status error; m2_last_error() gives a thread-local
+ *     human-readable message.  Nothing aborts, nothing throws.
+ *   - strides are in ELEMENTS of the tensor's dtype.
+ *
+ * The reference (HazyResearch/m2) has no C interface on this path: its default route is
+ * PyTorch ops and its optional native route is a pybind11 module taking torch::Tensor
+ * (csrc/flashmm/flash_mm.cpp:364-368).  Each entry point below cites the reference code
+ * whose computation it replaces.
+ */
+#ifndef M2_B200_H
+#define M2_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define M2_B200_ABI_VERSION 1
+
+typedef enum { M2_F32 = 0, M2_BF16 = 1 } m2_dtype;
+
+typedef enum {
+  M2_OK = 0,
+  M2_ERR_ARG = 1,          /* NULL pointer, non-positive size, inconsistent shapes */
+  M2_ERR_UNSUPPORTED = 2,  /* shape or dtype outside what the kernels cover */
+  M2_ERR_ALIGN = 3,        /* pointer or stride not aligned as documented */
+  M2_ERR_CUDA = 4,         /* a CUDA runtime call or launch failed */
+  M2_ERR_DEVICE = 5        /* a kernel gave up on a bounded wait (see m2_device_status) */
+} m2_status;
+
+/* ABI version of the loaded library (== M2_B200_ABI_VERSION it was built with). */
+int m2_version(void);
+
+/* Message of the last error returned on the calling thread ("" if none). */
+const char* m2_last_error(void);
+
+/* Reads and clears the device-side status word of the current device: 0 = no kernel has
+ * given up on a bounded wait since the last call.  Synchronises the device. */
+int m2_device_status(int* status_out);
+
+/* ---------------------------------------------------------------------------------------
+ * Implicit long-convolution filter.
+ * Replaces HyenaFilter.filter / filter_rev and the bidirectional merge
+ *   bert/src/mm/hyena_utils.py:201-217 (MLP on the positional embedding, :62-63 Sin,
+ *   :109-112 exponential modulation) and :231-234 (pad + flip + add).
+ * k_out (device, float32): (d_model, R) with R = m2_filter_row_len(seq_len) = twice the
+ *   power of two >= seq_len, the period of the circular convolution the kernels run:
+ *   bidirectional: row c = [ k_fwd[c, 0..L) | zeros | k_rev[c, L-1..0] ]
+ *   otherwise:     row c = [ k_fwd[c, 0..L) | zeros ]
+ *   (for a power-of-two seq_len this is exactly the reference's length-2L kernel).
+ * bf16_rounding != 0 reproduces the rounding points of the reference under
+ * torch.autocast(bfloat16): every Linear on bf16-rounded operands with a bf16-rounded
+ * result, Sin and the modulation in float32.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int d_model, seq_len, order, emb_dim;
+  int bidirectional;
+  int bf16_rounding;
+  float w_mod, shift;
+  const float* z;        /* device (seq_len, emb_dim): pos_emb.z[0, :seq_len] */
+  const float* t;        /* device (seq_len): pos_emb.t[0, :seq_len, 0] */
+  const float* w[4];     /* device implicit_filter.{0,2,4,6}.weight: (order,emb) (order,order) x2 (d_model,order) */
+  const float* b[3];     /* device implicit_filter.{0,2,4}.bias */
+  const float* w_rev[4]; /* implicit_filter_rev.*; ignored unless bidirectional */
+  const float* b_rev[3];
+  const float* freq;     /* device (order): the shared Sin.freq */
+  const float* deltas;   /* device (d_model): modulation.deltas */
+  float* k_out;
+} m2_filter_args;
+
+int m2_filter_row_len(int seq_len);
+int m2_hyena_filter(const m2_filter_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Filter spectrum in the layout the long-convolution kernel consumes.
+ * Replaces `k_f = torch.fft.rfft(k, n=2L) / (2L)`, bert/src/mm/hyena_utils.py:23-24.
+ * m2_longconv_kind() names the kernel family used for (seq_len, act_dtype);
+ * m2_filter_spectrum_floats() is the number of float32 the spectrum of one filter takes.
+ * k (device, float32): (d_model, m2_filter_row_len(seq_len)) as written by m2_hyena_filter.
+ * ------------------------------------------------------------------------------------- */
+int    m2_longconv_kind(int seq_len, m2_dtype act_dtype);
+size_t m2_filter_spectrum_floats(int kind, int d_model, int seq_len);
+int    m2_filter_spectrum(int kind, int d_model, int seq_len, const float* k, float* spec_out,
+                          void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Fused gated long convolution: everything between in_linear and out_linear.
+ * Replaces bert/src/mm/monarch_mixer_sequence_mixer.py:109-149 -- the layout change,
+ * the depthwise 3-tap short_filter (:112), x1/x2/v split (:114), v*x1 (:116), the FFT
+ * convolution + bias of HyenaFilter.forward / fftconv_ref (bert/src/mm/hyena_utils.py:16-42,
+ * :219-248), y*x2 (:144) and the residual long convolution on the raw layer input
+ * (:131-147).
+ *   xin : device, in_linear output; element (b, t, ch), ch in [0, 3*d_model) ordered x1|x2|v,
+ *         at xin[b*xin_sb + t*xin_st + ch*xin_sc]; either xin_st == 1 or xin_sc == 1.
+ *   u   : device, raw layer input (b, t, c) with its own strides and dtype; used only when
+ *         n_filters == 2.
+ *   out : device, (b, t, c) with its own strides, dtype act_dtype: the tensor out_linear
+ *         consumes.
+ * bf16_rounding != 0 rounds to bf16 where the reference under autocast does (conv output,
+ * v*x1, the convolution result, y*x2, the final sum).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int batch, seq_len, d_model;
+  int n_filters;            /* 1, or 2 with residual_long_conv */
+  int plain;                /* != 0: HyenaFilter.forward alone -- out = conv(xin, filter 0) + bias*xin
+                               with xin (b, t, c) of d_model channels: no short conv, no gates,
+                               n_filters must be 1 */
+  int kind;                 /* from m2_longconv_kind() */
+  m2_dtype act_dtype;       /* dtype of xin and out */
+  m2_dtype u_dtype;         /* dtype of u */
+  int bf16_rounding;
+  const void* xin; long long xin_sb, xin_st, xin_sc;
+  const void* u;   long long u_sb, u_st, u_sc;
+  void* out;       long long out_sb, out_st, out_sc;
+  const float* short_w;     /* device (3*d_model, 3): short_filter.weight */
+  const float* short_b;     /* device (3*d_model):    short_filter.bias */
+  const float* spec[2];     /* device, from m2_filter_spectrum (filter_fn, filter_fn2) */
+  const float* bias[2];     /* device (d_model): filter_fn.bias, filter_fn2.bias */
+} m2_longconv_args;
+
+int m2_longconv_fwd(const m2_longconv_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Block-diagonal linear:  out[:, k*q:(k+1)*q] = x[:, k*p:(k+1)*p] @ w[k]^T (+ bias).
+ * Replaces BlockdiagMultiply.forward, bert/src/mm/blockdiag_multiply.py:49-60, and the
+ * bias add of StructuredLinear.forward, bert/src/mm/structured_linear.py:67-70.
+ *   x (m, in_features) row stride ldx, in_features <= nblocks*p (missing columns read as
+ *   zero: StructuredLinear.preprocess, structured_linear.py:52-56); w (nblocks, q, p)
+ *   contiguous; out (m, out_features) row stride ldo, out_features <= nblocks*q (extra
+ *   columns are cropped: postprocess, :58-62); x, w, out share `dtype`; bias float32
+ *   (out_features) or NULL.  With M2_BF16 the product is rounded to bf16 before the
+ *   (bf16-rounded) bias is added, as the reference does.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int m, nblocks, p, q;
+  int in_features, out_features;
+  m2_dtype dtype;
+  const void* x; long long ldx;
+  const void* w;
+  const float* bias;
+  void* out; long long ldo;
+} m2_blockdiag_args;
+
+int m2_blockdiag_fwd(const m2_blockdiag_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Gated half of the GLU MLP: h = gelu(G[:, :I]) * G[:, I:],  G = blockdiag(x, wg).
+ * Replaces gated_layers + the slice/GELU/multiply of BertGatedLinearUnitMLP.forward,
+ * bert/src/bert_layers.py:492-501; G itself is never written.
+ *   x (m, d_model); wg (nblocks, 2*inter/nblocks, d_model/nblocks); h (m, inter).
+ *   nblocks must be even (column j of G pairs with column j + inter, which lies nblocks/2
+ *   blocks further on and reads a different slice of x).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int m, d_model, inter, nblocks;
+  m2_dtype dtype;
+  const void* x; long long ldx;
+  const void* wg;
+  void* h; long long ldh;
+} m2_glu_args;
+
+int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * out = LayerNorm(a + b) over the last dimension (float32 statistics).
+ * Replaces `self.layernorm(hidden_states + residual_connection)`, bert/src/bert_layers.py:506.
+ * a, b (m, n) of `in_dtype` (the sum is rounded to bf16 first when in_dtype is M2_BF16, as a
+ * bf16 tensor add does); out (m, n) of `out_dtype`; weight/bias float32 (n).
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int m, n;
+  m2_dtype in_dtype, out_dtype;
+  const void* a; long long lda;
+  const void* b; long long ldb;
+  const float* weight; const float* bias;
+  float eps;
+  void* out; long long ldo;
+} m2_add_layernorm_args;
+
+int m2_add_layernorm_fwd(const m2_add_layernorm_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* M2_B200_H */

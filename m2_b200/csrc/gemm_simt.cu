@@ -1,0 +1,231 @@
+// Block-diagonal linear layers and the GLU epilogue on CUDA cores with float32
+// accumulation (the float32-activation path; bf16 activations use the tensor-core
+// kernels), plus the residual-add + LayerNorm that closes the MLP.
+//
+// Computation replaced: bert/src/mm/blockdiag_multiply.py:49-60,
+// bert/src/mm/structured_linear.py:52-70, bert/src/bert_layers.py:492-506.
+#include "common.cuh"
+
+namespace m2 {
+
+constexpr int GT = 64;      // output tile edge
+constexpr int GK = 16;      // k-chunk
+constexpr int GPAD = 4;
+
+// acc[4][4] += A[rows, K] * B[cols, K]^T for a 64x64 tile; A and B row-major with K
+// contiguous; rows >= m_valid / cols >= n_valid / k >= k_valid read as zero.
+template <typename T>
+__device__ __forceinline__ void tile_mma(const T* __restrict__ A, long long lda, int m_valid,
+                                         const T* __restrict__ Bm, long long ldb, int n_valid,
+                                         int K, int k_valid, float (&acc)[4][4],
+                                         float (*sA)[GT + GPAD], float (*sB)[GT + GPAD]) {
+  const int tid = threadIdx.x;
+  const int tx = tid % 16, ty = tid / 16;
+  const int lr = tid / 4, lk = (tid % 4) * 4;
+  for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int k = k0 + lk + e;
+      float av = 0.f, bv = 0.f;
+      if (k < k_valid) {
+        if (lr < m_valid) av = ld_as_float(A + (long long)lr * lda + k);
+        if (lr < n_valid) bv = ld_as_float(Bm + (long long)lr * ldb + k);
+      }
+      sA[lk + e][lr] = av;
+      sB[lk + e][lr] = bv;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GK; ++k) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { a[i] = sA[k][ty * 4 + i]; b[i] = sB[k][tx * 4 + i]; }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, bool ROUND>
+__global__ void __launch_bounds__(256)
+blockdiag_simt_kernel(const T* x, long long ldx, const T* w, const float* bias, T* out, long long ldo,
+                      int m, int p, int q, int in_features, int out_features) {
+  __shared__ float sA[GK][GT + GPAD], sB[GK][GT + GPAD];
+  const int kb = blockIdx.z;
+  const int row0 = blockIdx.y * GT, col0 = blockIdx.x * GT;
+  float acc[4][4] = {};
+  int k_valid = in_features - kb * p;
+  k_valid = k_valid < 0 ? 0 : (k_valid > p ? p : k_valid);
+  tile_mma<T>(x + (long long)row0 * ldx + (long long)kb * p, ldx, m - row0,
+              w + ((long long)kb * q + col0) * p, p, q - col0, p, k_valid, acc, sA, sB);
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= m) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cq = col0 + tx * 4 + j;
+      const int c = kb * q + cq;
+      if (cq >= q || c >= out_features) continue;
+      float v = rnd<ROUND>(acc[i][j]);
+      if (bias) v = rnd<ROUND>(v + rnd<ROUND>(__ldg(bias + c)));
+      st_from_float(out + (long long)r * ldo + c, v);
+    }
+  }
+}
+
+template <typename T, bool ROUND>
+__global__ void __launch_bounds__(256)
+blockdiag_glu_simt_kernel(const T* x, long long ldx, const T* wg, T* h, long long ldh,
+                          int m, int p, int q, int half_blocks) {
+  __shared__ float sA[GK][GT + GPAD], sB[GK][GT + GPAD];
+  const int kb = blockIdx.z;            // gated block; its partner is kb + half_blocks
+  const int kn = kb + half_blocks;
+  const int row0 = blockIdx.y * GT, col0 = blockIdx.x * GT;
+  float accg[4][4] = {}, accn[4][4] = {};
+  tile_mma<T>(x + (long long)row0 * ldx + (long long)kb * p, ldx, m - row0,
+              wg + ((long long)kb * q + col0) * p, p, q - col0, p, p, accg, sA, sB);
+  tile_mma<T>(x + (long long)row0 * ldx + (long long)kn * p, ldx, m - row0,
+              wg + ((long long)kn * q + col0) * p, p, q - col0, p, p, accn, sA, sB);
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = row0 + ty * 4 + i;
+    if (r >= m) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int cq = col0 + tx * 4 + j;
+      if (cq >= q) continue;
+      const float g = rnd<ROUND>(accg[i][j]), n = rnd<ROUND>(accn[i][j]);
+      const float act = rnd<ROUND>(gelu_erf(g));
+      st_from_float(h + (long long)r * ldh + (long long)kb * q + cq, rnd<ROUND>(act * n));
+    }
+  }
+}
+
+// out = LayerNorm(a + b); one CTA per row, the summed row cached in shared memory.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(256)
+add_layernorm_kernel(const TI* a, long long lda, const TI* b, long long ldb, const float* w,
+                     const float* bias, float eps, TO* out, long long ldo, int n) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const TI* pa = a + (long long)r * lda;
+  const TI* pb = b + (long long)r * ldb;
+  float sum = 0.f;
+  for (int i = tid; i < n; i += nt) {
+    float v = ld_as_float(pa + i) + ld_as_float(pb + i);
+    if (sizeof(TI) == 2) v = bf16r(v);
+    row[i] = v;
+    sum += v;
+  }
+  auto block_sum = [&](float v) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = v;
+    __syncthreads();
+    float t = (tid < (nt >> 5)) ? red[tid] : 0.f;
+    if (tid < 32) for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (tid == 0) red[0] = t;
+    __syncthreads();
+    return red[0];
+  };
+  const float mean = block_sum(sum) / n;
+  float sq = 0.f;
+  for (int i = tid; i < n; i += nt) { const float d = row[i] - mean; sq += d * d; }
+  const float var = block_sum(sq) / n;
+  const float rstd = rsqrtf(var + eps);
+  TO* po = out + (long long)r * ldo;
+  for (int i = tid; i < n; i += nt)
+    st_from_float(po + i, (row[i] - mean) * rstd * __ldg(w + i) + __ldg(bias + i));
+}
+
+int blockdiag_tc_launch(const m2_blockdiag_args* a, cudaStream_t st);   // gemm_tc.cu
+int glu_tc_launch(const m2_glu_args* a, cudaStream_t st);
+bool blockdiag_tc_supported(const m2_blockdiag_args* a);
+bool glu_tc_supported(const m2_glu_args* a);
+
+}  // namespace m2
+
+extern "C" int m2_blockdiag_fwd(const m2_blockdiag_args* a, void* stream) {
+  using namespace m2;
+  M2_REQUIRE(a != nullptr, M2_ERR_ARG, "m2_blockdiag_fwd: args is NULL");
+  M2_REQUIRE(a->m >= 0 && a->nblocks > 0 && a->p > 0 && a->q > 0, M2_ERR_ARG,
+             "m2_blockdiag_fwd: bad sizes m=%d nblocks=%d p=%d q=%d", a->m, a->nblocks, a->p, a->q);
+  M2_REQUIRE(a->in_features > 0 && a->in_features <= a->nblocks * a->p && a->out_features > 0 &&
+             a->out_features <= a->nblocks * a->q, M2_ERR_ARG,
+             "m2_blockdiag_fwd: in_features=%d / out_features=%d do not fit %d blocks of (%d -> %d)",
+             a->in_features, a->out_features, a->nblocks, a->p, a->q);
+  if (a->m == 0) return M2_OK;
+  M2_REQUIRE(a->x && a->w && a->out, M2_ERR_ARG, "m2_blockdiag_fwd: NULL tensor pointer");
+  M2_REQUIRE(a->ldx >= a->in_features && a->ldo >= a->out_features, M2_ERR_ARG,
+             "m2_blockdiag_fwd: row stride smaller than the row");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (blockdiag_tc_supported(a)) return blockdiag_tc_launch(a, st);
+  dim3 grid((a->q + GT - 1) / GT, (a->m + GT - 1) / GT, a->nblocks);
+  M2_REQUIRE(grid.y <= 65535 && grid.z <= 65535, M2_ERR_UNSUPPORTED, "m2_blockdiag_fwd: too many row tiles");
+  if (a->dtype == M2_BF16)
+    blockdiag_simt_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)a->x, a->ldx, (const __nv_bfloat16*)a->w, a->bias, (__nv_bfloat16*)a->out,
+        a->ldo, a->m, a->p, a->q, a->in_features, a->out_features);
+  else
+    blockdiag_simt_kernel<float, false><<<grid, 256, 0, st>>>(
+        (const float*)a->x, a->ldx, (const float*)a->w, a->bias, (float*)a->out, a->ldo, a->m, a->p,
+        a->q, a->in_features, a->out_features);
+  M2_LAUNCH_CHECK("blockdiag_simt_kernel");
+  return M2_OK;
+}
+
+extern "C" int m2_blockdiag_glu_fwd(const m2_glu_args* a, void* stream) {
+  using namespace m2;
+  M2_REQUIRE(a != nullptr, M2_ERR_ARG, "m2_blockdiag_glu_fwd: args is NULL");
+  M2_REQUIRE(a->m >= 0 && a->d_model > 0 && a->inter > 0 && a->nblocks > 0, M2_ERR_ARG,
+             "m2_blockdiag_glu_fwd: bad sizes");
+  M2_REQUIRE(a->nblocks % 2 == 0, M2_ERR_UNSUPPORTED, "m2_blockdiag_glu_fwd: nblocks must be even");
+  M2_REQUIRE(a->d_model % a->nblocks == 0 && (2 * a->inter) % a->nblocks == 0, M2_ERR_UNSUPPORTED,
+             "m2_blockdiag_glu_fwd: d_model and 2*inter must be multiples of nblocks");
+  if (a->m == 0) return M2_OK;
+  M2_REQUIRE(a->x && a->wg && a->h, M2_ERR_ARG, "m2_blockdiag_glu_fwd: NULL tensor pointer");
+  M2_REQUIRE(a->ldx >= a->d_model && a->ldh >= a->inter, M2_ERR_ARG,
+             "m2_blockdiag_glu_fwd: row stride smaller than the row");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (glu_tc_supported(a)) return glu_tc_launch(a, st);
+  const int p = a->d_model / a->nblocks, q = 2 * a->inter / a->nblocks;
+  dim3 grid((q + GT - 1) / GT, (a->m + GT - 1) / GT, a->nblocks / 2);
+  M2_REQUIRE(grid.y <= 65535, M2_ERR_UNSUPPORTED, "m2_blockdiag_glu_fwd: too many row tiles");
+  if (a->dtype == M2_BF16)
+    blockdiag_glu_simt_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)a->x, a->ldx, (const __nv_bfloat16*)a->wg, (__nv_bfloat16*)a->h, a->ldh,
+        a->m, p, q, a->nblocks / 2);
+  else
+    blockdiag_glu_simt_kernel<float, false><<<grid, 256, 0, st>>>(
+        (const float*)a->x, a->ldx, (const float*)a->wg, (float*)a->h, a->ldh, a->m, p, q, a->nblocks / 2);
+  M2_LAUNCH_CHECK("blockdiag_glu_simt_kernel");
+  return M2_OK;
+}
+
+extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream) {
+  using namespace m2;
+  M2_REQUIRE(a != nullptr, M2_ERR_ARG, "m2_add_layernorm_fwd: args is NULL");
+  M2_REQUIRE(a->m >= 0 && a->n > 0, M2_ERR_ARG, "m2_add_layernorm_fwd: bad sizes m=%d n=%d", a->m, a->n);
+  M2_REQUIRE(a->n <= 12288, M2_ERR_UNSUPPORTED, "m2_add_layernorm_fwd: n > 12288");
+  if (a->m == 0) return M2_OK;
+  M2_REQUIRE(a->a && a->b && a->weight && a->bias && a->out, M2_ERR_ARG, "m2_add_layernorm_fwd: NULL tensor pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = (size_t)a->n * sizeof(float);
+  const int threads = a->n >= 1024 ? 256 : 128;
+#define M2_LN(TI, TO) add_layernorm_kernel<TI, TO><<<a->m, threads, smem, st>>>( \
+      (const TI*)a->a, a->lda, (const TI*)a->b, a->ldb, a->weight, a->bias, a->eps, (TO*)a->out, a->ldo, a->n)
+  if (a->in_dtype == M2_BF16 && a->out_dtype == M2_F32) M2_LN(__nv_bfloat16, float);
+  else if (a->in_dtype == M2_BF16 && a->out_dtype == M2_BF16) M2_LN(__nv_bfloat16, __nv_bfloat16);
+  else if (a->in_dtype == M2_F32 && a->out_dtype == M2_F32) M2_LN(float, float);
+  else return m2_set_error(M2_ERR_UNSUPPORTED, "m2_add_layernorm_fwd: unsupported dtype combination");
+#undef M2_LN
+  M2_LAUNCH_CHECK("add_layernorm_kernel");
+  return M2_OK;
+}

@@ -1,0 +1,57 @@
+// Entry points of the fused gated long convolution: kernel-family selection, filter
+// spectrum tables, argument validation.
+#include "common.cuh"
+
+namespace m2 {
+int longconv_simt_launch(const m2_longconv_args* a, cudaStream_t st);
+int spectrum_kind0_launch(int D, int L, const float* k, float* spec, cudaStream_t st);
+int longconv_tc_supported(int seq_len, m2_dtype act_dtype);
+size_t spectrum_kind1_floats(int D, int L);
+int spectrum_kind1_launch(int D, int L, const float* k, float* spec, cudaStream_t st);
+int longconv_tc_launch(const m2_longconv_args* a, cudaStream_t st);
+}  // namespace m2
+
+extern "C" int m2_longconv_kind(int seq_len, m2_dtype act_dtype) {
+  return m2::longconv_tc_supported(seq_len, act_dtype) ? 1 : 0;
+}
+
+extern "C" size_t m2_filter_spectrum_floats(int kind, int d_model, int seq_len) {
+  if (d_model <= 0 || seq_len <= 0) return 0;
+  if (kind == 1) return m2::spectrum_kind1_floats(d_model, seq_len);
+  const size_t M = (size_t)m2_filter_row_len(seq_len) / 2;
+  return M + 4 * M * (size_t)d_model;
+}
+
+extern "C" int m2_filter_spectrum(int kind, int d_model, int seq_len, const float* k, float* spec_out,
+                                  void* stream) {
+  M2_REQUIRE(d_model > 0 && seq_len > 0, M2_ERR_ARG, "m2_filter_spectrum: sizes must be positive");
+  M2_REQUIRE(k && spec_out, M2_ERR_ARG, "m2_filter_spectrum: NULL pointer");
+  M2_REQUIRE(m2_aligned(k, 8) && m2_aligned(spec_out, 16), M2_ERR_ALIGN,
+             "m2_filter_spectrum: k must be 8-byte and spec_out 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (kind == 0) return m2::spectrum_kind0_launch(d_model, seq_len, k, spec_out, st);
+  if (kind == 1) return m2::spectrum_kind1_launch(d_model, seq_len, k, spec_out, st);
+  return m2_set_error(M2_ERR_ARG, "m2_filter_spectrum: unknown kind %d", kind);
+}
+
+extern "C" int m2_longconv_fwd(const m2_longconv_args* a, void* stream) {
+  M2_REQUIRE(a != nullptr, M2_ERR_ARG, "m2_longconv_fwd: args is NULL");
+  M2_REQUIRE(a->batch >= 0 && a->seq_len > 0 && a->d_model > 0, M2_ERR_ARG,
+             "m2_longconv_fwd: bad sizes batch=%d seq_len=%d d_model=%d", a->batch, a->seq_len, a->d_model);
+  M2_REQUIRE(a->n_filters == 1 || a->n_filters == 2, M2_ERR_ARG, "m2_longconv_fwd: n_filters must be 1 or 2");
+  M2_REQUIRE(!a->plain || a->n_filters == 1, M2_ERR_ARG, "m2_longconv_fwd: plain mode takes one filter");
+  if (a->batch == 0) return M2_OK;
+  M2_REQUIRE(a->xin && a->out && (a->plain || (a->short_w && a->short_b)) && a->spec[0] && a->bias[0], M2_ERR_ARG,
+             "m2_longconv_fwd: NULL tensor pointer");
+  M2_REQUIRE(a->n_filters == 1 || (a->u && a->spec[1] && a->bias[1]), M2_ERR_ARG,
+             "m2_longconv_fwd: residual filter requested but u/spec[1]/bias[1] is NULL");
+  M2_REQUIRE(a->xin_st == 1 || a->xin_sc == 1, M2_ERR_UNSUPPORTED,
+             "m2_longconv_fwd: xin must be contiguous along time or along channels");
+  M2_REQUIRE(a->batch <= 65535, M2_ERR_UNSUPPORTED, "m2_longconv_fwd: batch > 65535");
+  M2_REQUIRE(m2_aligned(a->spec[0], 16) && (a->n_filters == 1 || m2_aligned(a->spec[1], 16)), M2_ERR_ALIGN,
+             "m2_longconv_fwd: spectrum tables must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->kind == 0 || a->plain) return m2::longconv_simt_launch(a, st);
+  if (a->kind == 1) return m2::longconv_tc_launch(a, st);
+  return m2_set_error(M2_ERR_ARG, "m2_longconv_fwd: unknown kind %d", a->kind);
+}

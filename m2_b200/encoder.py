@@ -1,0 +1,141 @@
+"""Host-side M2-BERT encoder around the accelerated mixer and MLP: embeddings, the layer
+loop and (optionally) the MLM-free encoder output.  Parameter names follow the reference's
+BertModel (bert/src/bert_layers.py:131-252 embeddings, :511-599 layer, :602-813 encoder,
+:880-1021 model) so a reference state_dict loads unchanged:
+
+    embeddings.{word,position,token_type}_embeddings.weight, embeddings.LayerNorm.*,
+    encoder.layer.<i>.attention.* (mixer), encoder.layer.<i>.mlp.* (GLU MLP)
+
+Unlike the reference's BertLayer this loop has no per-layer ``isnan().any()``
+device-to-host synchronisation; ``check_finite=True`` restores an equivalent check once,
+on the final output.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn as nn
+
+from .glu_mlp import BertGatedLinearUnitMLP
+from .sequence_mixer import MonarchMixerSequenceMixing
+
+
+@dataclass
+class M2BertConfig:
+    """The fields of the reference's BertConfig (bert/src/configuration_bert.py) that the
+    Monarch-Mixer branch reads; defaults are the 80M pretraining yaml's."""
+    vocab_size: int = 30528
+    hidden_size: int = 768
+    intermediate_size: int = 3072
+    num_hidden_layers: int = 12
+    max_position_embeddings: int = 128
+    type_vocab_size: int = 2
+    pad_token_id: int = 0
+    layer_norm_eps: float = 1e-12
+    hidden_dropout_prob: float = 0.1
+    use_positional_encodings: bool = True
+    monarch_mixer_sequence_mixing: bool = True
+    use_glu_mlp: bool = True
+    use_monarch_mlp: bool = True
+    monarch_mlp_nblocks: int = 4
+    long_conv_l_max: int = 128
+    long_conv_kernel_learning_rate: float = 1e-3
+    bidirectional: bool = True
+    residual_long_conv: bool = True
+    hyena_lr_pos_emb: float = 1e-5
+    hyena_w: int = 10
+    hyena_w_mod: int = 1
+    hyena_wd: float = 0.1
+    hyena_emb_dim: int = 5
+    hyena_filter_dropout: float = 0.0
+    hyena_filter_order: int = 128
+    hyena_training_additions: bool = False
+
+
+class M2BertEmbeddings(nn.Module):
+    """word + token-type (+ learned position) embeddings, LayerNorm, dropout."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.word_embeddings = nn.Embedding(config.vocab_size, config.hidden_size,
+                                            padding_idx=config.pad_token_id)
+        self.use_positional_encodings = config.use_positional_encodings
+        if config.use_positional_encodings:
+            self.position_embeddings = nn.Embedding(config.max_position_embeddings, config.hidden_size)
+            self.register_buffer("position_ids",
+                                 torch.arange(config.max_position_embeddings).expand((1, -1)))
+        self.token_type_embeddings = nn.Embedding(config.type_vocab_size, config.hidden_size)
+        self.LayerNorm = nn.LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
+        self.dropout = nn.Dropout(config.hidden_dropout_prob)
+
+    def forward(self, input_ids, token_type_ids=None, position_ids=None):
+        L = input_ids.shape[1]
+        e = self.word_embeddings(input_ids)
+        if token_type_ids is None:
+            e = e + self.token_type_embeddings.weight[0]
+        else:
+            e = e + self.token_type_embeddings(token_type_ids)
+        if self.use_positional_encodings:
+            if position_ids is None:
+                position_ids = self.position_ids[:, :L]
+            e = e + self.position_embeddings(position_ids)
+        return self.dropout(self.LayerNorm(e))
+
+
+class M2BertLayer(nn.Module):
+    """Sequence mixing then state mixing; no residual or LayerNorm around the mixer."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.attention = MonarchMixerSequenceMixing(
+            config.hidden_size, l_max=config.long_conv_l_max,
+            hyena_kernel_lr=config.long_conv_kernel_learning_rate,
+            bidirectional=config.bidirectional, hyena_lr_pos_emb=config.hyena_lr_pos_emb,
+            hyena_w=config.hyena_w, hyena_w_mod=config.hyena_w_mod, hyena_wd=config.hyena_wd,
+            hyena_emb_dim=config.hyena_emb_dim, hyena_filter_dropout=config.hyena_filter_dropout,
+            hyena_filter_order=config.hyena_filter_order,
+            residual_long_conv=config.residual_long_conv,
+            hyena_training_additions=config.hyena_training_additions)
+        self.mlp = BertGatedLinearUnitMLP(config)
+
+    def forward(self, hidden_states):
+        mixed, _ = self.attention(hidden_states)
+        return self.mlp(mixed)
+
+
+class M2BertEncoder(nn.Module):
+    def __init__(self, config):
+        super().__init__()
+        self.layer = nn.ModuleList([M2BertLayer(config) for _ in range(config.num_hidden_layers)])
+
+    def forward(self, hidden_states, attention_mask=None, output_all_encoded_layers=False):
+        # the mask does not enter the Monarch-Mixer layers (the reference passes it to the
+        # layer, which ignores it on this branch); padded positions are mixed like any other
+        outs = []
+        for layer in self.layer:
+            hidden_states = layer(hidden_states)
+            if output_all_encoded_layers:
+                outs.append(hidden_states)
+        if not output_all_encoded_layers:
+            outs.append(hidden_states)
+        return outs
+
+
+class M2BertModel(nn.Module):
+    """Embeddings + encoder; forward(input_ids, ...) -> (sequence_output, None)."""
+
+    def __init__(self, config, check_finite=False):
+        super().__init__()
+        self.config = config
+        self.embeddings = M2BertEmbeddings(config)
+        self.encoder = M2BertEncoder(config)
+        self.check_finite = check_finite
+
+    def forward(self, input_ids, token_type_ids=None, attention_mask=None, position_ids=None,
+                output_all_encoded_layers=False):
+        h = self.embeddings(input_ids, token_type_ids, position_ids)
+        outs = self.encoder(h, attention_mask, output_all_encoded_layers)
+        if self.check_finite and not torch.isfinite(outs[-1]).all():
+            raise ValueError("non-finite values in the encoder output")
+        return (outs if output_all_encoded_layers else outs[-1]), None

@@ -1,0 +1,55 @@
+"""The GLU feed-forward block of an M2-BERT layer on BlockdiagLinear weights, with the
+reference's constructor, forward signature and state_dict keys (reference:
+bert/src/bert_layers.py:457-508): gated_layers, wo, layernorm.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from .blockdiag_linear import BlockdiagLinear, _compute_dtype
+
+
+class BertGatedLinearUnitMLP(nn.Module):
+    """LayerNorm(wo(gelu(G[..., :I]) * G[..., I:]) + x),  G = gated_layers(x).
+
+    `config` needs hidden_size, intermediate_size, monarch_mlp_nblocks, layer_norm_eps,
+    hidden_dropout_prob (and use_monarch_mlp=True: dense nn.Linear layers are the
+    reference's other option and are not what this package accelerates).  G is never
+    materialised: the gated GEMM applies GELU and the product in its epilogue.
+    """
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        if not getattr(config, "use_monarch_mlp", True):
+            raise NotImplementedError("m2_b200.BertGatedLinearUnitMLP needs use_monarch_mlp=True")
+        self.is_padded = getattr(config, "monarch_mixer_sequence_mixing", True)
+        nb = config.monarch_mlp_nblocks
+        self.gated_layers = BlockdiagLinear(config.hidden_size, config.intermediate_size * 2,
+                                            bias=False, nblocks=nb)
+        self.act = nn.GELU(approximate="none")
+        self.wo = BlockdiagLinear(config.intermediate_size, config.hidden_size, nblocks=nb)
+        self.dropout = nn.Dropout(config.hidden_dropout_prob)
+        self.layernorm = nn.LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        from .sequence_mixer import _check_forward_only
+        _check_forward_only(self, hidden_states)
+        if self.training and self.dropout.p > 0:
+            raise RuntimeError("m2_b200: dropout inside the fused MLP is not implemented; use eval()")
+        cfg = self.config
+        x = hidden_states
+        dt = _compute_dtype(x)
+        x2 = x.reshape(-1, x.shape[-1])
+        if x2.dtype != dt:
+            x2 = x2.to(dt)
+        h = ops.blockdiag_glu_fwd(x2, self.gated_layers._weight_as(dt), cfg.intermediate_size)
+        o = ops.blockdiag_fwd(h, self.wo._weight_as(dt), self.wo.bias, cfg.intermediate_size,
+                              cfg.hidden_size)
+        # under autocast LayerNorm runs in float32 and returns float32
+        out_dtype = torch.float32 if dt == torch.bfloat16 else dt
+        y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,
+                                  self.layernorm.eps, out_dtype)
+        return y.reshape(x.shape)

@@ -1,0 +1,221 @@
+"""Tensor-level wrappers over the C ABI: validate, allocate outputs with torch, launch on
+torch's current stream.  These are what the nn.Modules call."""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+from ._lib import M2_BF16, M2_F32
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return M2_F32
+    if t.dtype == torch.bfloat16:
+        return M2_BF16
+    raise TypeError(f"m2_b200 supports float32 and bfloat16 tensors, got {t.dtype}")
+
+
+def _stream(t: torch.Tensor):
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("m2_b200 kernels need CUDA tensors; there is no CPU fallback")
+
+
+def _f32c(t: torch.Tensor) -> torch.Tensor:
+    t = t.detach()
+    if t.dtype != torch.float32:
+        t = t.float()
+    return t.contiguous()
+
+
+def filter_row_len(seq_len: int) -> int:
+    return _lib.lib().m2_filter_row_len(int(seq_len))
+
+
+def hyena_filter(z, t, weights, biases, weights_rev, biases_rev, freq, deltas, seq_len, *,
+                 bidirectional, bf16_rounding, w_mod=1.0, shift=0.0):
+    """Merged time-domain filter (d_model, filter_row_len(seq_len)) float32.
+
+    z (1, l_max, emb), t (1, l_max, 1): positional embedding buffers; weights = the four
+    Linear weights of the filter MLP, biases = the first three biases (the *_rev lists are
+    the reversed-direction net, ignored unless bidirectional).
+    """
+    _need_cuda(z)
+    L = int(seq_len)
+    d_model, order = weights[3].shape
+    emb = weights[0].shape[1]
+    keep = []
+
+    def ptr(x):
+        x = _f32c(x)
+        keep.append(x)
+        return x.data_ptr()
+
+    a = _lib.FilterArgs()
+    a.d_model, a.seq_len, a.order, a.emb_dim = d_model, L, order, emb
+    a.bidirectional, a.bf16_rounding = int(bool(bidirectional)), int(bool(bf16_rounding))
+    a.w_mod, a.shift = float(w_mod), float(shift)
+    a.z = ptr(z[0, :L])
+    a.t = ptr(t[0, :L, 0])
+    for i in range(4):
+        a.w[i] = ptr(weights[i])
+    for i in range(3):
+        a.b[i] = ptr(biases[i])
+    if bidirectional:
+        for i in range(4):
+            a.w_rev[i] = ptr(weights_rev[i])
+        for i in range(3):
+            a.b_rev[i] = ptr(biases_rev[i])
+    a.freq = ptr(freq.reshape(-1))
+    a.deltas = ptr(deltas.reshape(-1))
+    k = torch.empty((d_model, filter_row_len(L)), dtype=torch.float32, device=z.device)
+    a.k_out = k.data_ptr()
+    with torch.cuda.device(z.device):
+        _lib.check(_lib.lib().m2_hyena_filter(C.byref(a), _stream(z)), "m2_hyena_filter")
+    return k
+
+
+def longconv_kind(seq_len: int, act_dtype: torch.dtype) -> int:
+    return _lib.lib().m2_longconv_kind(int(seq_len), M2_BF16 if act_dtype == torch.bfloat16 else M2_F32)
+
+
+def filter_spectrum(k: torch.Tensor, seq_len: int, kind: int) -> torch.Tensor:
+    """Spectrum table of one filter for kernel family `kind` (float32, opaque layout)."""
+    _need_cuda(k)
+    assert k.dtype == torch.float32 and k.is_contiguous()
+    d_model = k.shape[0]
+    n = _lib.lib().m2_filter_spectrum_floats(kind, d_model, int(seq_len))
+    spec = torch.empty(n, dtype=torch.float32, device=k.device)
+    with torch.cuda.device(k.device):
+        _lib.check(_lib.lib().m2_filter_spectrum(kind, d_model, int(seq_len), k.data_ptr(),
+                                                 spec.data_ptr(), _stream(k)), "m2_filter_spectrum")
+    return spec
+
+
+def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding, out=None):
+    """Fused short conv + gates + long convolution(s).
+
+    xin (B, L, 3D) in_linear output (any strides with a unit stride along L or channels),
+    u (B, L, D) raw layer input or None, specs/biases: one entry per filter.  Returns
+    (B, L, D) in xin's dtype.
+    """
+    _need_cuda(xin)
+    B, L, D3 = xin.shape
+    D = D3 // 3
+    nf = len(specs)
+    if out is None:
+        out = torch.empty((B, L, D), dtype=xin.dtype, device=xin.device)
+    keep = [_f32c(short_w.reshape(D3, -1)), _f32c(short_b)] + [_f32c(b) for b in biases]
+    if keep[0].shape[1] != 3:
+        raise RuntimeError("m2_b200: short_filter must have kernel_size 3")
+    a = _lib.LongconvArgs()
+    a.batch, a.seq_len, a.d_model, a.n_filters, a.kind = B, L, D, nf, int(kind)
+    a.act_dtype = _dt(xin)
+    a.u_dtype = _dt(u) if u is not None else a.act_dtype
+    a.bf16_rounding = int(bool(bf16_rounding))
+    a.xin, (a.xin_sb, a.xin_st, a.xin_sc) = xin.data_ptr(), xin.stride()
+    if u is not None:
+        a.u, (a.u_sb, a.u_st, a.u_sc) = u.data_ptr(), u.stride()
+    a.out, (a.out_sb, a.out_st, a.out_sc) = out.data_ptr(), out.stride()
+    a.short_w, a.short_b = keep[0].data_ptr(), keep[1].data_ptr()
+    for i in range(nf):
+        a.spec[i] = specs[i].data_ptr()
+        a.bias[i] = keep[2 + i].data_ptr()
+    with torch.cuda.device(xin.device):
+        _lib.check(_lib.lib().m2_longconv_fwd(C.byref(a), _stream(xin)), "m2_longconv_fwd")
+    return out
+
+
+def blockdiag_fwd(x2d, w, bias, in_features, out_features):
+    """x2d (m, in_features) @ blockdiag(w)^T (+ bias) -> (m, out_features), dtype of x2d."""
+    _need_cuda(x2d, w)
+    nb, q, p = w.shape
+    if x2d.stride(-1) != 1:
+        x2d = x2d.contiguous()
+    m = x2d.shape[0]
+    out = torch.empty((m, out_features), dtype=x2d.dtype, device=x2d.device)
+    b = _f32c(bias) if bias is not None else None
+    a = _lib.BlockdiagArgs()
+    a.m, a.nblocks, a.p, a.q = m, nb, p, q
+    a.in_features, a.out_features, a.dtype = int(in_features), int(out_features), _dt(x2d)
+    a.x, a.ldx, a.w = x2d.data_ptr(), x2d.stride(0) if m > 1 else max(x2d.stride(0), in_features), w.data_ptr()
+    a.bias = b.data_ptr() if b is not None else None
+    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    assert w.dtype == x2d.dtype and w.is_contiguous()
+    with torch.cuda.device(x2d.device):
+        _lib.check(_lib.lib().m2_blockdiag_fwd(C.byref(a), _stream(x2d)), "m2_blockdiag_fwd")
+    return out
+
+
+def blockdiag_glu_fwd(x2d, wg, inter):
+    """h = gelu(G[:, :inter]) * G[:, inter:], G = x2d @ blockdiag(wg)^T, without writing G."""
+    _need_cuda(x2d, wg)
+    nb, q, p = wg.shape
+    if x2d.stride(-1) != 1:
+        x2d = x2d.contiguous()
+    m, d_model = x2d.shape
+    assert nb * p == d_model and nb * q == 2 * inter and wg.dtype == x2d.dtype and wg.is_contiguous()
+    h = torch.empty((m, inter), dtype=x2d.dtype, device=x2d.device)
+    a = _lib.GluArgs()
+    a.m, a.d_model, a.inter, a.nblocks, a.dtype = m, d_model, int(inter), nb, _dt(x2d)
+    a.x, a.ldx, a.wg = x2d.data_ptr(), max(x2d.stride(0), d_model), wg.data_ptr()
+    a.h, a.ldh = h.data_ptr(), h.stride(0)
+    with torch.cuda.device(x2d.device):
+        _lib.check(_lib.lib().m2_blockdiag_glu_fwd(C.byref(a), _stream(x2d)), "m2_blockdiag_glu_fwd")
+    return h
+
+
+def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype):
+    """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype."""
+    _need_cuda(a2d, b2d)
+    if a2d.stride(-1) != 1:
+        a2d = a2d.contiguous()
+    if b2d.stride(-1) != 1:
+        b2d = b2d.contiguous()
+    m, n = a2d.shape
+    assert b2d.shape == a2d.shape and b2d.dtype == a2d.dtype
+    out = torch.empty((m, n), dtype=out_dtype, device=a2d.device)
+    w, bb = _f32c(weight), _f32c(bias)
+    a = _lib.AddLayernormArgs()
+    a.m, a.n, a.in_dtype = m, n, _dt(a2d)
+    a.out_dtype = M2_BF16 if out_dtype == torch.bfloat16 else M2_F32
+    a.a, a.lda = a2d.data_ptr(), max(a2d.stride(0), n)
+    a.b, a.ldb = b2d.data_ptr(), max(b2d.stride(0), n)
+    a.weight, a.bias, a.eps = w.data_ptr(), bb.data_ptr(), float(eps)
+    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    with torch.cuda.device(a2d.device):
+        _lib.check(_lib.lib().m2_add_layernorm_fwd(C.byref(a), _stream(a2d)), "m2_add_layernorm_fwd")
+    return out
+
+
+def device_status() -> int:
+    v = C.c_int(0)
+    _lib.check(_lib.lib().m2_device_status(C.byref(v)), "m2_device_status")
+    return v.value
+
+
+def plain_longconv(x, filt, L, bf16_rounding, bias=None):
+    """HyenaFilter.forward alone: y = conv(x, k) + bias * x for x (B, d_model, L)."""
+    _need_cuda(x)
+    B, D, Lx = x.shape
+    assert Lx == L
+    spec = filt.spectrum(L, bf16_rounding, 0)
+    bvec = _f32c(filt.conv_bias(bias))
+    out = torch.empty_like(x)
+    a = _lib.LongconvArgs()
+    a.batch, a.seq_len, a.d_model, a.n_filters, a.plain, a.kind = B, L, D, 1, 1, 0
+    a.act_dtype = a.u_dtype = _dt(x)
+    a.bf16_rounding = int(bool(bf16_rounding))
+    a.xin, a.xin_sb, a.xin_sc, a.xin_st = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
+    a.out, a.out_sb, a.out_sc, a.out_st = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
+    a.spec[0], a.bias[0] = spec.data_ptr(), bvec.data_ptr()
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib().m2_longconv_fwd(C.byref(a), _stream(x)), "m2_longconv_fwd")
+    return out

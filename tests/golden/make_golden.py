@@ -1,0 +1,175 @@
+"""Generate the parity fixtures in this directory by running the REFERENCE on CPU.
+
+Usage (only where the reference checkout is mounted):
+
+    python -m tests.golden.make_golden /path/to/reference
+
+The reference's modules are imported in place with two shims (a stub ``opt_einsum``,
+whose ``contract`` the path binds but never calls, and a bare ``src`` package so that
+``bert/src/__init__.py`` -- which needs MosaicML Composer -- is skipped).  Weights and
+inputs come from ``cases.py``; for every case the reference is run in float64, float32
+and under ``torch.autocast("cpu", bfloat16)`` and a deterministic subsample of each
+output is stored in ``<case>.npz``.  Nothing of the reference's source is copied.
+"""
+from __future__ import annotations
+
+import contextlib
+import io
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+from tests.golden import cases as C
+
+
+def import_reference(ref_root):
+    bert = os.path.join(ref_root, "bert")
+    if "opt_einsum" not in sys.modules:
+        m = types.ModuleType("opt_einsum")
+        m.contract = None
+        sys.modules["opt_einsum"] = m
+    pkg = types.ModuleType("src")
+    pkg.__path__ = [os.path.join(bert, "src")]
+    sys.modules["src"] = pkg
+    for p in (bert, os.path.join(bert, "src")):
+        if p not in sys.path:
+            sys.path.insert(0, p)
+    from src.mm.monarch_mixer_sequence_mixer import MonarchMixerSequenceMixing
+    from src.mm.blockdiag_linear import BlockdiagLinear
+    import src.bert_layers as bert_layers
+    from src.configuration_bert import BertConfig
+    return MonarchMixerSequenceMixing, BlockdiagLinear, bert_layers, BertConfig
+
+
+def _load(module, sd):
+    t = {k: torch.from_numpy(np.asarray(v)) for k, v in sd.items()}
+    missing, unexpected = module.load_state_dict(t, strict=False)
+    missing = [m for m in missing if "position_ids" not in m and "pooler" not in m]
+    assert not missing and not unexpected, (missing, unexpected)
+
+
+class _LayerNormFp32(torch.nn.Module):
+    """LayerNorm as CUDA autocast runs it: float32 arithmetic on the upcast input."""
+
+    def __init__(self, ln):
+        super().__init__()
+        self.ln = ln.float()
+
+    def forward(self, x):
+        return self.ln(x.float())
+
+
+def _modes(fn, module, *inputs, bf16="autocast"):
+    """fn(module, *tensors) in float64, float32 and bfloat16.
+
+    bf16="autocast": under torch.autocast("cpu", bfloat16) -- the same cast policy as the
+    CUDA autocast the reference benchmarks under, for the ops the mixer uses.
+    bf16="cast": module and inputs converted to bfloat16.  BlockdiagMultiply casts its
+    inputs to bfloat16 only under *CUDA* autocast (torch.cuda.amp.custom_fwd,
+    bert/src/mm/blockdiag_multiply.py:50), which cannot be entered without a GPU;
+    converting the operands by hand runs the same reference code on the same dtypes.
+    bf16=None: no bfloat16 run.
+    """
+    out = {}
+    with torch.no_grad():
+        m64 = module.double()
+        out["fp64"] = fn(m64, *[i.double() if i.is_floating_point() else i for i in inputs])
+        m32 = module.float()
+        out["fp32"] = fn(m32, *inputs)
+        if bf16 == "autocast":
+            with torch.autocast("cpu", dtype=torch.bfloat16):
+                out["bf16"] = fn(m32, *inputs)
+        elif bf16 == "cast":
+            mb = module.bfloat16()
+            if hasattr(mb, "layernorm"):
+                mb.layernorm = _LayerNormFp32(mb.layernorm)
+            out["bf16"] = fn(mb, *[i.bfloat16() if i.is_floating_point() else i for i in inputs])
+    return out
+
+
+def run_case(name, cfg, ref):
+    Mixer, Blockdiag, bert_layers, BertConfig = ref
+    kind, seed = cfg["kind"], cfg["seed"]
+    store = {}
+
+    def put(key, tensor):
+        a = tensor.detach().to(torch.float64).numpy()
+        store[key] = C.subsample(a).astype(np.float32 if "fp64" not in key else np.float64)
+
+    if kind == "mixer":
+        l_max = cfg.get("l_max", cfg["L"])
+        with contextlib.redirect_stdout(io.StringIO()):
+            m = Mixer(cfg["D"], l_max=l_max, bidirectional=cfg["bidirectional"],
+                      hyena_emb_dim=cfg["emb"], hyena_filter_order=cfg["order"],
+                      hyena_w=cfg["w"], residual_long_conv=cfg["residual"],
+                      hyena_kernel_lr=1e-3, hyena_lr_pos_emb=1e-5).eval()
+        sd = C.mixer_state(seed, cfg["D"], l_max, cfg["emb"], cfg["order"], cfg["w"],
+                           cfg["bidirectional"], cfg["residual"])
+        _load(m, sd)
+        u = torch.from_numpy(C.randn(seed, "u", (cfg["B"], cfg["L"], cfg["D"])))
+        for mode, y in _modes(lambda mod, x: mod(x)[0], m, u).items():
+            put(f"out_{mode}", y)
+        L = cfg["L"]
+        filt = _modes(lambda mod: torch.stack(
+            [mod.filter_fn.filter(L)[0]] +
+            ([mod.filter_fn.filter_rev(L)[0]] if cfg["bidirectional"] else [])), m)
+        for mode, k in filt.items():
+            put(f"filter_{mode}", k)
+    elif kind == "blockdiag":
+        m = Blockdiag(cfg["inf"], cfg["outf"], bias=cfg["bias"], nblocks=cfg["nb"]).eval()
+        sd = {"weight": C.blockdiag_weight(seed, "weight", cfg["inf"], cfg["outf"], cfg["nb"])}
+        if cfg["bias"]:
+            sd["bias"] = C.randn(seed, "bias", (cfg["outf"],))
+        _load(m, sd)
+        x = torch.from_numpy(C.randn(seed, "x", (cfg["M"], cfg["inf"])))
+        for mode, y in _modes(lambda mod, a: mod(a), m, x, bf16="cast").items():
+            put(f"out_{mode}", y)
+    elif kind == "glu":
+        conf = BertConfig(hidden_size=cfg["D"], intermediate_size=cfg["I"], use_glu_mlp=True,
+                          use_monarch_mlp=True, monarch_mlp_nblocks=cfg["nb"],
+                          monarch_mixer_sequence_mixing=True, hidden_dropout_prob=0.1)
+        m = bert_layers.BertGatedLinearUnitMLP(conf).eval()
+        _load(m, C.mlp_state(seed, cfg["D"], cfg["I"], cfg["nb"]))
+        x = torch.from_numpy(C.randn(seed, "x", (cfg["B"], cfg["L"], cfg["D"])))
+        for mode, y in _modes(lambda mod, a: mod(a), m, x, bf16="cast").items():
+            put(f"out_{mode}", y)
+    elif kind == "encoder":
+        conf = BertConfig(vocab_size=cfg["vocab"], hidden_size=cfg["D"],
+                          intermediate_size=cfg["I"], num_hidden_layers=cfg["layers"],
+                          num_attention_heads=4, max_position_embeddings=cfg["L"],
+                          use_glu_mlp=True, use_monarch_mlp=True, monarch_mlp_nblocks=4,
+                          monarch_mixer_sequence_mixing=True, residual_long_conv=True,
+                          bidirectional=True, use_positional_encodings=True,
+                          hyena_filter_order=cfg["order"], hyena_emb_dim=5, hyena_w=10,
+                          hyena_wd=0.1, hyena_lr_pos_emb=1e-5, long_conv_l_max=cfg["L"],
+                          long_conv_kernel_learning_rate=1e-3, hyena_filter_dropout=0.0,
+                          hyena_training_additions=False)
+        with contextlib.redirect_stdout(io.StringIO()):
+            m = bert_layers.BertModel(conf, add_pooling_layer=False).eval()
+        _load(m, C.encoder_state(seed, cfg["layers"], cfg["D"], cfg["I"], cfg["L"],
+                                 vocab=cfg["vocab"], order=cfg["order"]))
+        ids = np.random.default_rng(seed).integers(0, cfg["vocab"], size=(cfg["B"], cfg["L"]))
+        ids_t = torch.from_numpy(ids)
+        for mode, y in _modes(lambda mod, a: mod(a)[0], m, ids_t, bf16=None).items():
+            put(f"out_{mode}", y)
+    else:
+        raise ValueError(kind)
+    return store
+
+
+def main():
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = import_reference(ref_root)
+    here = os.path.dirname(os.path.abspath(__file__))
+    torch.manual_seed(0)
+    for name, cfg in C.CASES.items():
+        store = run_case(name, cfg, ref)
+        np.savez_compressed(os.path.join(here, name + ".npz"), **store)
+        print(name, {k: v.shape for k, v in store.items()})
+
+
+if __name__ == "__main__":
+    main()
