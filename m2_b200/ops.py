@@ -10,6 +10,47 @@ from . import _lib
 from ._lib import M2_BF16, M2_F32
 
 
+LAUNCHES = 0          # kernels of this library launched since the counter was last reset
+PROFILE = None        # a LaunchProfile while a benchmark wants per-kernel device times
+
+
+class LaunchProfile:
+    """CUDA-event pairs around individual C-ABI launches, on the launching stream."""
+
+    def __init__(self):
+        self.events = {}
+
+    def names(self):
+        return sorted(self.events)
+
+    def count(self, name):
+        return len(self.events.get(name, []))
+
+    def mean_ms(self, name):
+        ev = self.events.get(name, [])
+        if not ev:
+            return None
+        torch.cuda.synchronize()
+        return sum(s.elapsed_time(e) for s, e in ev) / len(ev)
+
+
+def _launch(name, tensor, fn, *args):
+    """Call one launching C-ABI entry point on torch's current stream of tensor's device."""
+    global LAUNCHES
+    with torch.cuda.device(tensor.device):
+        st = torch.cuda.current_stream(tensor.device)
+        prof = PROFILE
+        if prof is not None:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(st)
+        rc = fn(*args, C.c_void_p(st.cuda_stream))
+        if prof is not None:
+            e.record(st)
+            prof.events.setdefault(name, []).append((s, e))
+    _lib.check(rc, name)
+    LAUNCHES += 1
+
+
 def _dt(t: torch.Tensor) -> int:
     if t.dtype == torch.float32:
         return M2_F32
@@ -77,8 +118,7 @@ def hyena_filter(z, t, weights, biases, weights_rev, biases_rev, freq, deltas, s
     a.deltas = ptr(deltas.reshape(-1))
     k = torch.empty((d_model, filter_row_len(L)), dtype=torch.float32, device=z.device)
     a.k_out = k.data_ptr()
-    with torch.cuda.device(z.device):
-        _lib.check(_lib.lib().m2_hyena_filter(C.byref(a), _stream(z)), "m2_hyena_filter")
+    _launch("m2_hyena_filter", z, _lib.lib().m2_hyena_filter, C.byref(a))
     return k
 
 
@@ -93,9 +133,8 @@ def filter_spectrum(k: torch.Tensor, seq_len: int, kind: int) -> torch.Tensor:
     d_model = k.shape[0]
     n = _lib.lib().m2_filter_spectrum_floats(kind, d_model, int(seq_len))
     spec = torch.empty(n, dtype=torch.float32, device=k.device)
-    with torch.cuda.device(k.device):
-        _lib.check(_lib.lib().m2_filter_spectrum(kind, d_model, int(seq_len), k.data_ptr(),
-                                                 spec.data_ptr(), _stream(k)), "m2_filter_spectrum")
+    _launch("m2_filter_spectrum", k, _lib.lib().m2_filter_spectrum, kind, d_model, int(seq_len),
+            k.data_ptr(), spec.data_ptr())
     return spec
 
 
@@ -128,8 +167,7 @@ def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding
     for i in range(nf):
         a.spec[i] = specs[i].data_ptr()
         a.bias[i] = keep[2 + i].data_ptr()
-    with torch.cuda.device(xin.device):
-        _lib.check(_lib.lib().m2_longconv_fwd(C.byref(a), _stream(xin)), "m2_longconv_fwd")
+    _launch("m2_longconv_fwd", xin, _lib.lib().m2_longconv_fwd, C.byref(a))
     return out
 
 
@@ -149,8 +187,7 @@ def blockdiag_fwd(x2d, w, bias, in_features, out_features):
     a.bias = b.data_ptr() if b is not None else None
     a.out, a.ldo = out.data_ptr(), out.stride(0)
     assert w.dtype == x2d.dtype and w.is_contiguous()
-    with torch.cuda.device(x2d.device):
-        _lib.check(_lib.lib().m2_blockdiag_fwd(C.byref(a), _stream(x2d)), "m2_blockdiag_fwd")
+    _launch("m2_blockdiag_fwd", x2d, _lib.lib().m2_blockdiag_fwd, C.byref(a))
     return out
 
 
@@ -167,8 +204,7 @@ def blockdiag_glu_fwd(x2d, wg, inter):
     a.m, a.d_model, a.inter, a.nblocks, a.dtype = m, d_model, int(inter), nb, _dt(x2d)
     a.x, a.ldx, a.wg = x2d.data_ptr(), max(x2d.stride(0), d_model), wg.data_ptr()
     a.h, a.ldh = h.data_ptr(), h.stride(0)
-    with torch.cuda.device(x2d.device):
-        _lib.check(_lib.lib().m2_blockdiag_glu_fwd(C.byref(a), _stream(x2d)), "m2_blockdiag_glu_fwd")
+    _launch("m2_blockdiag_glu_fwd", x2d, _lib.lib().m2_blockdiag_glu_fwd, C.byref(a))
     return h
 
 
@@ -190,8 +226,7 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype):
     a.b, a.ldb = b2d.data_ptr(), max(b2d.stride(0), n)
     a.weight, a.bias, a.eps = w.data_ptr(), bb.data_ptr(), float(eps)
     a.out, a.ldo = out.data_ptr(), out.stride(0)
-    with torch.cuda.device(a2d.device):
-        _lib.check(_lib.lib().m2_add_layernorm_fwd(C.byref(a), _stream(a2d)), "m2_add_layernorm_fwd")
+    _launch("m2_add_layernorm_fwd", a2d, _lib.lib().m2_add_layernorm_fwd, C.byref(a))
     return out
 
 
@@ -216,6 +251,5 @@ def plain_longconv(x, filt, L, bf16_rounding, bias=None):
     a.xin, a.xin_sb, a.xin_sc, a.xin_st = x.data_ptr(), x.stride(0), x.stride(1), x.stride(2)
     a.out, a.out_sb, a.out_sc, a.out_st = out.data_ptr(), out.stride(0), out.stride(1), out.stride(2)
     a.spec[0], a.bias[0] = spec.data_ptr(), bvec.data_ptr()
-    with torch.cuda.device(x.device):
-        _lib.check(_lib.lib().m2_longconv_fwd(C.byref(a), _stream(x)), "m2_longconv_fwd")
+    _launch("m2_longconv_plain", x, _lib.lib().m2_longconv_fwd, C.byref(a))
     return out

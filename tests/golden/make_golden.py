@@ -160,10 +160,35 @@ def run_case(name, cfg, ref):
     return store
 
 
+def dump_layout(ref, path):
+    """Names and shapes of the reference modules' state_dicts (drop-in contract)."""
+    import json
+    Mixer, Blockdiag, bert_layers, BertConfig = ref
+    with contextlib.redirect_stdout(io.StringIO()):
+        m = Mixer(768, l_max=128, bidirectional=True, hyena_emb_dim=5, hyena_filter_order=128,
+                  residual_long_conv=True)
+        conf = BertConfig(hidden_size=768, intermediate_size=3072, use_glu_mlp=True,
+                          use_monarch_mlp=True, monarch_mlp_nblocks=4,
+                          monarch_mixer_sequence_mixing=True)
+        mlp = bert_layers.BertGatedLinearUnitMLP(conf)
+        lin = Blockdiag(30, 50, nblocks=4)
+    shapes = lambda mod: {k: list(v.shape) for k, v in mod.state_dict().items()}
+    layout = {
+        "mixer": shapes(m),
+        "mixer_freq_params": [n for n, _ in m.named_parameters() if n.endswith("freq")],
+        "mixer_buffers": [n for n, _ in m.named_buffers()],
+        "glu": shapes(mlp),
+        "blockdiag_30_50": shapes(lin),
+    }
+    with open(path, "w") as f:
+        json.dump(layout, f, indent=1, sort_keys=True)
+
+
 def main():
     ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
     ref = import_reference(ref_root)
     here = os.path.dirname(os.path.abspath(__file__))
+    dump_layout(ref, os.path.join(here, "state_dict_layout.json"))
     torch.manual_seed(0)
     for name, cfg in C.CASES.items():
         store = run_case(name, cfg, ref)

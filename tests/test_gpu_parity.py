@@ -1,0 +1,295 @@
+"""Parity of the CUDA path (through the C ABI) with the oracle and the stored reference
+outputs.  All tests here need a B200."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import m2_b200
+from m2_b200 import ops
+from m2_b200.encoder import M2BertConfig, M2BertModel
+from oracle import m2_oracle as O
+from oracle import torch_oracle as T
+from tests.golden import cases as C
+from tests.helpers import build_glu, build_mixer, to_torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+TOL_FP32, TOL_BF16 = 1e-4, 2e-2          # on O.parity_error, the path's stated tolerances
+
+MIXER_CASES = sorted(n for n, c in C.CASES.items() if c["kind"] == "mixer")
+
+
+@pytest.fixture(autouse=True)
+def _no_grad_and_status():
+    with torch.no_grad():
+        yield
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+
+
+def npy(t):
+    return t.detach().float().cpu().double().numpy()
+
+
+# ---- filter --------------------------------------------------------------------------
+@pytest.mark.parametrize("name", MIXER_CASES)
+@pytest.mark.parametrize("mode", ["fp64", "bf16"])
+def test_hyena_filter(name, mode):
+    cfg = C.CASES[name]
+    m, sd = build_mixer(cfg, DEV)
+    L = cfg["L"]
+    k = npy(m.filter_fn.time_filter(L, mode == "bf16"))
+    R = k.shape[1]
+    kf = O.hyena_filter(sd, "filter_fn.", L, reverse=False, mode=mode).T
+    got_f = k[:, :L]
+    if cfg["bidirectional"]:
+        kr = O.hyena_filter(sd, "filter_fn.", L, reverse=True, mode=mode).T
+        got = np.stack([got_f, k[:, R - L:][:, ::-1]])
+        ref = np.stack([kf, kr])
+        assert np.all(k[:, L:R - L] == 0)
+    else:
+        got, ref = got_f, kf
+        assert np.all(k[:, L:] == 0)
+    if mode == "fp64":
+        assert O.parity_error(got, ref) < TOL_FP32
+    else:
+        rms = np.sqrt(np.mean(ref ** 2))
+        d = np.abs(got - ref)
+        assert np.sqrt(np.mean(d ** 2)) / rms < 1e-2     # see test_oracle_golden: chaotic taps
+        assert np.mean(d > 2e-2 * rms) < 5e-3
+    # the reference-API views of the same filter
+    with torch.autocast("cuda", dtype=torch.bfloat16, enabled=(mode == "bf16")):
+        assert np.array_equal(npy(m.filter_fn.filter(L))[0].T, got_f)
+
+
+# ---- mixer ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", MIXER_CASES)
+def test_mixer_fp32(name):
+    cfg = C.CASES[name]
+    m, sd = build_mixer(cfg, DEV)
+    u = C.randn(cfg["seed"], "u", (cfg["B"], cfg["L"], cfg["D"]))
+    y, none = m(torch.from_numpy(u).to(DEV))
+    assert none is None and y.dtype == torch.float32
+    gold = np.load(os.path.join(GOLD, name + ".npz"))
+    assert O.parity_error(C.subsample(npy(y)), gold["out_fp64"]) < TOL_FP32
+    if cfg["B"] * cfg["L"] * cfg["D"] <= 1 << 16:
+        ref = O.mixer_forward(sd, u, bidirectional=cfg["bidirectional"],
+                              residual_long_conv=cfg["residual"], mode="fp64")
+        assert O.parity_error(npy(y), ref) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", MIXER_CASES)
+@pytest.mark.parametrize("u_bf16", [False, True])
+def test_mixer_bf16_autocast(name, u_bf16):
+    cfg = C.CASES[name]
+    m, sd = build_mixer(cfg, DEV)
+    u = torch.from_numpy(C.randn(cfg["seed"], "u", (cfg["B"], cfg["L"], cfg["D"]))).to(DEV)
+    if u_bf16:
+        u = u.bfloat16()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y, _ = m(u)
+        ref_t = T.mixer_forward(to_torch(sd, DEV), u, bidirectional=cfg["bidirectional"],
+                                residual_long_conv=cfg["residual"])
+    assert y.dtype == torch.bfloat16
+    # against the stock-PyTorch-op path under the same autocast (what the reference runs)
+    assert O.parity_error(npy(y), npy(ref_t)) < TOL_BF16
+    # against the numpy oracle with autocast's rounding points, and the stored CPU-autocast output
+    if not u_bf16:
+        gold = np.load(os.path.join(GOLD, name + ".npz"))
+        assert O.parity_error(C.subsample(npy(y)), gold["out_bf16"]) < TOL_BF16
+    if cfg["B"] * cfg["L"] * cfg["D"] <= 1 << 16:
+        ref = O.mixer_forward(sd, npy(u), bidirectional=cfg["bidirectional"],
+                              residual_long_conv=cfg["residual"], mode="bf16", u_is_bf16=u_bf16)
+        assert O.parity_error(npy(y), ref) < TOL_BF16
+
+
+@pytest.mark.parametrize("L", [1, 2, 3, 24, 100, 128])
+def test_mixer_ragged_lengths(L):
+    """L below l_max, odd and non-power-of-two lengths (the reference slices filters to L)."""
+    cfg = dict(C.CASES["mixer_small"], L=L, l_max=128, D=24, B=2)
+    m, sd = build_mixer(cfg, DEV)
+    u = C.randn(5, "u", (2, L, 24))
+    y, _ = m(torch.from_numpy(u).to(DEV))
+    ref = O.mixer_forward(sd, u, bidirectional=True, residual_long_conv=True, mode="fp64")
+    assert O.parity_error(npy(y), ref) < TOL_FP32
+
+
+def test_mixer_empty_batch():
+    cfg = C.CASES["mixer_small"]
+    m, _ = build_mixer(cfg, DEV)
+    y, _ = m(torch.zeros((0, cfg["L"], cfg["D"]), device=DEV))
+    assert y.shape == (0, cfg["L"], cfg["D"])
+
+
+def test_plain_long_conv_impulse_and_linearity():
+    """HyenaFilter.forward alone: an impulse returns the filter taps; the map is linear."""
+    cfg = dict(C.CASES["mixer_small"], L=512, D=16, order=32)
+    m, sd = build_mixer(cfg, DEV)
+    f = m.filter_fn
+    L, D = 512, 16
+    s = 200
+    x = torch.zeros((1, D, L), device=DEV)
+    x[0, :, s] = 1.0
+    y = npy(f(x, L))[0]
+    kf = O.hyena_filter(sd, "filter_fn.", L, reverse=False).T
+    kr = O.hyena_filter(sd, "filter_fn.", L, reverse=True).T
+    expect = np.zeros((D, L))
+    expect[:, s:] = kf[:, :L - s]
+    expect[:, :s] = kr[:, :s][:, ::-1]
+    expect[:, s] += np.asarray(sd["filter_fn.bias"], np.float64)
+    assert O.parity_error(y, expect) < TOL_FP32
+    g = torch.Generator(device="cpu").manual_seed(3)
+    a = torch.randn((2, D, L), generator=g).to(DEV)
+    b = torch.randn((2, D, L), generator=g).to(DEV)
+    lhs = npy(f(2.0 * a - 3.0 * b, L))
+    rhs = 2.0 * npy(f(a, L)) - 3.0 * npy(f(b, L))
+    assert O.parity_error(lhs, rhs) < TOL_FP32
+    ref = O.fftconv(npy(a), O.merge_bidirectional(kf, kr), sd["filter_fn.bias"])
+    assert O.parity_error(npy(f(a, L)), ref) < TOL_FP32
+
+
+@pytest.mark.parametrize("L,B,D", [(8192, 2, 64), (16384, 1, 32)])
+def test_long_sequences_bf16(L, B, D):
+    """Long rows against the stock-op path under autocast; batch rows are independent."""
+    cfg = dict(C.CASES["mixer_small"], L=L, l_max=L, D=D, B=B, order=64, seed=77)
+    m, sd = build_mixer(cfg, DEV)
+    u = torch.from_numpy(C.randn(77, "u", (B, L, D))).to(DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y, _ = m(u)
+        ref = T.mixer_forward(to_torch(sd, DEV), u, bidirectional=True, residual_long_conv=True)
+        y0, _ = m(u[:1])
+    assert O.parity_error(npy(y), npy(ref)) < TOL_BF16
+    assert torch.equal(y0, y[:1])
+
+
+# ---- BlockdiagLinear and the GLU MLP -------------------------------------------------
+@pytest.mark.parametrize("name", sorted(n for n, c in C.CASES.items() if c["kind"] == "blockdiag"))
+@pytest.mark.parametrize("mode", ["fp64", "bf16"])
+def test_blockdiag_linear(name, mode):
+    cfg = C.CASES[name]
+    seed = cfg["seed"]
+    lin = m2_b200.BlockdiagLinear(cfg["inf"], cfg["outf"], bias=cfg["bias"], nblocks=cfg["nb"]).eval()
+    w = C.blockdiag_weight(seed, "weight", cfg["inf"], cfg["outf"], cfg["nb"])
+    b = C.randn(seed, "bias", (cfg["outf"],)) if cfg["bias"] else None
+    sd = {"weight": w}
+    if b is not None:
+        sd["bias"] = b
+    lin.load_state_dict(to_torch(sd))
+    lin = lin.to(DEV)
+    x = C.randn(seed, "x", (cfg["M"], cfg["inf"]))
+    xt = torch.from_numpy(x).to(DEV)
+    gold = np.load(os.path.join(GOLD, name + ".npz"))
+    if mode == "fp64":
+        y = lin(xt)
+        ref = O.blockdiag_linear(x, w, b, out_features=cfg["outf"], mode="fp64")
+        assert y.dtype == torch.float32
+        assert O.parity_error(npy(y), ref) < TOL_FP32
+        assert O.parity_error(C.subsample(npy(y)), gold["out_fp64"]) < TOL_FP32
+        # 3-D input and the un-biased product
+        y3 = lin.forward_matmul(xt.reshape(1, cfg["M"], cfg["inf"]))
+        ref3 = O.blockdiag_linear(x, w, None, out_features=cfg["outf"], mode="fp64")
+        assert O.parity_error(npy(y3)[0], ref3) < TOL_FP32
+    else:
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = lin(xt)
+        assert y.dtype == torch.bfloat16
+        ref = O.blockdiag_linear(x, w, b, out_features=cfg["outf"], mode="bf16")
+        assert O.parity_error(npy(y), ref) < TOL_BF16
+        assert O.parity_error(C.subsample(npy(y)), gold["out_bf16"]) < TOL_BF16
+
+
+def test_blockdiag_multiply_function_and_dense():
+    w = torch.from_numpy(C.blockdiag_weight(3, "w", 64, 96, 4)).to(DEV)
+    x = torch.from_numpy(C.randn(3, "x", (5, 7, 64))).to(DEV)
+    y = m2_b200.blockdiag_multiply(x, w)
+    dense = m2_b200.blockdiag_weight_to_dense_weight(w)
+    assert O.parity_error(npy(y), npy(x) @ npy(dense).T) < TOL_FP32
+
+
+@pytest.mark.parametrize("name", ["glu_small", "glu_80m"])
+@pytest.mark.parametrize("mode", ["fp64", "bf16"])
+def test_glu_mlp(name, mode):
+    cfg = C.CASES[name]
+    m, sd = build_glu(cfg, DEV)
+    x = C.randn(cfg["seed"], "x", (cfg["B"], cfg["L"], cfg["D"]))
+    xt = torch.from_numpy(x).to(DEV)
+    gold = np.load(os.path.join(GOLD, name + ".npz"))
+    if mode == "fp64":
+        y = m(xt)
+        assert O.parity_error(npy(y), O.glu_mlp_forward(sd, x, mode="fp64")) < TOL_FP32
+        assert O.parity_error(C.subsample(npy(y)), gold["out_fp64"]) < TOL_FP32
+    else:
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = m(xt.bfloat16())
+            ref_t = T.glu_mlp_forward(to_torch(sd, DEV), xt.bfloat16())
+        assert y.dtype == torch.float32
+        assert O.parity_error(npy(y), O.glu_mlp_forward(sd, x, mode="bf16")) < TOL_BF16
+        assert O.parity_error(npy(y), npy(ref_t)) < TOL_BF16
+        assert O.parity_error(C.subsample(npy(y)), gold["out_bf16"]) < TOL_BF16
+
+
+def test_glu_mlp_ragged_rows():
+    """Row counts that are not a multiple of any tile."""
+    cfg = dict(C.CASES["glu_small"], B=1, L=77)
+    m, sd = build_glu(cfg, DEV)
+    x = C.randn(9, "x", (1, 77, cfg["D"]))
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(torch.from_numpy(x).to(DEV).bfloat16())
+    assert O.parity_error(npy(y), O.glu_mlp_forward(sd, x, mode="bf16")) < TOL_BF16
+
+
+# ---- encoder -------------------------------------------------------------------------
+def _encoder(cfg, device):
+    conf = M2BertConfig(vocab_size=cfg["vocab"], hidden_size=cfg["D"], intermediate_size=cfg["I"],
+                        num_hidden_layers=cfg["layers"], max_position_embeddings=cfg["L"],
+                        long_conv_l_max=cfg["L"], hyena_filter_order=cfg["order"])
+    model = M2BertModel(conf).eval()
+    sd = C.encoder_state(cfg["seed"], cfg["layers"], cfg["D"], cfg["I"], cfg["L"],
+                         vocab=cfg["vocab"], order=cfg["order"])
+    missing, unexpected = model.load_state_dict(to_torch(sd), strict=False)
+    assert not unexpected and all("position_ids" in k for k in missing)
+    return model.to(device), sd
+
+
+def test_encoder_small_fp32_and_bf16():
+    cfg = C.CASES["encoder_small"]
+    model, sd = _encoder(cfg, DEV)
+    ids = np.random.default_rng(cfg["seed"]).integers(0, cfg["vocab"], size=(cfg["B"], cfg["L"]))
+    ids_t = torch.from_numpy(ids).to(DEV)
+    y, _ = model(ids_t)
+    gold = np.load(os.path.join(GOLD, "encoder_small.npz"))
+    assert O.parity_error(C.subsample(npy(y)), gold["out_fp64"]) < 5e-4   # two layers deep
+    sdt = to_torch(sd, DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        yb, _ = model(ids_t)
+        ref = T.encoder_forward(sdt, T.embeddings_forward(sdt, ids_t), cfg["layers"])
+    assert O.parity_error(npy(yb), npy(ref)) < TOL_BF16
+
+
+def test_encoder_80m_shape_bf16():
+    """Two 80M-shaped layers at the benchmark's (B, L) against the stock-op path."""
+    cfg = dict(kind="encoder", seed=43, B=16, L=128, D=768, I=3072, layers=2, vocab=30528, order=128)
+    model, sd = _encoder(cfg, DEV)
+    ids_t = torch.from_numpy(np.random.default_rng(1).integers(0, 30528, size=(16, 128))).to(DEV)
+    sdt = to_torch(sd, DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y, _ = model(ids_t)
+        ref = T.encoder_forward(sdt, T.embeddings_forward(sdt, ids_t), 2)
+    assert O.parity_error(npy(y), npy(ref)) < TOL_BF16
+
+
+# ---- error behaviour -----------------------------------------------------------------
+def test_errors_are_loud():
+    cfg = C.CASES["mixer_small"]
+    m, _ = build_mixer(cfg, DEV)
+    with pytest.raises(RuntimeError):
+        m(torch.zeros((1, cfg["L"], cfg["D"])))                  # CPU tensor: no fallback
+    with pytest.raises(RuntimeError):
+        m(torch.zeros((1, cfg["L"], cfg["D"]), device=DEV, dtype=torch.bfloat16))   # bf16 without autocast
+    with pytest.raises(RuntimeError):
+        m(torch.zeros((1, 2 * cfg["L"], cfg["D"]), device=DEV))  # longer than l_max
+    with torch.enable_grad(), pytest.raises(RuntimeError):
+        m(torch.zeros((1, cfg["L"], cfg["D"]), device=DEV))      # forward-only
