@@ -1,8 +1,317 @@
-// placeholder until the tensor-core GEMMs land
-#include "common.cuh"
+// Block-diagonal bf16 GEMMs on the 5th-generation tensor cores (tcgen05), operands staged
+// by TMA into 128-byte-swizzled shared memory, float32 accumulators in tensor memory.
+//
+//   plain: out[:, k*q + n] = x[:, k*p : (k+1)*p] . w[k][n, :]  (+ bias)            (wo)
+//   GLU  : h[:, k*q + n]   = gelu(x_k . wg[k][n, :]) * (x_{k+nb/2} . wg[k+nb/2][n, :])
+//          -- the gated GEMM with GELU and the product applied in the epilogue, so the
+//          (m, 2*inter) pre-activation is never written.
+//
+// One persistent CTA per SM walks output tiles of 128 rows x BN columns.  Warp 0 issues TMA
+// loads into a ring of shared-memory stages, warp 1 issues the MMAs (one thread) into one of
+// two TMEM accumulator buffers, warps 2-5 drain the other buffer (tcgen05.ld), apply the
+// epilogue with the reference's bf16 rounding points and store.  Every mbarrier wait is
+// bounded; a wait that runs out sets the device status word and the CTA winds down.
+//
+// Computation replaced: bert/src/mm/blockdiag_multiply.py:49-60 (torch.bmm per block),
+// bert/src/mm/structured_linear.py:67-70 (bias), bert/src/bert_layers.py:492-501 (GLU).
+#include "tc_common.cuh"
+
 namespace m2 {
-bool blockdiag_tc_supported(const m2_blockdiag_args*) { return false; }
-bool glu_tc_supported(const m2_glu_args*) { return false; }
-int blockdiag_tc_launch(const m2_blockdiag_args*, cudaStream_t) { return M2_ERR_UNSUPPORTED; }
-int glu_tc_launch(const m2_glu_args*, cudaStream_t) { return M2_ERR_UNSUPPORTED; }
+
+int m2_get_encode_fn(m2_encode_tiled_fn* fn) {
+  static m2_encode_tiled_fn cached = nullptr;
+  if (!cached) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !p)
+      return m2_set_error(M2_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cached = reinterpret_cast<m2_encode_tiled_fn>(p);
+  }
+  *fn = cached;
+  return M2_OK;
 }
+
+int m2_make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                         uint32_t box_rows) {
+  m2_encode_tiled_fn enc;
+  int rc = m2_get_encode_fn(&enc);
+  if (rc) return rc;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return m2_set_error(M2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  return M2_OK;
+}
+
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BK = 64;                 // one 128-byte swizzle row of bf16
+constexpr int THREADS = 192;
+constexpr int A_BYTES = BM * BK * 2;   // 16 KB
+constexpr int SMEM_BUDGET = 200 * 1024;
+
+struct Params {
+  int M, p, q, nb_out, pair_off, ntn, ntm, ksteps, total_tiles, out_cols;
+  void* out; long long ldo;
+  const float* bias;
+};
+
+template <int BN, bool GLU>
+struct Cfg {
+  static constexpr int NACC = GLU ? 2 : 1;
+  static constexpr int B_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = NACC * (A_BYTES + B_BYTES);
+  static constexpr int NSTAGES = (SMEM_BUDGET / STAGE_BYTES) > 8 ? 8 : (SMEM_BUDGET / STAGE_BYTES);
+  static constexpr int ACC_COLS = NACC * BN;         // TMEM columns of one accumulator buffer
+  static constexpr int TCOLS = (2 * ACC_COLS <= 32) ? 32 : (2 * ACC_COLS <= 64) ? 64 : (2 * ACC_COLS <= 128) ? 128
+                               : (2 * ACC_COLS <= 256) ? 256 : 512;
+  static constexpr int SMEM = NSTAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static_assert(2 * ACC_COLS <= 512, "accumulators exceed tensor memory");
+  static_assert(NSTAGES >= 2, "need at least two stages");
+};
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int BN, bool GLU>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params P) {
+  using C = Cfg<BN, GLU>;
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment is what the 128-byte swizzle pattern is anchored to
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::NSTAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::NSTAGES;
+  uint64_t* tfull = bars + 2 * C::NSTAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::NSTAGES; ++s) { tc::mbar_init(full + s, 1); tc::mbar_init(empty + s, 1); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull + b, 1); tc::mbar_init(tempty + b, 128); }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tmA);
+    tc::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, C::TCOLS);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
+        const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
+        for (int ks = 0; ks < P.ksteps; ++ks) {
+          if (!tc::mbar_wait(empty + stage, phase ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          unsigned char* st = smem + stage * C::STAGE_BYTES;
+          tc::mbar_expect_tx(full + stage, C::STAGE_BYTES);
+          tc::tma_load_2d(st, &tmA, full + stage, kb * P.p + ks * BK, mt * BM);
+          tc::tma_load_2d(st + A_BYTES, &tmB, full + stage, ks * BK, kb * P.q + nt * BN);
+          if (GLU) {
+            const int kn = kb + P.pair_off;
+            tc::tma_load_2d(st + A_BYTES + C::B_BYTES, &tmA, full + stage, kn * P.p + ks * BK, mt * BM);
+            tc::tma_load_2d(st + 2 * A_BYTES + C::B_BYTES, &tmB, full + stage, ks * BK, kn * P.q + nt * BN);
+          }
+          if (++stage == C::NSTAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ---------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc(BM, BN, 1);
+      int stage = 0; uint32_t phase = 0;
+      int buf = 0; uint32_t bphase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
+        if (!tc::mbar_wait(tempty + buf, bphase ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) break;
+        tc::tc_fence_after();
+        const uint32_t acc = tmem_base + buf * C::ACC_COLS;
+        for (int ks = 0; ks < P.ksteps; ++ks) {
+          if (!tc::mbar_wait(full + stage, phase, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t sa = tc::smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint64_t dA = tc::smem_desc_k_sw128(sa), dB = tc::smem_desc_k_sw128(sa + A_BYTES);
+          const uint64_t dA2 = tc::smem_desc_k_sw128(sa + A_BYTES + C::B_BYTES);
+          const uint64_t dB2 = tc::smem_desc_k_sw128(sa + 2 * A_BYTES + C::B_BYTES);
+#pragma unroll
+          for (int kk = 0; kk < BK / 16; ++kk) {
+            const uint32_t accum = (ks | kk) ? 1u : 0u;
+            // 16 bf16 along K = 32 bytes = 2 units of the descriptor's 16-byte address field
+            tc::mma_ss(acc, dA + 2 * kk, dB + 2 * kk, idesc, accum);
+            if (GLU) tc::mma_ss(acc + BN, dA2 + 2 * kk, dB2 + 2 * kk, idesc, accum);
+          }
+          tc::mma_commit(empty + stage);        // stage reusable once these MMAs have read it
+          if (++stage == C::NSTAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc::mma_commit(tfull + buf);            // accumulator complete
+        if ((buf ^= 1) == 0) bphase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -----------------------------------
+    const int quarter = warp & 3;               // TMEM lanes this warp may touch: 32*quarter ..
+    int buf = 0; uint32_t bphase = 0;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
+    for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
+      const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
+      if (!tc::mbar_wait(tfull + buf, bphase, abort_flag, tc::ST_TIMEOUT_EPI)) break;
+      tc::tc_fence_after();
+      const int row = mt * BM + quarter * 32 + lane;
+      const int col0 = kb * P.q + nt * BN;
+      const uint32_t tacc = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      __nv_bfloat16* orow = out + (long long)row * P.ldo + col0;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t a[32], b[32];
+        tc::tmem_ld32(tacc + c0, a);
+        if (GLU) tc::tmem_ld32(tacc + BN + c0, b);
+        tc::tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float v0, v1;
+          if (GLU) {
+            const float g0 = bf16r(__uint_as_float(a[j])), g1 = bf16r(__uint_as_float(a[j + 1]));
+            const float n0 = bf16r(__uint_as_float(b[j])), n1 = bf16r(__uint_as_float(b[j + 1]));
+            v0 = bf16r(gelu_erf(g0)) * n0;
+            v1 = bf16r(gelu_erf(g1)) * n1;
+          } else {
+            v0 = bf16r(__uint_as_float(a[j]));
+            v1 = bf16r(__uint_as_float(a[j + 1]));
+            if (P.bias) {
+              v0 += bf16r(__ldg(P.bias + col0 + c0 + j));
+              v1 += bf16r(__ldg(P.bias + col0 + c0 + j + 1));
+            }
+          }
+          packed[j >> 1] = pack_bf16(v0, v1);
+        }
+        if (row < P.M) {
+          uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+        }
+      }
+      tc::tc_fence_before();
+      tc::mbar_arrive(tempty + buf);
+      if ((buf ^= 1) == 0) bphase ^= 1;
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // give loads that were issued before the abort a bounded time to land
+    for (int s = 0; s < C::NSTAGES; ++s)
+      for (uint32_t i = 0; i < 4096 && !tc::mbar_try_wait(full + s, 0) && !tc::mbar_try_wait(full + s, 1); ++i) {}
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, C::TCOLS);
+  }
+}
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev);
+  return cached[dev] > 0 ? cached[dev] : 148;
+}
+
+template <int BN, bool GLU>
+static int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const Params& P, cudaStream_t st) {
+  using C = Cfg<BN, GLU>;
+  auto kern = gemm_tc_kernel<BN, GLU>;
+  M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+  int grid = P.total_tiles < sm_count() ? P.total_tiles : sm_count();
+  kern<<<grid, THREADS, C::SMEM, st>>>(tmA, tmB, P);
+  M2_LAUNCH_CHECK("gemm_tc_kernel");
+  return M2_OK;
+}
+
+static int pick_bn(int q) {
+  const int cand[] = {256, 192, 128, 64, 32};
+  for (int c : cand) if (q % c == 0) return c;
+  return 0;
+}
+
+}  // namespace gemm
+
+bool blockdiag_tc_supported(const m2_blockdiag_args* a) {
+  return a->dtype == M2_BF16 && a->p % 64 == 0 && gemm::pick_bn(a->q) != 0 &&
+         a->in_features == a->nblocks * a->p && a->out_features == a->nblocks * a->q &&
+         a->ldx % 8 == 0 && a->ldo % 8 == 0 && m2_aligned(a->x, 16) && m2_aligned(a->w, 16) &&
+         m2_aligned(a->out, 16) && a->m >= 1;
+}
+
+bool glu_tc_supported(const m2_glu_args* a) {
+  const int p = a->d_model / a->nblocks, q = 2 * a->inter / a->nblocks;
+  return a->dtype == M2_BF16 && p % 64 == 0 && q % 128 == 0 && a->ldx % 8 == 0 && a->ldh % 8 == 0 &&
+         m2_aligned(a->x, 16) && m2_aligned(a->wg, 16) && m2_aligned(a->h, 16) && a->m >= 1;
+}
+
+int blockdiag_tc_launch(const m2_blockdiag_args* a, cudaStream_t st) {
+  using namespace gemm;
+  const int bn = pick_bn(a->q);
+  CUtensorMap tmA, tmB;
+  int rc = m2_make_tmap_bf16_2d(&tmA, a->x, a->m, a->in_features, a->ldx, BM);
+  if (rc) return rc;
+  rc = m2_make_tmap_bf16_2d(&tmB, a->w, (uint64_t)a->nblocks * a->q, a->p, a->p, bn);
+  if (rc) return rc;
+  Params P;
+  P.M = a->m; P.p = a->p; P.q = a->q; P.nb_out = a->nblocks; P.pair_off = 0;
+  P.ntn = a->q / bn; P.ntm = (a->m + BM - 1) / BM; P.ksteps = a->p / BK;
+  P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->out_features;
+  P.out = a->out; P.ldo = a->ldo; P.bias = a->bias;
+  switch (bn) {
+    case 256: return launch<256, false>(tmA, tmB, P, st);
+    case 192: return launch<192, false>(tmA, tmB, P, st);
+    case 128: return launch<128, false>(tmA, tmB, P, st);
+    case 64: return launch<64, false>(tmA, tmB, P, st);
+    default: return launch<32, false>(tmA, tmB, P, st);
+  }
+}
+
+int glu_tc_launch(const m2_glu_args* a, cudaStream_t st) {
+  using namespace gemm;
+  const int p = a->d_model / a->nblocks, q = 2 * a->inter / a->nblocks;
+  CUtensorMap tmA, tmB;
+  int rc = m2_make_tmap_bf16_2d(&tmA, a->x, a->m, a->d_model, a->ldx, BM);
+  if (rc) return rc;
+  rc = m2_make_tmap_bf16_2d(&tmB, a->wg, (uint64_t)a->nblocks * q, p, p, 128);
+  if (rc) return rc;
+  Params P;
+  P.M = a->m; P.p = p; P.q = q; P.nb_out = a->nblocks / 2; P.pair_off = a->nblocks / 2;
+  P.ntn = q / 128; P.ntm = (a->m + BM - 1) / BM; P.ksteps = p / BK;
+  P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->inter;
+  P.out = a->h; P.ldo = a->ldh; P.bias = nullptr;
+  return launch<128, true>(tmA, tmB, P, st);
+}
+
+}  // namespace m2

@@ -293,3 +293,27 @@ def test_errors_are_loud():
         m(torch.zeros((1, 2 * cfg["L"], cfg["D"]), device=DEV))  # longer than l_max
     with torch.enable_grad(), pytest.raises(RuntimeError):
         m(torch.zeros((1, cfg["L"], cfg["D"]), device=DEV))      # forward-only
+
+
+# ---- tensor-core GEMM shapes: row counts around the 128-row tile, both model sizes -----
+@pytest.mark.parametrize("M", [1, 100, 128, 129, 1000])
+@pytest.mark.parametrize("D,I", [(768, 3072), (1536, 6144)])
+def test_glu_mlp_tile_edges_bf16(M, D, I):
+    cfg = dict(kind="glu", seed=50 + M, B=1, L=M, D=D, I=I, nb=4)
+    m, sd = build_glu(cfg, DEV)
+    x = torch.from_numpy(C.randn(cfg["seed"], "x", (1, M, D))).to(DEV).bfloat16()
+    sdt = to_torch(sd, DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = m(x)
+        ref = T.glu_mlp_forward(sdt, x)
+        # the two halves separately: gated activation, then wo + bias
+        h = ops.blockdiag_glu_fwd(x[0], m.gated_layers._weight_as(torch.bfloat16), I)
+        g = T.blockdiag_linear(x[0], sdt["gated_layers.weight"], None)
+        h_ref = torch.nn.functional.gelu(g[..., :I]) * g[..., I:]
+        o = m.wo(h_ref)
+        o_ref = T.blockdiag_linear(h_ref, sdt["wo.weight"], sdt["wo.bias"], out_features=D)
+        gl = m.gated_layers(x[0])
+    assert O.parity_error(npy(h), npy(h_ref)) < TOL_BF16
+    assert O.parity_error(npy(o), npy(o_ref)) < TOL_BF16
+    assert O.parity_error(npy(gl), npy(g)) < TOL_BF16
+    assert O.parity_error(npy(y), npy(ref)) < TOL_BF16
