@@ -86,11 +86,13 @@ int m2_hyena_filter(const m2_filter_args* args, void* stream);
 /* ---------------------------------------------------------------------------------------
  * Filter spectrum in the layout the long-convolution kernel consumes.
  * Replaces `k_f = torch.fft.rfft(k, n=2L) / (2L)`, bert/src/mm/hyena_utils.py:23-24.
- * m2_longconv_kind() names the kernel family used for (seq_len, act_dtype);
+ * m2_longconv_kind() names the kernel family used for (seq_len, act_dtype, d_model): 0 = float32
+ * arithmetic on CUDA cores (any shape), 1 = tcgen05 tensor cores (bf16, 64 < seq_len <= 128,
+ * d_model a multiple of 128, channel-contiguous tensors);
  * m2_filter_spectrum_floats() is the number of float32 the spectrum of one filter takes.
  * k (device, float32): (d_model, m2_filter_row_len(seq_len)) as written by m2_hyena_filter.
  * ------------------------------------------------------------------------------------- */
-int    m2_longconv_kind(int seq_len, m2_dtype act_dtype);
+int    m2_longconv_kind(int seq_len, m2_dtype act_dtype, int d_model);
 size_t m2_filter_spectrum_floats(int kind, int d_model, int seq_len);
 int    m2_filter_spectrum(int kind, int d_model, int seq_len, const float* k, float* spec_out,
                           void* stream);

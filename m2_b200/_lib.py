@@ -76,7 +76,7 @@ SYMBOLS = {
     "m2_device_status": (C.c_int, [C.POINTER(C.c_int)]),
     "m2_filter_row_len": (C.c_int, [C.c_int]),
     "m2_hyena_filter": (C.c_int, [C.POINTER(FilterArgs), C.c_void_p]),
-    "m2_longconv_kind": (C.c_int, [C.c_int, C.c_int]),
+    "m2_longconv_kind": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "m2_filter_spectrum_floats": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "m2_filter_spectrum": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "m2_longconv_fwd": (C.c_int, [C.POINTER(LongconvArgs), C.c_void_p]),

@@ -5,14 +5,14 @@
 namespace m2 {
 int longconv_simt_launch(const m2_longconv_args* a, cudaStream_t st);
 int spectrum_kind0_launch(int D, int L, const float* k, float* spec, cudaStream_t st);
-int longconv_tc_supported(int seq_len, m2_dtype act_dtype);
+int longconv_tc_supported(int seq_len, m2_dtype act_dtype, int d_model);
 size_t spectrum_kind1_floats(int D, int L);
 int spectrum_kind1_launch(int D, int L, const float* k, float* spec, cudaStream_t st);
 int longconv_tc_launch(const m2_longconv_args* a, cudaStream_t st);
 }  // namespace m2
 
-extern "C" int m2_longconv_kind(int seq_len, m2_dtype act_dtype) {
-  return m2::longconv_tc_supported(seq_len, act_dtype) ? 1 : 0;
+extern "C" int m2_longconv_kind(int seq_len, m2_dtype act_dtype, int d_model) {
+  return m2::longconv_tc_supported(seq_len, act_dtype, d_model) ? 1 : 0;
 }
 
 extern "C" size_t m2_filter_spectrum_floats(int kind, int d_model, int seq_len) {

@@ -122,8 +122,9 @@ def hyena_filter(z, t, weights, biases, weights_rev, biases_rev, freq, deltas, s
     return k
 
 
-def longconv_kind(seq_len: int, act_dtype: torch.dtype) -> int:
-    return _lib.lib().m2_longconv_kind(int(seq_len), M2_BF16 if act_dtype == torch.bfloat16 else M2_F32)
+def longconv_kind(seq_len: int, act_dtype: torch.dtype, d_model: int) -> int:
+    return _lib.lib().m2_longconv_kind(int(seq_len), M2_BF16 if act_dtype == torch.bfloat16 else M2_F32,
+                                       int(d_model))
 
 
 def filter_spectrum(k: torch.Tensor, seq_len: int, kind: int) -> torch.Tensor:

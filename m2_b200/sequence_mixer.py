@@ -82,7 +82,7 @@ class MonarchMixerSequenceMixing(nn.Module):
             u = u.unsqueeze(0)
         u_orig = u
         xin = self.in_linear(u)                        # bf16 under autocast, float32 otherwise
-        kind = ops.longconv_kind(L, xin.dtype)
+        kind = ops.longconv_kind(L, xin.dtype, self.d_model)
         filters = [self.filter_fn] + ([self.filter_fn2] if self.residual_long_conv else [])
         specs = [f.spectrum(L, bf16, kind) for f in filters]
         biases = [f.conv_bias() for f in filters]

@@ -317,3 +317,30 @@ def test_glu_mlp_tile_edges_bf16(M, D, I):
     assert O.parity_error(npy(o), npy(o_ref)) < TOL_BF16
     assert O.parity_error(npy(gl), npy(g)) < TOL_BF16
     assert O.parity_error(npy(y), npy(ref)) < TOL_BF16
+
+
+# ---- tensor-core long convolution (lengths 65..128) against the CUDA-core family -------
+@pytest.mark.parametrize("L", [65, 100, 127, 128])
+@pytest.mark.parametrize("residual,u_bf16", [(True, False), (True, True), (False, False)])
+def test_longconv_tensor_core_family(L, residual, u_bf16):
+    D, B = 256, 3
+    cfg = dict(C.CASES["mixer_small"], L=L, l_max=128, D=D, B=B, order=32, residual=residual, seed=61)
+    m, sd = build_mixer(cfg, DEV)
+    g = torch.Generator().manual_seed(L)
+    xin = torch.randn((B, L, 3 * D), generator=g).to(DEV).bfloat16()
+    u = torch.randn((B, L, D), generator=g).to(DEV)
+    if u_bf16:
+        u = u.bfloat16()
+    assert ops.longconv_kind(L, torch.bfloat16, D) == 1
+    filters = [m.filter_fn] + ([m.filter_fn2] if residual else [])
+    outs = []
+    for kind in (0, 1):
+        specs = [f.spectrum(L, True, kind) for f in filters]
+        outs.append(ops.longconv_fwd(xin, u if residual else None, m.short_filter.weight,
+                                     m.short_filter.bias, specs, [f.conv_bias() for f in filters],
+                                     kind=kind, bf16_rounding=True))
+    ref = O.mixer_core(npy(xin), npy(u), sd, bidirectional=True, residual_long_conv=residual,
+                       mode="bf16", u_is_bf16=u_bf16)
+    assert O.parity_error(npy(outs[0]), ref) < TOL_BF16
+    assert O.parity_error(npy(outs[1]), ref) < TOL_BF16
+    assert O.parity_error(npy(outs[1]), npy(outs[0])) < TOL_BF16
