@@ -114,6 +114,7 @@ spectrum_kind1_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
 struct Params {
   int B, L, D, nf, units, ctiles;
   uint32_t lbo, sbo;
+  int prefetch_ok;   // rows are 16-byte aligned, so bulk L2 prefetches are legal
   const __nv_bfloat16* xin; long long xsb, xst;
   const void* u; long long usb, ust;
   __nv_bfloat16* out; long long osb, ost;
@@ -205,6 +206,26 @@ longconv_tc128_kernel(const Params P) {
 
   if (warp == 8) {
     // ============================ control: MMA issue ============================
+    if (lane != 0) {
+      // lanes 1..31 pull the next unit's input rows into L2 while this unit is computed
+      for (int unit = blockIdx.x; unit < P.units; unit += gridDim.x) {
+        const int nxt = unit + gridDim.x;
+        if (nxt >= P.units || *abort_flag || !P.prefetch_ok) break;
+        const int ct = nxt % P.ctiles, b = nxt / P.ctiles;
+        const __nv_bfloat16* xb = P.xin + (long long)b * P.xsb + ct * CT;
+        const char* ub = reinterpret_cast<const char*>(P.u) + ((long long)b * P.usb + ct * CT) * (long long)sizeof(TU);
+        for (int i = lane - 1; i < P.L * 4; i += 31) {
+          const int t = i >> 2, which = i & 3;
+          if (which < 3) {
+            const void* ptr = xb + (long long)t * P.xst + which * P.D;
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(CT * 2) : "memory");
+          } else if (P.nf == 2) {
+            const void* ptr = ub + (long long)t * P.ust * (long long)sizeof(TU);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"((int)(CT * sizeof(TU))) : "memory");
+          }
+        }
+      }
+    }
     if (lane == 0) {
       constexpr uint32_t id32 = tc::make_idesc(128, 32, 0), id16 = tc::make_idesc(128, 16, 0);
       uint32_t ph = 0;
@@ -359,13 +380,18 @@ longconv_tc128_kernel(const Params P) {
         for (int g = 0; g < 2; ++g) {
           uint32_t pk[8][4];                                  // [ri*4+kq][n2 pair]
 #pragma unroll
-          for (int np = 0; np < 4; ++np) {
-            uint32_t e[8], o[8];
+          for (int np = 0; np < 4; np += 2) {
+            uint32_t e[8], o[8], e2[8], o2[8];
             tmem_ld8(tlane + 32 * (2 * np) + 16 * half + 8 * g, e);
             tmem_ld8(tlane + 32 * (2 * np + 1) + 16 * half + 8 * g, o);
+            tmem_ld8(tlane + 32 * (2 * np + 2) + 16 * half + 8 * g, e2);
+            tmem_ld8(tlane + 32 * (2 * np + 3) + 16 * half + 8 * g, o2);
             tc::tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 8; ++q) pk[q][np] = pack_h2(__uint_as_float(e[q]), __uint_as_float(o[q]));
+            for (int q = 0; q < 8; ++q) {
+              pk[q][np] = pack_h2(__uint_as_float(e[q]), __uint_as_float(o[q]));
+              pk[q][np + 1] = pack_h2(__uint_as_float(e2[q]), __uint_as_float(o2[q]));
+            }
           }
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
@@ -385,6 +411,9 @@ longconv_tc128_kernel(const Params P) {
         {
           const float2* G = reinterpret_cast<const float2*>(P.spec[f] + MAT_FLOATS) + (size_t)(c0 + r) * 128;
           const float bk = __ldg(P.bias[f] + c0 + r) * KAPPA;
+          float4 gn[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) gn[q] = __ldg(reinterpret_cast<const float4*>(G + (8 * half) * 8) + q);
 #pragma unroll 1
           for (int kl = 0; kl < 8; ++kl) {
             const int k1 = 8 * half + kl;
@@ -392,7 +421,11 @@ longconv_tc128_kernel(const Params P) {
             tc::tmem_ld16(tlane + 16 * k1, z);
             float4 gq[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) gq[q] = __ldg(reinterpret_cast<const float4*>(G + k1 * 8) + q);
+            for (int q = 0; q < 4; ++q) gq[q] = gn[q];
+            if (kl < 7) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) gn[q] = __ldg(reinterpret_cast<const float4*>(G + (k1 + 1) * 8) + q);
+            }
             tc::tmem_ld_wait();
             float yr[8], yi[8];
 #pragma unroll
@@ -421,13 +454,18 @@ longconv_tc128_kernel(const Params P) {
         for (int ri = 0; ri < 2; ++ri) {
           uint32_t pk[8][4];                                  // [n2][k1 pair]
 #pragma unroll
-          for (int kp = 0; kp < 4; ++kp) {
-            uint32_t e[8], o[8];
+          for (int kp = 0; kp < 4; kp += 2) {
+            uint32_t e[8], o[8], e2[8], o2[8];
             tmem_ld8(tlane + 16 * (8 * half + 2 * kp) + 8 * ri, e);
             tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 1) + 8 * ri, o);
+            tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 2) + 8 * ri, e2);
+            tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 3) + 8 * ri, o2);
             tc::tmem_ld_wait();
 #pragma unroll
-            for (int n2 = 0; n2 < 8; ++n2) pk[n2][kp] = pack_h2(__uint_as_float(e[n2]), __uint_as_float(o[n2]));
+            for (int n2 = 0; n2 < 8; ++n2) {
+              pk[n2][kp] = pack_h2(__uint_as_float(e[n2]), __uint_as_float(o[n2]));
+              pk[n2][kp + 1] = pack_h2(__uint_as_float(e2[n2]), __uint_as_float(o2[n2]));
+            }
           }
 #pragma unroll
           for (int n2 = 0; n2 < 8; ++n2)
@@ -444,13 +482,17 @@ longconv_tc128_kernel(const Params P) {
         {
           float* Y = reinterpret_cast<float*>(Hb);
 #pragma unroll 1
-          for (int nn = 0; nn < 4; ++nn) {
+          for (int nn = 0; nn < 4; nn += 2) {
             const int n2 = 4 * half + nn;
-            uint32_t v[16];
+            uint32_t v[16], w[16];
             tc::tmem_ld16(tlane + 16 * n2, v);
+            tc::tmem_ld16(tlane + 16 * (n2 + 1), w);
             tc::tmem_ld_wait();
 #pragma unroll
-            for (int n1 = 0; n1 < 16; ++n1) Y[(8 * n1 + n2) * CT + r] = __uint_as_float(v[n1]);
+            for (int n1 = 0; n1 < 16; ++n1) {
+              Y[(8 * n1 + n2) * CT + r] = __uint_as_float(v[n1]);
+              Y[(8 * n1 + n2 + 1) * CT + r] = __uint_as_float(w[n1]);
+            }
           }
         }
         tc::tc_fence_before();
@@ -552,6 +594,8 @@ int longconv_tc_launch(const m2_longconv_args* a, cudaStream_t st) {
   P.out = (__nv_bfloat16*)a->out; P.osb = a->out_sb; P.ost = a->out_st;
   P.sw = a->short_w; P.sb = a->short_b;
   for (int f = 0; f < 2; ++f) { P.spec[f] = a->spec[f]; P.bias[f] = a->bias[f]; }
+  P.prefetch_ok = m2_aligned(a->xin, 16) && a->xin_st % 8 == 0 && a->xin_sb % 8 == 0 &&
+                  (a->n_filters == 1 || (m2_aligned(a->u, 16) && a->u_st % 8 == 0 && a->u_sb % 8 == 0));
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
