@@ -8,7 +8,7 @@
 //
 // One persistent CTA per SM walks output tiles of 128 rows x BN columns.  Warp 0 issues TMA
 // loads into a ring of shared-memory stages, warp 1 issues the MMAs (one thread) into one of
-// two TMEM accumulator buffers, warps 2-9 drain the other buffer (tcgen05.ld), apply the
+// two TMEM accumulator buffers, warps 2-17 drain the other buffer (tcgen05.ld), apply the
 // epilogue with the reference's bf16 rounding points and store.  Every mbarrier wait is
 // bounded; a wait that runs out sets the device status word and the CTA winds down.
 //
@@ -52,18 +52,10 @@ namespace gemm {
 
 constexpr int BM = 128;
 constexpr int BK = 64;                 // one 128-byte swizzle row of bf16
-constexpr int EPI_WARPS = 8;               // two warps per TMEM lane quarter, each half the columns
+constexpr int EPI_WARPS = 16;              // four warps per TMEM lane quarter, each a quarter of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
-constexpr int SMEM_BUDGET = 192 * 1024;
-
-// GELU of a bf16 value, rounded to bf16, as a table over the bf16 bit patterns with
-// 2^-10 <= |x| < 16 (outside that range the slow path evaluates the formula).  Entries are
-// produced at kernel start with the same float32 expression the epilogue would evaluate
-// (0.5 x (1 + erff(x / sqrt 2))), so results are bit-identical to evaluating it per element.
-constexpr int LUT_EXP0 = 117 << 7;           // bit pattern of 2^-10
-constexpr int LUT_HALF = 14 * 128;           // 14 binades x 128 mantissas, per sign
-constexpr int LUT_BYTES = 2 * LUT_HALF * 2;
+constexpr int SMEM_BUDGET = 200 * 1024;
 
 struct Params {
   int M, p, q, nb_out, pair_off, ntn, ntm, ksteps, total_tiles, out_cols;
@@ -80,17 +72,10 @@ struct Cfg {
   static constexpr int ACC_COLS = NACC * BN;         // TMEM columns of one accumulator buffer
   static constexpr int TCOLS = (2 * ACC_COLS <= 32) ? 32 : (2 * ACC_COLS <= 64) ? 64 : (2 * ACC_COLS <= 128) ? 128
                                : (2 * ACC_COLS <= 256) ? 256 : 512;
-  static constexpr int SMEM = NSTAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ +
-                              (GLU ? LUT_BYTES : 0);
+  static constexpr int SMEM = NSTAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
   static_assert(2 * ACC_COLS <= 512, "accumulators exceed tensor memory");
   static_assert(NSTAGES >= 2, "need at least two stages");
 };
-
-__device__ __forceinline__ float gelu_bf16_lut(uint32_t bits16, const uint16_t* lut) {
-  const uint32_t idx = (bits16 & 0x7FFFu) - LUT_EXP0;
-  if (idx < (uint32_t)LUT_HALF) return __uint_as_float((uint32_t)lut[(bits16 >> 15) * LUT_HALF + idx] << 16);
-  return bf16r(gelu_erf(__uint_as_float(bits16 << 16)));
-}
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -111,17 +96,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint16_t* lut = reinterpret_cast<uint16_t*>(smem + C::NSTAGES * C::STAGE_BYTES + 256);
-
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  if (GLU) {
-    for (int i = threadIdx.x; i < 2 * LUT_HALF; i += THREADS) {
-      const uint32_t bits = (uint32_t)((i / LUT_HALF) << 15) | (uint32_t)(LUT_EXP0 + i % LUT_HALF);
-      const float v = gelu_erf(__uint_as_float(bits << 16));
-      lut[i] = (uint16_t)(__float_as_uint(bf16r(v)) >> 16);
-    }
-  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::NSTAGES; ++s) { tc::mbar_init(full + s, 1); tc::mbar_init(empty + s, 1); }
     for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull + b, 1); tc::mbar_init(tempty + b, 32 * EPI_WARPS); }
@@ -197,8 +173,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else {
     // ------------------------------- epilogue -----------------------------------
     const int quarter = warp & 3;               // TMEM lanes this warp may touch: 32*quarter ..
-    const int chalf = (warp - 2) >> 2;          // which half of the tile's columns
-    constexpr int CW = BN / 2;                  // columns per warp
+    const int chalf = (warp - 2) >> 2;          // which slice of the tile's columns
+    constexpr int CW = BN / (EPI_WARPS / 4);    // columns per warp
+    static_assert(CW % 16 == 0, "column slice must be a multiple of 16");
     int buf = 0; uint32_t bphase = 0;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
     for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
@@ -210,20 +187,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t tacc = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* orow = out + (long long)row * P.ldo + col0;
 #pragma unroll 1
-      for (int c0 = chalf * CW; c0 < (chalf + 1) * CW; c0 += 32) {
-        uint32_t a[32], b[32];
-        tc::tmem_ld32(tacc + c0, a);
-        if (GLU) tc::tmem_ld32(tacc + BN + c0, b);
+      for (int c0 = chalf * CW; c0 < (chalf + 1) * CW; c0 += 16) {
+        uint32_t a[16], b[16];
+        tc::tmem_ld16(tacc + c0, a);
+        if (GLU) tc::tmem_ld16(tacc + BN + c0, b);
         tc::tmem_ld_wait();
-        uint32_t packed[16];
+        uint32_t packed[8];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
+        for (int j = 0; j < 16; j += 2) {
           float v0, v1;
           if (GLU) {
             const uint32_t g = pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1]));
             const uint32_t n = pack_bf16(__uint_as_float(b[j]), __uint_as_float(b[j + 1]));
-            v0 = gelu_bf16_lut(g & 0xFFFFu, lut) * __uint_as_float(n << 16);
-            v1 = gelu_bf16_lut(g >> 16, lut) * __uint_as_float(n & 0xFFFF0000u);
+            v0 = bf16r(gelu_erf(__uint_as_float(g << 16))) * __uint_as_float(n << 16);
+            v1 = bf16r(gelu_erf(__uint_as_float(g & 0xFFFF0000u))) * __uint_as_float(n & 0xFFFF0000u);
           } else {
             v0 = bf16r(__uint_as_float(a[j]));
             v1 = bf16r(__uint_as_float(a[j + 1]));
@@ -237,7 +214,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (row < P.M) {
           uint4* dst = reinterpret_cast<uint4*>(orow + c0);
 #pragma unroll
-          for (int v = 0; v < 4; ++v)
+          for (int v = 0; v < 2; ++v)
             dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
         }
       }

@@ -25,15 +25,24 @@
 // Computation replaced: bert/src/mm/monarch_mixer_sequence_mixer.py:109-149 and
 // bert/src/mm/hyena_utils.py:16-42, :219-248 of the reference.
 #include "tc_common.cuh"
-#include <stdlib.h>
 
 namespace m2 {
 namespace lc {
 
+// Phase timing for kernel tuning: built only with -DM2_LC_TIMING; worker thread 0 of every
+// CTA adds the clock cycles it spent in each phase to a device array.
+#ifdef M2_LC_TIMING
+__device__ unsigned long long g_phase_cycles[16];
+#define LC_T0() long long t_prev_ = clock64()
+#define LC_MARK(i) do { if (tid == 0) { long long n_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(n_ - t_prev_)); t_prev_ = n_; } } while (0)
+#else
+#define LC_T0() do {} while (0)
+#define LC_MARK(i) do {} while (0)
+#endif
+
 constexpr int NFFT = 256;
 constexpr int CT = 128;                    // channels per unit
-constexpr int WORKERS = 256;
-constexpr int THREADS = WORKERS + 32;
+constexpr int THREADS = 256;
 constexpr int TILE = 4096;                 // one [128 x 16] fp16 A-operand tile
 constexpr int H_BYTES = 16 * TILE;         // 64 KB: operand tiles, later the float32 y tile
 constexpr int F1_OFF = 0, F2_OFF = 1024, I2_OFF = F2_OFF + 8192, I1_OFF = I2_OFF + 8192;
@@ -42,6 +51,7 @@ constexpr int MAT_FLOATS = MAT_BYTES / 4;
 constexpr float S1 = 0.25f, S2 = 0.5f, S3 = 0.5f, S4 = 0.25f;   // per-stage scalings (exact powers of two)
 constexpr float KAPPA = (2.0f / NFFT) / (S1 * S2 * S3 * S4);     // folded into the filter table
 // core-matrix strides of every operand tile: LBO between the two K halves, SBO between 8-row groups
+constexpr uint32_t LBO = 128, SBO = 256;
 
 // byte offset of element (row, k) in a K-major un-swizzled tile with 16 K columns
 __host__ __device__ constexpr int tile_off(int row, int k) {
@@ -50,7 +60,7 @@ __host__ __device__ constexpr int tile_off(int row, int k) {
 
 // ---------------------------------------------------------------------------------------
 // Spectrum table (kind 1): [MAT_FLOATS floats: the fp16 matrices] then per channel
-// G[k1][k2] as float2, k1 < 16, k2 < 8, already multiplied by KAPPA.
+// G[k1][k2] as half2 (re, im), k1 < 16, k2 < 8, already multiplied by KAPPA.
 // ---------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 spectrum_kind1_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D, int L) {
@@ -106,14 +116,13 @@ spectrum_kind1_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
     re += g * cs;
     im -= g * sn;
   }
-  float2* G = reinterpret_cast<float2*>(spec + MAT_FLOATS) + (size_t)c * 128;
-  G[k1 * 8 + k2] = make_float2((float)(re * KAPPA), (float)(im * KAPPA));
+  __half2* G = reinterpret_cast<__half2*>(spec + MAT_FLOATS) + (size_t)c * 128;
+  G[k1 * 8 + k2] = __floats2half2_rn((float)(re * KAPPA), (float)(im * KAPPA));
 }
 
 // ---------------------------------------------------------------------------------------
 struct Params {
   int B, L, D, nf, units, ctiles;
-  uint32_t lbo, sbo;
   int prefetch_ok;   // rows are 16-byte aligned, so bulk L2 prefetches are legal
   const __nv_bfloat16* xin; long long xsb, xst;
   const void* u; long long usb, ust;
@@ -165,6 +174,31 @@ __device__ __forceinline__ uint32_t conv_step(const Taps& T, float (&win)[2][2],
   return pack_bf2(c0, c1);
 }
 
+// MMAs of one stage, issued by a single thread once every operand tile is in shared memory.
+__device__ __forceinline__ void issue_stage(int stage, uint32_t tmem, uint32_t Hs, uint32_t Ms) {
+  constexpr uint32_t id32 = tc::make_idesc(128, 32, 0), id16 = tc::make_idesc(128, 16, 0);
+  // every tile lies within the first 256 KB of shared memory, so adding a tile offset (in
+  // 16-byte units) to the descriptor never carries out of its 14-bit address field
+  const uint64_t dH = tc::smem_desc_k_nosw(Hs, LBO, SBO);
+  const uint64_t dM = tc::smem_desc_k_nosw(Ms, LBO, SBO);
+  if (stage == 0) {
+#pragma unroll
+    for (int n2 = 0; n2 < 8; ++n2)
+      tc::mma_ss(tmem + 32 * n2, dH + n2 * (TILE >> 4), dM + (F1_OFF >> 4), id32, 0);
+  } else if (stage == 1 || stage == 2) {
+    const uint64_t dB = dM + ((stage == 1 ? F2_OFF : I2_OFF) >> 4);
+#pragma unroll
+    for (int k1 = 0; k1 < 16; ++k1)
+      tc::mma_ss(tmem + 16 * k1, dH + k1 * (TILE >> 4), dB + k1 * (512 >> 4), id16, 0);
+  } else {
+#pragma unroll
+    for (int n2 = 0; n2 < 8; ++n2) {
+      tc::mma_ss(tmem + 16 * n2, dH + (2 * n2) * (TILE >> 4), dM + (I1_OFF >> 4), id16, 0);
+      tc::mma_ss(tmem + 16 * n2, dH + (2 * n2 + 1) * (TILE >> 4), dM + ((I1_OFF + 512) >> 4), id16, 1);
+    }
+  }
+}
+
 template <typename TU>
 __global__ void __launch_bounds__(THREADS, 2)
 longconv_tc128_kernel(const Params P) {
@@ -172,28 +206,27 @@ longconv_tc128_kernel(const Params P) {
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
   unsigned char* Hb = smem;                            // operand tiles / y tile
   unsigned char* Mb = smem + H_BYTES;                  // DFT matrices
-  uint64_t* bar_ops = reinterpret_cast<uint64_t*>(Mb + MAT_BYTES);   // workers -> control (256)
-  uint64_t* bar_mma = bar_ops + 1;                                    // control -> workers (commit)
+  uint64_t* bar_ops = reinterpret_cast<uint64_t*>(Mb + MAT_BYTES);   // operand tiles written (256 arrivals)
+  uint64_t* bar_mma = bar_ops + 1;                                    // stage's MMAs complete (commit)
   uint64_t* bar_w = bar_ops + 2;                                      // workers <-> workers (256)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_ops + 3);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    tc::mbar_init(bar_ops, WORKERS);
+    tc::mbar_init(bar_ops, THREADS);
     tc::mbar_init(bar_mma, 1);
-    tc::mbar_init(bar_w, WORKERS);
+    tc::mbar_init(bar_w, THREADS);
     *abort_flag = 0;
     tc::mbar_fence_init();
   }
-  // constant matrices: global (spectrum header of filter 0) -> shared
-  {
+  {  // constant matrices: global (spectrum header of filter 0) -> shared
     const uint4* src = reinterpret_cast<const uint4*>(P.spec[0]);
     uint4* dst = reinterpret_cast<uint4*>(Mb);
     for (int i = tid; i < MAT_BYTES / 16; i += THREADS) dst[i] = __ldg(src + i);
     tc::fence_proxy_async_smem();
   }
-  if (warp == 8) {
+  if (warp == 0) {
     tc::tmem_alloc(tmem_slot, 256);
     tc::tmem_relinquish();
   }
@@ -202,354 +235,337 @@ longconv_tc128_kernel(const Params P) {
   tc::tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t Hs = tc::smem_u32(Hb), Ms = tc::smem_u32(Mb);
-  const uint32_t LBO = P.lbo, SBO = P.sbo;
 
-  if (warp == 8) {
-    // ============================ control: MMA issue ============================
-    if (lane != 0) {
-      // lanes 1..31 pull the next unit's input rows into L2 while this unit is computed
-      for (int unit = blockIdx.x; unit < P.units; unit += gridDim.x) {
-        const int nxt = unit + gridDim.x;
-        if (nxt >= P.units || *abort_flag || !P.prefetch_ok) break;
-        const int ct = nxt % P.ctiles, b = nxt / P.ctiles;
-        const __nv_bfloat16* xb = P.xin + (long long)b * P.xsb + ct * CT;
-        const char* ub = reinterpret_cast<const char*>(P.u) + ((long long)b * P.usb + ct * CT) * (long long)sizeof(TU);
-        for (int i = lane - 1; i < P.L * 4; i += 31) {
-          const int t = i >> 2, which = i & 3;
-          if (which < 3) {
-            const void* ptr = xb + (long long)t * P.xst + which * P.D;
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(CT * 2) : "memory");
-          } else if (P.nf == 2) {
-            const void* ptr = ub + (long long)t * P.ust * (long long)sizeof(TU);
-            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"((int)(CT * sizeof(TU))) : "memory");
-          }
+  const int quarter = warp & 3, half = warp >> 2;
+  const int r = quarter * 32 + lane;                         // TMEM lane = channel within the tile
+  const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16);
+  const uint32_t rowoff = (uint32_t)((r >> 3) * 256 + (r & 7) * 16);
+  const int pi = tid & 63, tq = tid >> 6;                    // channel pair, quarter of the time axis
+  const int t_begin = 32 * tq;
+  const uint32_t prow0 = (uint32_t)(((2 * pi) >> 3) * 256 + ((2 * pi) & 7) * 16);   // row 2pi; row 2pi+1 is +16
+  const uint32_t pkoff = (uint32_t)((tq >> 1) * 128 + (tq & 1) * 8);                 // n1 = 4 tq + i
+  uint32_t ph_ops = 0, ph_mma = 0, ph_w = 0;
+  bool ok = true;
+
+  // operand tiles are complete: thread 0 issues the stage's MMAs, everybody waits for them
+#define LC_STAGE(stage_)                                                                              \
+  tc::fence_proxy_async_smem();                                                                       \
+  tc::mbar_arrive(bar_ops);                                                                           \
+  if (tid == 0) {                                                                                     \
+    if (tc::mbar_wait(bar_ops, ph_ops, abort_flag, tc::ST_TIMEOUT_MMA)) {                             \
+      tc::tc_fence_after();                                                                           \
+      issue_stage(stage_, tmem, Hs, Ms);                                                    \
+      tc::mma_commit(bar_mma);                                                                        \
+    }                                                                                                 \
+    ph_ops ^= 1;                                                                                      \
+  }                                                                                                   \
+  if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_mma, ph_mma, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; } \
+  ph_mma ^= 1;                                                                                        \
+  tc::tc_fence_after();
+
+#define LC_WORKER_BARRIER()                                                                           \
+  tc::mbar_arrive(bar_w);                                                                             \
+  if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_w, ph_w, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; } \
+  ph_w ^= 1;
+
+  for (int unit = blockIdx.x; unit < P.units && ok; unit += gridDim.x) {
+    const int ct = unit % P.ctiles, b = unit / P.ctiles;
+    const int c0 = ct * CT;
+    const int ch = c0 + 2 * pi;
+    const __nv_bfloat16* xb = P.xin + (long long)b * P.xsb + ch;
+    __nv_bfloat16* ob = P.out + (long long)b * P.osb + ch;
+
+    // pull the next unit's input rows into L2 while this one is computed
+    if (P.prefetch_ok && unit + (int)gridDim.x < P.units) {
+      const int nxt = unit + gridDim.x;
+      const int nct = nxt % P.ctiles, nb = nxt / P.ctiles;
+      const __nv_bfloat16* nx = P.xin + (long long)nb * P.xsb + nct * CT;
+      const char* nu = reinterpret_cast<const char*>(P.u) + ((long long)nb * P.usb + nct * CT) * (long long)sizeof(TU);
+      for (int i = tid; i < P.L * 4; i += THREADS) {
+        const int t = i >> 2, which = i & 3;
+        if (which < 3) {
+          const void* ptr = nx + (long long)t * P.xst + which * P.D;
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"(CT * 2) : "memory");
+        } else if (P.nf == 2) {
+          const void* ptr = nu + (long long)t * P.ust * (long long)sizeof(TU);
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(ptr), "r"((int)(CT * sizeof(TU))) : "memory");
         }
       }
     }
-    if (lane == 0) {
-      constexpr uint32_t id32 = tc::make_idesc(128, 32, 0), id16 = tc::make_idesc(128, 16, 0);
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int unit = blockIdx.x; unit < P.units && ok; unit += gridDim.x) {
-        for (int f = 0; f < P.nf && ok; ++f) {
-#pragma unroll 1
-          for (int stage = 0; stage < 4; ++stage) {
-            if (!tc::mbar_wait(bar_ops, ph, abort_flag, tc::ST_TIMEOUT_MMA)) { ok = false; break; }
-            ph ^= 1;
-            tc::tc_fence_after();
-            if (stage == 0) {
-              const uint64_t dB = tc::smem_desc_k_nosw(Ms + F1_OFF, LBO, SBO);
-#pragma unroll
-              for (int n2 = 0; n2 < 8; ++n2)
-                tc::mma_ss(tmem + 32 * n2, tc::smem_desc_k_nosw(Hs + n2 * TILE, LBO, SBO), dB, id32, 0);
-            } else if (stage == 1 || stage == 2) {
-              const uint32_t mo = Ms + (stage == 1 ? F2_OFF : I2_OFF);
-#pragma unroll
-              for (int k1 = 0; k1 < 16; ++k1)
-                tc::mma_ss(tmem + 16 * k1, tc::smem_desc_k_nosw(Hs + k1 * TILE, LBO, SBO),
-                           tc::smem_desc_k_nosw(mo + k1 * 512, LBO, SBO), id16, 0);
-            } else {
-              const uint64_t dB0 = tc::smem_desc_k_nosw(Ms + I1_OFF, LBO, SBO);
-              const uint64_t dB1 = tc::smem_desc_k_nosw(Ms + I1_OFF + 512, LBO, SBO);
-#pragma unroll
-              for (int n2 = 0; n2 < 8; ++n2) {
-                tc::mma_ss(tmem + 16 * n2, tc::smem_desc_k_nosw(Hs + (2 * n2) * TILE, LBO, SBO), dB0, id16, 0);
-                tc::mma_ss(tmem + 16 * n2, tc::smem_desc_k_nosw(Hs + (2 * n2 + 1) * TILE, LBO, SBO), dB1, id16, 1);
-              }
-            }
-            tc::mma_commit(bar_mma);
-          }
-        }
-      }
-    }
-  } else {
-    // ============================ workers ============================
-    const int quarter = warp & 3, half = warp >> 2;
-    const int r = quarter * 32 + lane;                         // TMEM lane = channel within the tile
-    const uint32_t tlane = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t rowoff = (uint32_t)((r >> 3) * 256 + (r & 7) * 16);
-    const int pi = tid & 63, tq = tid >> 6;                    // channel pair, quarter of the time axis
-    const int t_begin = 32 * tq;
-    const uint32_t prow0 = (uint32_t)(((2 * pi) >> 3) * 256 + ((2 * pi) & 7) * 16);   // row 2pi; row 2pi+1 is +16
-    const uint32_t pkoff = (uint32_t)((tq >> 1) * 128 + (tq & 1) * 8);                 // n1 = 4 tq + i
-    uint32_t ph_mma = 0, ph_w = 0;
-    bool ok = true;
 
-    for (int unit = blockIdx.x; unit < P.units && ok; unit += gridDim.x) {
-      const int ct = unit % P.ctiles, b = unit / P.ctiles;
-      const int c0 = ct * CT;
-      const int ch = c0 + 2 * pi;
-      const __nv_bfloat16* xb = P.xin + (long long)b * P.xsb + ch;
-      __nv_bfloat16* ob = P.out + (long long)b * P.osb + ch;
-
-      for (int f = 0; f < P.nf && ok; ++f) {
-        // ---------------- operand tiles of stage F1: a[t] as fp16, tile n2 = t % 8, k = t / 8 ----------------
-        {
-          uint32_t hv[2][8][2];                              // [row][n2][two packed pairs over i]
-          if (f == 0) {
-            Taps Tx, Tv;
-            load_taps(Tx, P.sw, P.sb, ch);
-            load_taps(Tv, P.sw, P.sb, 2 * P.D + ch);
-            float wx[2][2], wv[2][2];
+    LC_T0();
+    for (int f = 0; f < P.nf && ok; ++f) {
+      // ---------------- operand tiles of stage F1: a[t] as fp16, tile n2 = t % 8, k = t / 8 ----------------
+      {
+        uint32_t hv[2][8][2];                              // [row][n2][two packed pairs over i]
+        if (f == 0) {
+          Taps Tx, Tv;
+          load_taps(Tx, P.sw, P.sb, ch);
+          load_taps(Tv, P.sw, P.sb, 2 * P.D + ch);
+          float wx[2][2], wv[2][2];
+          uint32_t lx[2][8], lv[2][8];                     // double-buffered loads: chunk i+1 in flight during chunk i
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              const int t = t_begin - 2 + hh;
-              uint32_t px = 0, pv = 0;
-              if (t >= 0) {
-                px = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
-                pv = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
-              }
-              wx[0][hh] = bf_lo(px); wx[1][hh] = bf_hi(px);
-              wv[0][hh] = bf_lo(pv); wv[1][hh] = bf_hi(pv);
+          for (int hh = 0; hh < 2; ++hh) {
+            const int t = t_begin - 2 + hh;
+            uint32_t px = 0, pv = 0;
+            if (t >= 0) {
+              px = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
+              pv = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t lx[8], lv[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int t = t_begin + 8 * i + j;
-                lx[j] = lv[j] = 0;
-                if (t < P.L) {
-                  lx[j] = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
-                  lv[j] = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
-                }
-              }
-              float a0[8], a1[8];
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const uint32_t cx = conv_step(Tx, wx, lx[j]);
-                const uint32_t cv = conv_step(Tv, wv, lv[j]);
-                const uint32_t pr = pack_bf2(bf_lo(cv) * bf_lo(cx), bf_hi(cv) * bf_hi(cx));
-                const bool live = (t_begin + 8 * i + j) < P.L;
-                a0[j] = live ? bf_lo(pr) : 0.f;
-                a1[j] = live ? bf_hi(pr) : 0.f;
-              }
-              // element i of the 4-wide group: pack (i even, i odd) pairs afterwards
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                if ((i & 1) == 0) {
-                  hv[0][j][i >> 1] = __float_as_uint(a0[j]);
-                  hv[1][j][i >> 1] = __float_as_uint(a1[j]);
-                } else {
-                  hv[0][j][i >> 1] = pack_h2(__uint_as_float(hv[0][j][i >> 1]), a0[j]);
-                  hv[1][j][i >> 1] = pack_h2(__uint_as_float(hv[1][j][i >> 1]), a1[j]);
-                }
-              }
-            }
-          } else {
-            const TU* up = reinterpret_cast<const TU*>(P.u) + (long long)b * P.usb + ch;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int t = t_begin + 8 * i + j;
-                float u0 = 0.f, u1 = 0.f;
-                if (t < P.L) {
-                  if (sizeof(TU) == 4) {
-                    const float2 v = __ldg(reinterpret_cast<const float2*>(up + (long long)t * P.ust));
-                    u0 = v.x; u1 = v.y;
-                  } else {
-                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(up + (long long)t * P.ust));
-                    u0 = bf_lo(v); u1 = bf_hi(v);
-                  }
-                }
-                if ((i & 1) == 0) {
-                  hv[0][j][i >> 1] = __float_as_uint(u0);
-                  hv[1][j][i >> 1] = __float_as_uint(u1);
-                } else {
-                  hv[0][j][i >> 1] = pack_h2(__uint_as_float(hv[0][j][i >> 1]), u0);
-                  hv[1][j][i >> 1] = pack_h2(__uint_as_float(hv[1][j][i >> 1]), u1);
-                }
-              }
-            }
+            wx[0][hh] = bf_lo(px); wx[1][hh] = bf_hi(px);
+            wv[0][hh] = bf_lo(pv); wv[1][hh] = bf_hi(pv);
           }
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            sts64(Hs + j * TILE + prow0 + pkoff, hv[0][j][0], hv[0][j][1]);
-            sts64(Hs + j * TILE + prow0 + 16 + pkoff, hv[1][j][0], hv[1][j][1]);
-          }
-        }
-        tc::fence_proxy_async_smem();
-        tc::mbar_arrive(bar_ops);
-
-        // ---------------- hop 1: F1 result -> operand tiles of F2 ----------------
-        if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_mma, ph_mma, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; }
-        ph_mma ^= 1;
-        tc::tc_fence_after();
-#pragma unroll 1
-        for (int g = 0; g < 2; ++g) {
-          uint32_t pk[8][4];                                  // [ri*4+kq][n2 pair]
-#pragma unroll
-          for (int np = 0; np < 4; np += 2) {
-            uint32_t e[8], o[8], e2[8], o2[8];
-            tmem_ld8(tlane + 32 * (2 * np) + 16 * half + 8 * g, e);
-            tmem_ld8(tlane + 32 * (2 * np + 1) + 16 * half + 8 * g, o);
-            tmem_ld8(tlane + 32 * (2 * np + 2) + 16 * half + 8 * g, e2);
-            tmem_ld8(tlane + 32 * (2 * np + 3) + 16 * half + 8 * g, o2);
-            tc::tmem_ld_wait();
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              pk[q][np] = pack_h2(__uint_as_float(e[q]), __uint_as_float(o[q]));
-              pk[q][np + 1] = pack_h2(__uint_as_float(e2[q]), __uint_as_float(o2[q]));
+            const int t = t_begin + j;
+            lx[0][j] = lv[0][j] = 0;
+            if (t < P.L) {
+              lx[0][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
+              lv[0][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
             }
           }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            if (i < 3) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int t = t_begin + 8 * (i + 1) + j;
+                lx[(i + 1) & 1][j] = lv[(i + 1) & 1][j] = 0;
+                if (t < P.L) {
+                  lx[(i + 1) & 1][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
+                  lv[(i + 1) & 1][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t cx = conv_step(Tx, wx, lx[i & 1][j]);
+              const uint32_t cv = conv_step(Tv, wv, lv[i & 1][j]);
+              const uint32_t pr = pack_bf2(bf_lo(cv) * bf_lo(cx), bf_hi(cv) * bf_hi(cx));
+              const bool live = (t_begin + 8 * i + j) < P.L;
+              const float a0 = live ? bf_lo(pr) : 0.f, a1 = live ? bf_hi(pr) : 0.f;
+              if ((i & 1) == 0) {
+                hv[0][j][i >> 1] = __float_as_uint(a0);
+                hv[1][j][i >> 1] = __float_as_uint(a1);
+              } else {
+                hv[0][j][i >> 1] = pack_h2(__uint_as_float(hv[0][j][i >> 1]), a0);
+                hv[1][j][i >> 1] = pack_h2(__uint_as_float(hv[1][j][i >> 1]), a1);
+              }
+            }
+          }
+        } else {
+          const TU* up = reinterpret_cast<const TU*>(P.u) + (long long)b * P.usb + ch;
+#pragma unroll
+          for (int ii = 0; ii < 4; ii += 2) {
+            float u0[16], u1[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = t_begin + 8 * ii + j;
+              u0[j] = u1[j] = 0.f;
+              if (t < P.L) {
+                if (sizeof(TU) == 4) {
+                  const float2 v = __ldg(reinterpret_cast<const float2*>(up + (long long)t * P.ust));
+                  u0[j] = v.x; u1[j] = v.y;
+                } else {
+                  const uint32_t v = __ldg(reinterpret_cast<const uint32_t*>(up + (long long)t * P.ust));
+                  u0[j] = bf_lo(v); u1[j] = bf_hi(v);
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {                  // elements i = ii (t = 8 ii + j) and i = ii + 1
+              hv[0][j][ii >> 1] = pack_h2(u0[j], u0[8 + j]);
+              hv[1][j][ii >> 1] = pack_h2(u1[j], u1[8 + j]);
+            }
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          sts64(Hs + j * TILE + prow0 + pkoff, hv[0][j][0], hv[0][j][1]);
+          sts64(Hs + j * TILE + prow0 + 16 + pkoff, hv[1][j][0], hv[1][j][1]);
+        }
+      }
+      LC_MARK(0);
+      LC_STAGE(0)
+      LC_MARK(1);
+
+      // ---------------- hop 1: F1 result -> operand tiles of F2 ----------------
+#pragma unroll 1
+      for (int g = 0; g < 2; ++g) {
+        uint32_t pk[8][4];                                  // [ri*4+kq][n2 pair]
+#pragma unroll
+        for (int np = 0; np < 4; np += 2) {
+          uint32_t e[8], o[8], e2[8], o2[8];
+          tmem_ld8(tlane + 32 * (2 * np) + 16 * half + 8 * g, e);
+          tmem_ld8(tlane + 32 * (2 * np + 1) + 16 * half + 8 * g, o);
+          tmem_ld8(tlane + 32 * (2 * np + 2) + 16 * half + 8 * g, e2);
+          tmem_ld8(tlane + 32 * (2 * np + 3) + 16 * half + 8 * g, o2);
+          tc::tmem_ld_wait();
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            const int ri = q >> 2, kq = q & 3;
-            const int k1 = 8 * half + 4 * g + kq;
-            sts128(Hs + k1 * TILE + rowoff + ri * 128, pk[q][0], pk[q][1], pk[q][2], pk[q][3]);
+            pk[q][np] = pack_h2(__uint_as_float(e[q]), __uint_as_float(o[q]));
+            pk[q][np + 1] = pack_h2(__uint_as_float(e2[q]), __uint_as_float(o2[q]));
           }
         }
-        tc::tc_fence_before();
-        tc::fence_proxy_async_smem();
-        tc::mbar_arrive(bar_ops);
-
-        // ---------------- hop 2: spectrum x filter -> operand tiles of I2 ----------------
-        if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_mma, ph_mma, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; }
-        ph_mma ^= 1;
-        tc::tc_fence_after();
-        {
-          const float2* G = reinterpret_cast<const float2*>(P.spec[f] + MAT_FLOATS) + (size_t)(c0 + r) * 128;
-          const float bk = __ldg(P.bias[f] + c0 + r) * KAPPA;
-          float4 gn[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) gn[q] = __ldg(reinterpret_cast<const float4*>(G + (8 * half) * 8) + q);
-#pragma unroll 1
-          for (int kl = 0; kl < 8; ++kl) {
-            const int k1 = 8 * half + kl;
-            uint32_t z[16];
-            tc::tmem_ld16(tlane + 16 * k1, z);
-            float4 gq[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) gq[q] = gn[q];
-            if (kl < 7) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) gn[q] = __ldg(reinterpret_cast<const float4*>(G + (k1 + 1) * 8) + q);
-            }
-            tc::tmem_ld_wait();
-            float yr[8], yi[8];
-#pragma unroll
-            for (int k2 = 0; k2 < 8; ++k2) {
-              const float gr = ((k2 & 1) ? gq[k2 >> 1].z : gq[k2 >> 1].x) + bk;
-              const float gi = (k2 & 1) ? gq[k2 >> 1].w : gq[k2 >> 1].y;
-              const float zr = __uint_as_float(z[k2]), zi = __uint_as_float(z[8 + k2]);
-              yr[k2] = zr * gr - zi * gi;
-              yi[k2] = zr * gi + zi * gr;
-            }
-            sts128(Hs + k1 * TILE + rowoff, pack_h2(yr[0], yr[1]), pack_h2(yr[2], yr[3]), pack_h2(yr[4], yr[5]),
-                   pack_h2(yr[6], yr[7]));
-            sts128(Hs + k1 * TILE + rowoff + 128, pack_h2(yi[0], yi[1]), pack_h2(yi[2], yi[3]),
-                   pack_h2(yi[4], yi[5]), pack_h2(yi[6], yi[7]));
-          }
+        for (int q = 0; q < 8; ++q) {
+          const int ri = q >> 2, kq = q & 3;
+          const int k1 = 8 * half + 4 * g + kq;
+          sts128(Hs + k1 * TILE + rowoff + ri * 128, pk[q][0], pk[q][1], pk[q][2], pk[q][3]);
         }
-        tc::tc_fence_before();
-        tc::fence_proxy_async_smem();
-        tc::mbar_arrive(bar_ops);
-
-        // ---------------- hop 3: I2 result -> operand tiles of I1 (tile 2 n2 + ri, k = k1) ----------------
-        if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_mma, ph_mma, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; }
-        ph_mma ^= 1;
-        tc::tc_fence_after();
-#pragma unroll 1
-        for (int ri = 0; ri < 2; ++ri) {
-          uint32_t pk[8][4];                                  // [n2][k1 pair]
-#pragma unroll
-          for (int kp = 0; kp < 4; kp += 2) {
-            uint32_t e[8], o[8], e2[8], o2[8];
-            tmem_ld8(tlane + 16 * (8 * half + 2 * kp) + 8 * ri, e);
-            tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 1) + 8 * ri, o);
-            tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 2) + 8 * ri, e2);
-            tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 3) + 8 * ri, o2);
-            tc::tmem_ld_wait();
-#pragma unroll
-            for (int n2 = 0; n2 < 8; ++n2) {
-              pk[n2][kp] = pack_h2(__uint_as_float(e[n2]), __uint_as_float(o[n2]));
-              pk[n2][kp + 1] = pack_h2(__uint_as_float(e2[n2]), __uint_as_float(o2[n2]));
-            }
-          }
-#pragma unroll
-          for (int n2 = 0; n2 < 8; ++n2)
-            sts128(Hs + (2 * n2 + ri) * TILE + rowoff + half * 128, pk[n2][0], pk[n2][1], pk[n2][2], pk[n2][3]);
-        }
-        tc::tc_fence_before();
-        tc::fence_proxy_async_smem();
-        tc::mbar_arrive(bar_ops);
-
-        // ---------------- hop 4: y (float32) -> shared [t][channel] ----------------
-        if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_mma, ph_mma, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; }
-        ph_mma ^= 1;
-        tc::tc_fence_after();
-        {
-          float* Y = reinterpret_cast<float*>(Hb);
-#pragma unroll 1
-          for (int nn = 0; nn < 4; nn += 2) {
-            const int n2 = 4 * half + nn;
-            uint32_t v[16], w[16];
-            tc::tmem_ld16(tlane + 16 * n2, v);
-            tc::tmem_ld16(tlane + 16 * (n2 + 1), w);
-            tc::tmem_ld_wait();
-#pragma unroll
-            for (int n1 = 0; n1 < 16; ++n1) {
-              Y[(8 * n1 + n2) * CT + r] = __uint_as_float(v[n1]);
-              Y[(8 * n1 + n2 + 1) * CT + r] = __uint_as_float(w[n1]);
-            }
-          }
-        }
-        tc::tc_fence_before();
-        tc::mbar_arrive(bar_w);
-        if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_w, ph_w, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; }
-        ph_w ^= 1;
-
-        // ---------------- epilogue: gate / residual add, coalesced bf16 stores ----------------
-        {
-          const float2* Y2 = reinterpret_cast<const float2*>(Hb);
-          if (f == 0) {
-            Taps T2;
-            load_taps(T2, P.sw, P.sb, P.D + ch);
-            float w2[2][2];
-#pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-              const int t = t_begin - 2 + hh;
-              uint32_t px = 0;
-              if (t >= 0) px = __ldg(reinterpret_cast<const uint32_t*>(xb + P.D + (long long)t * P.xst));
-              w2[0][hh] = bf_lo(px); w2[1][hh] = bf_hi(px);
-            }
-#pragma unroll 8
-            for (int j = 0; j < 32; ++j) {
-              const int t = t_begin + j;
-              if (t >= P.L) break;
-              const uint32_t px = __ldg(reinterpret_cast<const uint32_t*>(xb + P.D + (long long)t * P.xst));
-              const uint32_t c2 = conv_step(T2, w2, px);
-              const float2 y = Y2[t * (CT / 2) + pi];
-              const uint32_t yr = pack_bf2(y.x, y.y);          // conv + bias term, cast to bf16
-              const uint32_t res = pack_bf2(bf_lo(yr) * bf_lo(c2), bf_hi(yr) * bf_hi(c2));
-              *reinterpret_cast<uint32_t*>(ob + (long long)t * P.ost) = res;
-            }
-          } else {
-#pragma unroll 8
-            for (int j = 0; j < 32; ++j) {
-              const int t = t_begin + j;
-              if (t >= P.L) break;
-              float2 y = Y2[t * (CT / 2) + pi];
-              if (sizeof(TU) == 2) {                           // bf16 layer input: yu is cast to bf16 first
-                const uint32_t yr = pack_bf2(y.x, y.y);
-                y.x = bf_lo(yr); y.y = bf_hi(yr);
-              }
-              uint32_t* po = reinterpret_cast<uint32_t*>(ob + (long long)t * P.ost);
-              const uint32_t prev = *po;                       // y * x2 written by this thread for f == 0
-              *po = pack_bf2(bf_lo(prev) + y.x, bf_hi(prev) + y.y);
-            }
-          }
-        }
-        tc::mbar_arrive(bar_w);                                // the y tile is free again
-        if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_w, ph_w, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; }
-        ph_w ^= 1;
       }
+      // filter values of hop 2 are independent of the data: fetch them before waiting on the MMAs
+      const uint4* G = reinterpret_cast<const uint4*>(P.spec[f] + MAT_FLOATS) + ((size_t)(c0 + r) * 16 + 8 * half) * 2;
+      uint4 gq[4][2];
+#pragma unroll
+      for (int kl = 0; kl < 4; ++kl) { gq[kl][0] = __ldg(G + 2 * kl); gq[kl][1] = __ldg(G + 2 * kl + 1); }
+      const float bk = __ldg(P.bias[f] + c0 + r) * KAPPA;
+      tc::tc_fence_before();
+      LC_MARK(2);
+      LC_STAGE(1)
+      LC_MARK(3);
+
+      // ---------------- hop 2: spectrum x filter -> operand tiles of I2 ----------------
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb) {
+        if (kb == 1) {
+#pragma unroll
+          for (int kl = 0; kl < 4; ++kl) { gq[kl][0] = __ldg(G + 8 + 2 * kl); gq[kl][1] = __ldg(G + 8 + 2 * kl + 1); }
+        }
+#pragma unroll
+        for (int kl = 0; kl < 4; ++kl) {
+          const int k1 = 8 * half + 4 * kb + kl;
+          uint32_t z[16];
+          tc::tmem_ld16(tlane + 16 * k1, z);
+          tc::tmem_ld_wait();
+          const uint32_t gw[8] = {gq[kl][0].x, gq[kl][0].y, gq[kl][0].z, gq[kl][0].w,
+                                  gq[kl][1].x, gq[kl][1].y, gq[kl][1].z, gq[kl][1].w};
+          float yr[8], yi[8];
+#pragma unroll
+          for (int k2 = 0; k2 < 8; ++k2) {
+            const float2 gg = __half22float2(*reinterpret_cast<const __half2*>(&gw[k2]));
+            const float gr = gg.x + bk, gi = gg.y;
+            const float zr = __uint_as_float(z[k2]), zi = __uint_as_float(z[8 + k2]);
+            yr[k2] = zr * gr - zi * gi;
+            yi[k2] = zr * gi + zi * gr;
+          }
+          sts128(Hs + k1 * TILE + rowoff, pack_h2(yr[0], yr[1]), pack_h2(yr[2], yr[3]), pack_h2(yr[4], yr[5]),
+                 pack_h2(yr[6], yr[7]));
+          sts128(Hs + k1 * TILE + rowoff + 128, pack_h2(yi[0], yi[1]), pack_h2(yi[2], yi[3]),
+                 pack_h2(yi[4], yi[5]), pack_h2(yi[6], yi[7]));
+        }
+      }
+      tc::tc_fence_before();
+      LC_MARK(4);
+      LC_STAGE(2)
+      LC_MARK(5);
+
+      // ---------------- hop 3: I2 result -> operand tiles of I1 (tile 2 n2 + ri, k = k1) ----------------
+#pragma unroll 1
+      for (int ri = 0; ri < 2; ++ri) {
+        uint32_t pk[8][4];                                  // [n2][k1 pair]
+#pragma unroll
+        for (int kp = 0; kp < 4; kp += 2) {
+          uint32_t e[8], o[8], e2[8], o2[8];
+          tmem_ld8(tlane + 16 * (8 * half + 2 * kp) + 8 * ri, e);
+          tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 1) + 8 * ri, o);
+          tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 2) + 8 * ri, e2);
+          tmem_ld8(tlane + 16 * (8 * half + 2 * kp + 3) + 8 * ri, o2);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int n2 = 0; n2 < 8; ++n2) {
+            pk[n2][kp] = pack_h2(__uint_as_float(e[n2]), __uint_as_float(o[n2]));
+            pk[n2][kp + 1] = pack_h2(__uint_as_float(e2[n2]), __uint_as_float(o2[n2]));
+          }
+        }
+#pragma unroll
+        for (int n2 = 0; n2 < 8; ++n2)
+          sts128(Hs + (2 * n2 + ri) * TILE + rowoff + half * 128, pk[n2][0], pk[n2][1], pk[n2][2], pk[n2][3]);
+      }
+      tc::tc_fence_before();
+      LC_MARK(6);
+      LC_STAGE(3)
+      LC_MARK(7);
+
+      // ---------------- hop 4: y (float32) -> shared [t][channel] ----------------
+      {
+        float* Y = reinterpret_cast<float*>(Hb);
+#pragma unroll 1
+        for (int nn = 0; nn < 4; nn += 2) {
+          const int n2 = 4 * half + nn;
+          uint32_t v[16], w[16];
+          tc::tmem_ld16(tlane + 16 * n2, v);
+          tc::tmem_ld16(tlane + 16 * (n2 + 1), w);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int n1 = 0; n1 < 16; ++n1) {
+            Y[(8 * n1 + n2) * CT + r] = __uint_as_float(v[n1]);
+            Y[(8 * n1 + n2 + 1) * CT + r] = __uint_as_float(w[n1]);
+          }
+        }
+      }
+      // the gate's inputs (f == 0) or the partial result (f == 1) can be fetched while the others finish
+      uint32_t gl[34];
+      if (f == 0) {
+#pragma unroll
+        for (int j = 0; j < 34; ++j) {
+          const int t = t_begin - 2 + j;
+          gl[j] = 0;
+          if (t >= 0 && t < P.L) gl[j] = __ldg(reinterpret_cast<const uint32_t*>(xb + P.D + (long long)t * P.xst));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int t = t_begin + j;
+          gl[j] = 0;
+          if (t < P.L) gl[j] = *reinterpret_cast<const uint32_t*>(ob + (long long)t * P.ost);   // written by this thread
+        }
+      }
+      tc::tc_fence_before();
+      LC_MARK(8);
+      LC_WORKER_BARRIER()
+      LC_MARK(9);
+
+      // ---------------- epilogue: gate / residual add, coalesced bf16 stores ----------------
+      {
+        const float2* Y2 = reinterpret_cast<const float2*>(Hb);
+        if (f == 0) {
+          Taps T2;
+          load_taps(T2, P.sw, P.sb, P.D + ch);
+          float w2[2][2] = {{bf_lo(gl[0]), bf_lo(gl[1])}, {bf_hi(gl[0]), bf_hi(gl[1])}};
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int t = t_begin + j;
+            const uint32_t c2 = conv_step(T2, w2, gl[j + 2]);
+            const float2 y = Y2[t * (CT / 2) + pi];
+            const uint32_t yr = pack_bf2(y.x, y.y);          // conv + bias term, cast to bf16
+            const uint32_t res = pack_bf2(bf_lo(yr) * bf_lo(c2), bf_hi(yr) * bf_hi(c2));
+            if (t < P.L) *reinterpret_cast<uint32_t*>(ob + (long long)t * P.ost) = res;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int t = t_begin + j;
+            float2 y = Y2[t * (CT / 2) + pi];
+            if (sizeof(TU) == 2) {                           // bf16 layer input: yu is cast to bf16 first
+              const uint32_t yr = pack_bf2(y.x, y.y);
+              y.x = bf_lo(yr); y.y = bf_hi(yr);
+            }
+            if (t < P.L)
+              *reinterpret_cast<uint32_t*>(ob + (long long)t * P.ost) = pack_bf2(bf_lo(gl[j]) + y.x, bf_hi(gl[j]) + y.y);
+          }
+        }
+      }
+      LC_MARK(10 + (f == 0 ? 0 : 1));
+      LC_WORKER_BARRIER()                                    // the y tile is free again
+      LC_MARK(12);
     }
   }
+#undef LC_STAGE
+#undef LC_WORKER_BARRIER
 
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 0) {
     tc::tc_fence_after();
     tc::tmem_dealloc(tmem, 256);
   }
@@ -559,13 +575,23 @@ constexpr size_t SMEM_BYTES = H_BYTES + MAT_BYTES + 64 + 128;
 
 }  // namespace lc
 
+#ifdef M2_LC_TIMING
+extern "C" int m2_debug_phase_cycles(unsigned long long* out, int reset) {
+  unsigned long long z[16] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, lc::g_phase_cycles, sizeof(z));
+  if (reset) cudaMemcpyToSymbol(lc::g_phase_cycles, z, sizeof(z));
+  return 0;
+}
+#endif
+
 int longconv_tc_supported(int seq_len, m2_dtype act_dtype, int d_model) {
   return act_dtype == M2_BF16 && seq_len > 64 && seq_len <= 128 && d_model % lc::CT == 0;
 }
 
 size_t spectrum_kind1_floats(int D, int L) {
   (void)L;
-  return (size_t)lc::MAT_FLOATS + (size_t)256 * D;
+  return (size_t)lc::MAT_FLOATS + (size_t)128 * D;
 }
 
 int spectrum_kind1_launch(int D, int L, const float* k, float* spec, cudaStream_t st) {
@@ -587,8 +613,6 @@ int longconv_tc_launch(const m2_longconv_args* a, cudaStream_t st) {
   Params P;
   P.B = a->batch; P.L = a->seq_len; P.D = a->d_model; P.nf = a->n_filters;
   P.ctiles = a->d_model / CT; P.units = P.B * P.ctiles;
-  P.lbo = 128; P.sbo = 256;
-  if (getenv("M2_LC_SWAP_STRIDES")) { P.lbo = 256; P.sbo = 128; }   // bring-up aid
   P.xin = (const __nv_bfloat16*)a->xin; P.xsb = a->xin_sb; P.xst = a->xin_st;
   P.u = a->u; P.usb = a->u_sb; P.ust = a->u_st;
   P.out = (__nv_bfloat16*)a->out; P.osb = a->out_sb; P.ost = a->out_st;

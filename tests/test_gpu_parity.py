@@ -270,15 +270,32 @@ def test_encoder_small_fp32_and_bf16():
 
 
 def test_encoder_80m_shape_bf16():
-    """Two 80M-shaped layers at the benchmark's (B, L) against the stock-op path."""
+    """Two 80M-shaped layers at the benchmark's L against the stock-op path.
+
+    The path's tolerance (2e-2) is a per-layer statement: each layer is checked on the SAME
+    input the stock-op path saw.  Run free, the differences of layer 1 (single bf16 rounding
+    flips of intermediates, which any two correct implementations show) are re-mixed by
+    layer 2, so the stacked output is held to twice the per-layer bound.
+    """
     cfg = dict(kind="encoder", seed=43, B=16, L=128, D=768, I=3072, layers=2, vocab=30528, order=128)
     model, sd = _encoder(cfg, DEV)
     ids_t = torch.from_numpy(np.random.default_rng(1).integers(0, 30528, size=(16, 128))).to(DEV)
     sdt = to_torch(sd, DEV)
     with torch.autocast("cuda", dtype=torch.bfloat16):
+        h_ref = T.embeddings_forward(sdt, ids_t)
+        h_own = model.embeddings(ids_t)
+        assert O.parity_error(npy(h_own), npy(h_ref)) < 1e-5
+        for i, layer in enumerate(model.encoder.layer):
+            p = f"encoder.layer.{i}."
+            a_ref = T.mixer_forward(sdt, h_ref, bidirectional=True, residual_long_conv=True, prefix=p + "attention.")
+            nxt_ref = T.glu_mlp_forward(sdt, a_ref, prefix=p + "mlp.")
+            a_own, _ = layer.attention(h_ref)
+            assert O.parity_error(npy(a_own), npy(a_ref)) < TOL_BF16
+            assert O.parity_error(npy(layer.mlp(a_ref)), npy(nxt_ref)) < TOL_BF16
+            assert O.parity_error(npy(layer(h_ref)), npy(nxt_ref)) < TOL_BF16
+            h_ref = nxt_ref
         y, _ = model(ids_t)
-        ref = T.encoder_forward(sdt, T.embeddings_forward(sdt, ids_t), 2)
-    assert O.parity_error(npy(y), npy(ref)) < TOL_BF16
+    assert O.parity_error(npy(y), npy(h_ref)) < 2 * TOL_BF16
 
 
 # ---- error behaviour -----------------------------------------------------------------
