@@ -136,11 +136,24 @@ hyena_filter_kernel(FilterParams p) {
 // bit-reversed position of their bin.
 template <typename R> struct Cplx { R x, y; };
 
-template <typename R>
+// alpha/beta of bin k from Z[k] and conj(Z[M-k])
+__device__ __forceinline__ void alpha_beta(double2 Zk, double2 Zm, int k, int N, double invM, float2* alpha, float2* beta) {
+  const double2 Xe = make_double2(0.5 * (Zk.x + Zm.x), 0.5 * (Zk.y + Zm.y));
+  const double2 Xo = make_double2(0.5 * (Zk.y - Zm.y), -0.5 * (Zk.x - Zm.x));   // (Zk - Zm) / (2i)
+  double sn, cs;
+  sincospi(2.0 * k / N, &sn, &cs);                                            // theta = 2 pi k / N
+  const double2 Dk = make_double2(Xo.x * cs + Xo.y * sn, Xo.y * cs - Xo.x * sn);   // W^k Xo, W^k = cos - i sin
+  *alpha = make_float2((float)((Xe.x - Dk.x * sn) * invM), (float)((Xe.y - Dk.y * sn) * invM));
+  *beta = make_float2((float)(-Dk.y * cs * invM), (float)(Dk.x * cs * invM));
+}
+
+// R: scalar type of the work array.  GLOBAL = false keeps the M work points in shared
+// memory; GLOBAL = true (rows too long for shared memory) works in place in the channel's
+// own beta region of the output table, which is overwritten pair by pair at the end.
+template <typename R, bool GLOBAL>
 __global__ void __launch_bounds__(256)
 spectrum_kind0_kernel(const float* __restrict__ k2, float* __restrict__ spec, int D, int M) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  Cplx<R>* s = reinterpret_cast<Cplx<R>*>(smem_raw);   // M complex points
   const int N = 2 * M;
   const int lg = 31 - __clz(M);
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -154,6 +167,10 @@ spectrum_kind0_kernel(const float* __restrict__ k2, float* __restrict__ spec, in
     return;
   }
   const int c = blockIdx.x;
+  float2* alpha = reinterpret_cast<float2*>(spec + M + (size_t)c * 4 * M);
+  float2* beta = alpha + M;
+  Cplx<R>* s = GLOBAL ? reinterpret_cast<Cplx<R>*>(beta) : reinterpret_cast<Cplx<R>*>(smem_raw);
+  static_assert(!GLOBAL || sizeof(Cplx<R>) == sizeof(float2), "in-place work array must match the table's element size");
   const float* row = k2 + (size_t)c * N;
   for (int n = tid; n < M; n += nt) s[n] = Cplx<R>{(R)row[2 * n], (R)row[2 * n + 1]};
   __syncthreads();
@@ -170,24 +187,19 @@ spectrum_kind0_kernel(const float* __restrict__ k2, float* __restrict__ spec, in
     }
     __syncthreads();
   }
-  float2* alpha = reinterpret_cast<float2*>(spec + M + (size_t)c * 4 * M);
-  float2* beta = alpha + M;
   const double invM = 1.0 / M;
-  for (int k = tid; k < M; k += nt) {
-    const int pk = (lg == 0) ? 0 : (int)(__brev((unsigned)k) >> (32 - lg));
+  // bins are finished in pairs (k, M-k): both inputs are read before either output is written
+  for (int k = tid; k <= M / 2; k += nt) {
     const int km = (M - k) % M;
+    const int pk = (lg == 0) ? 0 : (int)(__brev((unsigned)k) >> (32 - lg));
     const int pm = (lg == 0) ? 0 : (int)(__brev((unsigned)km) >> (32 - lg));
     const double2 Zk = make_double2((double)s[pk].x, (double)s[pk].y);
-    const double2 Zm = make_double2((double)s[pm].x, -(double)s[pm].y);
-    const double2 Xe = make_double2(0.5 * (Zk.x + Zm.x), 0.5 * (Zk.y + Zm.y));
-    // Xo = (Zk - Zm) / (2i)
-    const double2 Xo = make_double2(0.5 * (Zk.y - Zm.y), -0.5 * (Zk.x - Zm.x));
-    double sn, cs;
-    sincospi(2.0 * k / N, &sn, &cs);           // theta = 2 pi k / N
-    // Dk = W^k Xo, W^k = cos - i sin
-    const double2 Dk = make_double2(Xo.x * cs + Xo.y * sn, Xo.y * cs - Xo.x * sn);
-    alpha[pk] = make_float2((float)((Xe.x - Dk.x * sn) * invM), (float)((Xe.y - Dk.y * sn) * invM));
-    beta[pk] = make_float2((float)(-Dk.y * cs * invM), (float)(Dk.x * cs * invM));
+    const double2 Zq = make_double2((double)s[pm].x, (double)s[pm].y);
+    float2 a1, b1, a2, b2;
+    alpha_beta(Zk, make_double2(Zq.x, -Zq.y), k, N, invM, &a1, &b1);
+    alpha_beta(Zq, make_double2(Zk.x, -Zk.y), km, N, invM, &a2, &b2);
+    alpha[pk] = a1; beta[pk] = b1;
+    if (pm != pk) { alpha[pm] = a2; beta[pm] = b2; }
   }
 }
 
@@ -196,15 +208,17 @@ int spectrum_kind0_launch(int D, int L, const float* k, float* spec, cudaStream_
   while (M < L) M <<= 1;
   if (M <= 8192) {
     const size_t smem = (size_t)M * sizeof(Cplx<double>);
-    auto kern = spectrum_kind0_kernel<double>;
+    auto kern = spectrum_kind0_kernel<double, false>;
+    M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<D + 1, 256, smem, st>>>(k, spec, D, M);
+  } else if (M <= 16384) {
+    const size_t smem = (size_t)M * sizeof(Cplx<float>);
+    auto kern = spectrum_kind0_kernel<float, false>;
     M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<D + 1, 256, smem, st>>>(k, spec, D, M);
   } else {
-    const size_t smem = (size_t)M * sizeof(Cplx<float>);
-    M2_REQUIRE(smem <= 200 * 1024, M2_ERR_UNSUPPORTED, "m2_filter_spectrum: seq_len %d too long for kind 0", L);
-    auto kern = spectrum_kind0_kernel<float>;
-    M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<D + 1, 256, smem, st>>>(k, spec, D, M);
+    M2_REQUIRE(M <= 32768, M2_ERR_UNSUPPORTED, "m2_filter_spectrum: seq_len %d too long for kind 0", L);
+    spectrum_kind0_kernel<float, true><<<D + 1, 256, 0, st>>>(k, spec, D, M);
   }
   M2_LAUNCH_CHECK("spectrum_kind0_kernel");
   return M2_OK;

@@ -151,7 +151,7 @@ def test_plain_long_conv_impulse_and_linearity():
     assert O.parity_error(npy(f(a, L)), ref) < TOL_FP32
 
 
-@pytest.mark.parametrize("L,B,D", [(8192, 2, 64), (16384, 1, 32)])
+@pytest.mark.parametrize("L,B,D", [(8192, 2, 64), (16384, 1, 32), (32768, 2, 16), (20000, 1, 8)])
 def test_long_sequences_bf16(L, B, D):
     """Long rows against the stock-op path under autocast; batch rows are independent."""
     cfg = dict(C.CASES["mixer_small"], L=L, l_max=L, D=D, B=B, order=64, seed=77)
@@ -163,6 +163,11 @@ def test_long_sequences_bf16(L, B, D):
         y0, _ = m(u[:1])
     assert O.parity_error(npy(y), npy(ref)) < TOL_BF16
     assert torch.equal(y0, y[:1])
+    # float32 path of the same long rows against the stock-op path in float64
+    yf, _ = m(u)
+    sd64 = to_torch(sd, DEV, torch.float64)
+    ref64 = T.mixer_forward(sd64, u.double(), bidirectional=True, residual_long_conv=True)
+    assert O.parity_error(npy(yf), ref64.cpu().numpy()) < TOL_FP32
 
 
 # ---- BlockdiagLinear and the GLU MLP -------------------------------------------------
