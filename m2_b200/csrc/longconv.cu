@@ -9,15 +9,22 @@ int longconv_tc_supported(int seq_len, m2_dtype act_dtype, int d_model);
 size_t spectrum_kind1_floats(int D, int L);
 int spectrum_kind1_launch(int D, int L, const float* k, float* spec, cudaStream_t st);
 int longconv_tc_launch(const m2_longconv_args* a, cudaStream_t st);
+int longconv_tcl_supported(int seq_len, m2_dtype act_dtype);
+size_t spectrum_kind2_floats(int D, int L);
+int spectrum_kind2_launch(int D, int L, const float* k, float* spec, cudaStream_t st);
+int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st);
 }  // namespace m2
 
 extern "C" int m2_longconv_kind(int seq_len, m2_dtype act_dtype, int d_model) {
-  return m2::longconv_tc_supported(seq_len, act_dtype, d_model) ? 1 : 0;
+  if (m2::longconv_tc_supported(seq_len, act_dtype, d_model)) return 1;
+  if (m2::longconv_tcl_supported(seq_len, act_dtype)) return 2;
+  return 0;
 }
 
 extern "C" size_t m2_filter_spectrum_floats(int kind, int d_model, int seq_len) {
   if (d_model <= 0 || seq_len <= 0) return 0;
   if (kind == 1) return m2::spectrum_kind1_floats(d_model, seq_len);
+  if (kind == 2) return m2::spectrum_kind2_floats(d_model, seq_len);
   const size_t M = (size_t)m2_filter_row_len(seq_len) / 2;
   return M + 4 * M * (size_t)d_model;
 }
@@ -31,6 +38,7 @@ extern "C" int m2_filter_spectrum(int kind, int d_model, int seq_len, const floa
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (kind == 0) return m2::spectrum_kind0_launch(d_model, seq_len, k, spec_out, st);
   if (kind == 1) return m2::spectrum_kind1_launch(d_model, seq_len, k, spec_out, st);
+  if (kind == 2) return m2::spectrum_kind2_launch(d_model, seq_len, k, spec_out, st);
   return m2_set_error(M2_ERR_ARG, "m2_filter_spectrum: unknown kind %d", kind);
 }
 
@@ -53,5 +61,6 @@ extern "C" int m2_longconv_fwd(const m2_longconv_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->kind == 0 || a->plain) return m2::longconv_simt_launch(a, st);
   if (a->kind == 1) return m2::longconv_tc_launch(a, st);
+  if (a->kind == 2) return m2::longconv_tcl_launch(a, st);
   return m2_set_error(M2_ERR_ARG, "m2_longconv_fwd: unknown kind %d", a->kind);
 }

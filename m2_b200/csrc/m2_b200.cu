@@ -4,6 +4,7 @@
 #include "filter.cu"
 #include "longconv_simt.cu"
 #include "longconv_tc.cu"
+#include "longconv_tcl.cu"
 #include "longconv.cu"
 #include "gemm_tc.cu"
 #include "gemm_simt.cu"

@@ -86,8 +86,16 @@ class MonarchMixerSequenceMixing(nn.Module):
         filters = [self.filter_fn] + ([self.filter_fn2] if self.residual_long_conv else [])
         specs = [f.spectrum(L, bf16, kind) for f in filters]
         biases = [f.conv_bias() for f in filters]
-        y = ops.longconv_fwd(xin, u_orig if self.residual_long_conv else None,
-                             self.short_filter.weight, self.short_filter.bias, specs, biases,
-                             kind=kind, bf16_rounding=bf16)
+        ures = u_orig if self.residual_long_conv else None
+        if kind == 2:
+            # the long-row kernel reads and writes time-contiguous rows: (B, channels, L)
+            xin = xin.transpose(1, 2).contiguous().transpose(1, 2)
+            if ures is not None:
+                ures = ures.transpose(1, 2).contiguous().transpose(1, 2)
+            out = torch.empty((u.shape[0], self.d_model, L), dtype=xin.dtype, device=xin.device).transpose(1, 2)
+        else:
+            out = None
+        y = ops.longconv_fwd(xin, ures, self.short_filter.weight, self.short_filter.bias, specs, biases,
+                             kind=kind, bf16_rounding=bf16, out=out)
         y = self.out_linear(y)
         return y, None

@@ -376,3 +376,37 @@ def test_longconv_tensor_core_family(L, residual, u_bf16):
             O.parity_error(npy(outs[1]), npy(outs[0])))
     print("kind0-vs-oracle %.3e  kind1-vs-oracle %.3e  kind1-vs-kind0 %.3e" % errs)
     assert max(errs) < TOL_BF16, errs
+
+
+# ---- long-row tensor-core family (time-contiguous rows) against the CUDA-core family ----
+@pytest.mark.parametrize("L,D,B", [(2048, 64, 2), (1500, 16, 1), (8192, 32, 2), (6000, 8, 1), (4100, 8, 1)])
+@pytest.mark.parametrize("residual,u_bf16", [(True, False), (True, True), (False, False)])
+def test_longconv_long_row_family(L, D, B, residual, u_bf16):
+    cfg = dict(C.CASES["mixer_small"], L=L, l_max=L, D=D, B=B, order=32, residual=residual, seed=71)
+    m, sd = build_mixer(cfg, DEV)
+    g = torch.Generator().manual_seed(L)
+    xinT = (0.6 * torch.randn((B, 3 * D, L), generator=g)).to(DEV).bfloat16()
+    uT = torch.randn((B, D, L), generator=g).to(DEV)
+    if u_bf16:
+        uT = uT.bfloat16()
+    xin, u = xinT.transpose(1, 2), uT.transpose(1, 2)        # (B, L, C) views of time-contiguous rows
+    assert ops.longconv_kind(L, torch.bfloat16, D) == 2
+    filters = [m.filter_fn] + ([m.filter_fn2] if residual else [])
+    outs = []
+    for kind in (0, 2):
+        specs = [f.spectrum(L, True, kind) for f in filters]
+        out = torch.empty((B, D, L), dtype=torch.bfloat16, device=DEV).transpose(1, 2)
+        outs.append(ops.longconv_fwd(xin, u if residual else None, m.short_filter.weight,
+                                     m.short_filter.bias, specs, [f.conv_bias() for f in filters],
+                                     kind=kind, bf16_rounding=True, out=out))
+    errs = [O.parity_error(npy(outs[1]), npy(outs[0]))]
+    if B * L * D <= 1 << 18:
+        taps = []
+        for f in filters:
+            k = npy(f.time_filter(L, True))
+            taps.append((k[:, :L], k[:, k.shape[1] - L:][:, ::-1], npy(f.bias)))
+        ref = O.mixer_core(npy(xin), npy(u), sd, bidirectional=True, residual_long_conv=residual,
+                           mode="bf16", u_is_bf16=u_bf16, filters=taps)
+        errs += [O.parity_error(npy(outs[0]), ref), O.parity_error(npy(outs[1]), ref)]
+    print("kind2-vs-kind0 / kind0-vs-oracle / kind2-vs-oracle:", ["%.3e" % e for e in errs])
+    assert max(errs) < TOL_BF16, errs
