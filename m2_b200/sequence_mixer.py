@@ -12,6 +12,29 @@ from . import ops
 from .hyena_filter import HyenaFilter, _autocast_bf16
 
 
+_PAD = 64   # extra contraction columns that carry the bias through the GEMM
+
+
+class _AugmentedLinear:
+    """bf16 copy of a Linear's weight with the bias as one more input column, refreshed when
+    the parameters change.  Feeding an input whose extra column is 1 makes the GEMM add the
+    (bf16-rounded, as under autocast) bias inside its float32 accumulator, so the result is
+    rounded to bf16 exactly once -- like F.linear -- whatever layout the GEMM writes."""
+
+    def __init__(self):
+        self.key, self.w = None, None
+
+    def get(self, lin):
+        key = (lin.weight.data_ptr(), lin.weight._version, lin.bias._version, lin.weight.device)
+        if key != self.key:
+            out_f, in_f = lin.weight.shape
+            w = torch.zeros((out_f, in_f + _PAD), dtype=torch.bfloat16, device=lin.weight.device)
+            w[:, :in_f] = lin.weight.detach()
+            w[:, in_f] = lin.bias.detach()
+            self.key, self.w = key, w
+        return self.w
+
+
 def _check_forward_only(module, x):
     """The kernels implement the forward pass only; refuse to build an autograd graph
     silently."""
@@ -64,6 +87,28 @@ class MonarchMixerSequenceMixing(nn.Module):
         width = d_model * self.NUM_PROJECTIONS
         self.short_filter = nn.Conv1d(width, width, kernel_size=3, groups=width, padding=2)
 
+    def _forward_long_rows(self, u, ures, specs, biases):
+        """bf16 path for long sequences: the convolution kernel works on time-contiguous
+        rows, so in_linear writes (B, 3D, L) and out_linear reads (B, D, L) -- both as
+        library GEMMs on transposed operands, no transposed copy of an activation."""
+        B, L, D = u.shape
+        if not hasattr(self, "_aug_in"):
+            self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
+        w_in, w_out = self._aug_in.get(self.in_linear), self._aug_out.get(self.out_linear)
+        x_aug = torch.zeros((B, L, D + _PAD), dtype=torch.bfloat16, device=u.device)
+        x_aug[..., :D] = u
+        x_aug[..., D] = 1.0
+        with torch.autocast("cuda", enabled=False):
+            xin_t = torch.matmul(w_in, x_aug.transpose(1, 2))                    # (B, 3D, L)
+            u_t = ures.transpose(1, 2).contiguous() if ures is not None else None
+            y_t = torch.empty((B, D + _PAD, L), dtype=torch.bfloat16, device=u.device)
+            y_t[:, D] = 1.0
+            y_t[:, D + 1:] = 0.0
+            ops.longconv_fwd(xin_t.transpose(1, 2), u_t.transpose(1, 2) if u_t is not None else None,
+                             self.short_filter.weight, self.short_filter.bias, specs, biases,
+                             kind=2, bf16_rounding=True, out=y_t[:, :D].transpose(1, 2))
+            return torch.matmul(y_t.transpose(1, 2), w_out.t())                  # (B, L, D)
+
     def forward(self, u, **kwargs):
         _check_forward_only(self, u)
         if not u.is_cuda:
@@ -81,21 +126,16 @@ class MonarchMixerSequenceMixing(nn.Module):
         if u.dim() == 2:
             u = u.unsqueeze(0)
         u_orig = u
-        xin = self.in_linear(u)                        # bf16 under autocast, float32 otherwise
-        kind = ops.longconv_kind(L, xin.dtype, self.d_model)
         filters = [self.filter_fn] + ([self.filter_fn2] if self.residual_long_conv else [])
-        specs = [f.spectrum(L, bf16, kind) for f in filters]
         biases = [f.conv_bias() for f in filters]
+        act_dtype = torch.bfloat16 if bf16 else u.dtype
+        kind = ops.longconv_kind(L, act_dtype, self.d_model)
+        specs = [f.spectrum(L, bf16, kind) for f in filters]
         ures = u_orig if self.residual_long_conv else None
         if kind == 2:
-            # the long-row kernel reads and writes time-contiguous rows: (B, channels, L)
-            xin = xin.transpose(1, 2).contiguous().transpose(1, 2)
-            if ures is not None:
-                ures = ures.transpose(1, 2).contiguous().transpose(1, 2)
-            out = torch.empty((u.shape[0], self.d_model, L), dtype=xin.dtype, device=xin.device).transpose(1, 2)
-        else:
-            out = None
+            return self._forward_long_rows(u, ures, specs, biases), None
+        xin = self.in_linear(u)                        # bf16 under autocast, float32 otherwise
         y = ops.longconv_fwd(xin, ures, self.short_filter.weight, self.short_filter.bias, specs, biases,
-                             kind=kind, bf16_rounding=bf16, out=out)
+                             kind=kind, bf16_rounding=bf16)
         y = self.out_linear(y)
         return y, None
