@@ -182,6 +182,9 @@ int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);
  * Replaces `self.layernorm(hidden_states + residual_connection)`, bert/src/bert_layers.py:506.
  * a, b (m, n) of `in_dtype` (the sum is rounded to bf16 first when in_dtype is M2_BF16, as a
  * bf16 tensor add does); out (m, n) of `out_dtype`; weight/bias float32 (n).
+ * out_bf16 (optional, may be NULL): a second copy of the result rounded to bf16, row stride
+ * ld_bf16 -- what the next layer's in_linear reads under autocast (its cast of the float32
+ * LayerNorm output), written here instead of by a separate cast pass.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int m, n;
@@ -191,6 +194,7 @@ typedef struct {
   const float* weight; const float* bias;
   float eps;
   void* out; long long ldo;
+  void* out_bf16; long long ld_bf16;
 } m2_add_layernorm_args;
 
 int m2_add_layernorm_fwd(const m2_add_layernorm_args* args, void* stream);

@@ -66,6 +66,7 @@ class AddLayernormArgs(C.Structure):
         ("a", C.c_void_p), ("lda", C.c_longlong), ("b", C.c_void_p), ("ldb", C.c_longlong),
         ("weight", C.c_void_p), ("bias", C.c_void_p), ("eps", C.c_float),
         ("out", C.c_void_p), ("ldo", C.c_longlong),
+        ("out_bf16", C.c_void_p), ("ld_bf16", C.c_longlong),
     ]
 
 

@@ -145,6 +145,69 @@ add_layernorm_kernel(const TI* a, long long lda, const TI* b, long long ldb, con
     st_from_float(po + i, (row[i] - mean) * rstd * __ldg(w + i) + __ldg(bias + i));
 }
 
+// Vectorised variant: one warp per row, the row held in registers (n a multiple of 256 up to
+// 2048, 16-byte aligned rows); optional second output rounded to bf16.
+template <typename TO, int VI>
+__global__ void __launch_bounds__(256)
+add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* b, long long ldb,
+                          const float* __restrict__ w, const float* __restrict__ bias, float eps, TO* out,
+                          long long ldo, __nv_bfloat16* out2, long long ld2, int m) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= m) return;
+  const uint4* pa = reinterpret_cast<const uint4*>(a + (long long)warp * lda);
+  const uint4* pb = reinterpret_cast<const uint4*>(b + (long long)warp * ldb);
+  float v[VI][8];
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < VI; ++i) {
+    const uint4 xa = __ldg(pa + i * 32 + lane), xb = __ldg(pb + i * 32 + lane);
+    const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      // bf16 + bf16 -> bf16 (the residual add of two bf16 tensors), then float32 statistics
+      v[i][2 * j] = bf16r(__uint_as_float(wa[j] << 16) + __uint_as_float(wb[j] << 16));
+      v[i][2 * j + 1] = bf16r(__uint_as_float(wa[j] & 0xffff0000u) + __uint_as_float(wb[j] & 0xffff0000u));
+      sum += v[i][2 * j] + v[i][2 * j + 1];
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const int n = VI * 256;
+  const float mean = sum / n;
+  float sq = 0.f;
+#pragma unroll
+  for (int i = 0; i < VI; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float d = v[i][j] - mean; sq += d * d; }
+  for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+  const float rstd = rsqrtf(sq / n + eps);
+#pragma unroll
+  for (int i = 0; i < VI; ++i) {
+    const int c0 = (i * 32 + lane) * 8;
+    const float4 w0 = __ldg(reinterpret_cast<const float4*>(w + c0)), w1 = __ldg(reinterpret_cast<const float4*>(w + c0 + 4));
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(bias + c0)), b1 = __ldg(reinterpret_cast<const float4*>(bias + c0 + 4));
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+    float y[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = (v[i][j] - mean) * rstd * ww[j] + bb[j];
+    uint32_t pk[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
+      pk[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    if (sizeof(TO) == 4) {
+      float4* po = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (long long)warp * ldo + c0);
+      po[0] = make_float4(y[0], y[1], y[2], y[3]);
+      po[1] = make_float4(y[4], y[5], y[6], y[7]);
+    } else {
+      *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out) + (long long)warp * ldo + c0) =
+          make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    }
+    if (out2) *reinterpret_cast<uint4*>(out2 + (long long)warp * ld2 + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+}
+
 int blockdiag_tc_launch(const m2_blockdiag_args* a, cudaStream_t st);   // gemm_tc.cu
 int glu_tc_launch(const m2_glu_args* a, cudaStream_t st);
 bool blockdiag_tc_supported(const m2_blockdiag_args* a);
@@ -217,6 +280,27 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
   if (a->m == 0) return M2_OK;
   M2_REQUIRE(a->a && a->b && a->weight && a->bias && a->out, M2_ERR_ARG, "m2_add_layernorm_fwd: NULL tensor pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  M2_REQUIRE(a->out_bf16 == nullptr || a->ld_bf16 >= a->n, M2_ERR_ARG, "m2_add_layernorm_fwd: ld_bf16 smaller than the row");
+  const bool vec = a->in_dtype == M2_BF16 && a->n % 256 == 0 && a->n <= 2048 && a->lda % 8 == 0 && a->ldb % 8 == 0 &&
+                   m2_aligned(a->a, 16) && m2_aligned(a->b, 16) && m2_aligned(a->out, 16) && a->ldo % 8 == 0 &&
+                   m2_aligned(a->weight, 16) && m2_aligned(a->bias, 16) &&
+                   (a->out_bf16 == nullptr || (m2_aligned(a->out_bf16, 16) && a->ld_bf16 % 8 == 0));
+  if (vec) {
+    const int blocks = (a->m + 7) / 8;
+#define M2_LNW(TO, VI) add_layernorm_warp_kernel<TO, VI><<<blocks, 256, 0, st>>>( \
+      (const __nv_bfloat16*)a->a, a->lda, (const __nv_bfloat16*)a->b, a->ldb, a->weight, a->bias, a->eps, \
+      (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m)
+#define M2_LNW_VI(TO) switch (a->n / 256) { case 1: M2_LNW(TO, 1); break; case 2: M2_LNW(TO, 2); break; \
+      case 3: M2_LNW(TO, 3); break; case 4: M2_LNW(TO, 4); break; case 5: M2_LNW(TO, 5); break; \
+      case 6: M2_LNW(TO, 6); break; case 7: M2_LNW(TO, 7); break; default: M2_LNW(TO, 8); break; }
+    if (a->out_dtype == M2_F32) { M2_LNW_VI(float) } else { M2_LNW_VI(__nv_bfloat16) }
+#undef M2_LNW_VI
+#undef M2_LNW
+    M2_LAUNCH_CHECK("add_layernorm_warp_kernel");
+    return M2_OK;
+  }
+  M2_REQUIRE(a->out_bf16 == nullptr, M2_ERR_UNSUPPORTED,
+             "m2_add_layernorm_fwd: the bf16 copy needs bf16 inputs, n a multiple of 256 (<= 2048) and 16-byte aligned rows");
   const size_t smem = (size_t)a->n * sizeof(float);
   const int threads = a->n >= 1024 ? 256 : 128;
 #define M2_LN(TI, TO) add_layernorm_kernel<TI, TO><<<a->m, threads, smem, st>>>( \

@@ -50,6 +50,15 @@ class BertGatedLinearUnitMLP(nn.Module):
                               cfg.hidden_size)
         # under autocast LayerNorm runs in float32 and returns float32
         out_dtype = torch.float32 if dt == torch.bfloat16 else dt
+        aug = None
+        if dt == torch.bfloat16 and x.dim() == 3 and x.shape[-1] % 256 == 0 and x.shape[-1] <= 2048:
+            # the next layer's in_linear reads this output cast to bf16: write that copy here
+            # (with the bias column its GEMM uses) instead of leaving it to a separate cast pass
+            from .sequence_mixer import make_augmented
+            aug = make_augmented(x2.shape[0], x.shape[-1], x.device)
         y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,
-                                  self.layernorm.eps, out_dtype)
-        return y.reshape(x.shape)
+                                  self.layernorm.eps, out_dtype, bf16_copy=aug)
+        y = y.reshape(x.shape)
+        if aug is not None:
+            y._m2_aug = aug
+        return y

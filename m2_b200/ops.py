@@ -209,8 +209,9 @@ def blockdiag_glu_fwd(x2d, wg, inter):
     return h
 
 
-def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype):
-    """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype."""
+def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None):
+    """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype.  bf16_copy:
+    optional (m, >= n) bf16 tensor that receives the result rounded to bf16."""
     _need_cuda(a2d, b2d)
     if a2d.stride(-1) != 1:
         a2d = a2d.contiguous()
@@ -227,6 +228,9 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype):
     a.b, a.ldb = b2d.data_ptr(), max(b2d.stride(0), n)
     a.weight, a.bias, a.eps = w.data_ptr(), bb.data_ptr(), float(eps)
     a.out, a.ldo = out.data_ptr(), out.stride(0)
+    if bf16_copy is not None:
+        assert bf16_copy.dtype == torch.bfloat16 and bf16_copy.stride(-1) == 1 and bf16_copy.shape[0] == m
+        a.out_bf16, a.ld_bf16 = bf16_copy.data_ptr(), bf16_copy.stride(0)
     _launch("m2_add_layernorm_fwd", a2d, _lib.lib().m2_add_layernorm_fwd, C.byref(a))
     return out
 

@@ -35,6 +35,27 @@ class _AugmentedLinear:
         return self.w
 
 
+def make_augmented(m_rows, d, device):
+    """(m_rows, d + _PAD) bf16 buffer whose extra columns are [1, 0, 0, ...]; the first d
+    columns are left for the caller to fill."""
+    buf = torch.empty((m_rows, d + _PAD), dtype=torch.bfloat16, device=device)
+    buf[:, d] = 1.0
+    buf[:, d + 1:] = 0.0
+    return buf
+
+
+def augmented_input(u):
+    """bf16 copy of u with the bias column appended: reuses the copy a preceding m2_b200
+    LayerNorm left on the tensor (attribute `_m2_aug`), else casts u."""
+    B, L, D = u.shape
+    aug = getattr(u, "_m2_aug", None)
+    if aug is not None and aug.shape == (B * L, D + _PAD) and aug.device == u.device:
+        return aug.view(B, L, D + _PAD)
+    aug = make_augmented(B * L, D, u.device).view(B, L, D + _PAD)
+    aug[..., :D] = u
+    return aug
+
+
 def _check_forward_only(module, x):
     """The kernels implement the forward pass only; refuse to build an autograd graph
     silently."""
@@ -95,9 +116,7 @@ class MonarchMixerSequenceMixing(nn.Module):
         if not hasattr(self, "_aug_in"):
             self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
         w_in, w_out = self._aug_in.get(self.in_linear), self._aug_out.get(self.out_linear)
-        x_aug = torch.zeros((B, L, D + _PAD), dtype=torch.bfloat16, device=u.device)
-        x_aug[..., :D] = u
-        x_aug[..., D] = 1.0
+        x_aug = augmented_input(u)
         with torch.autocast("cuda", enabled=False):
             xin_t = torch.matmul(w_in, x_aug.transpose(1, 2))                    # (B, 3D, L)
             u_t = ures.transpose(1, 2).contiguous() if ures is not None else None
@@ -134,7 +153,15 @@ class MonarchMixerSequenceMixing(nn.Module):
         ures = u_orig if self.residual_long_conv else None
         if kind == 2:
             return self._forward_long_rows(u, ures, specs, biases), None
-        xin = self.in_linear(u)                        # bf16 under autocast, float32 otherwise
+        if bf16:
+            # in_linear on the bf16 input with the bias carried as one more input column: the
+            # same single rounding as F.linear under autocast, without per-call weight casts
+            if not hasattr(self, "_aug_in"):
+                self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
+            with torch.autocast("cuda", enabled=False):
+                xin = torch.matmul(augmented_input(u), self._aug_in.get(self.in_linear).t())
+        else:
+            xin = self.in_linear(u)
         y = ops.longconv_fwd(xin, ures, self.short_filter.weight, self.short_filter.bias, specs, biases,
                              kind=kind, bf16_rounding=bf16)
         y = self.out_linear(y)
