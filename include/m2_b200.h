@@ -89,7 +89,7 @@ int m2_hyena_filter(const m2_filter_args* args, void* stream);
  * m2_longconv_kind() names the kernel family used for (seq_len, act_dtype, d_model): 0 = float32
  * arithmetic on CUDA cores (any shape), 1 = tcgen05 tensor cores (bf16, 64 < seq_len <= 128,
  * d_model a multiple of 128, channel-contiguous tensors), 2 = tcgen05 tensor cores for long rows
- * (bf16, 1024 < seq_len <= 2048 or 4096 < seq_len <= 8192, seq_len a multiple of 4; needs
+ * (bf16, seq_len in (1024, 2048], (4096, 8192] or (16384, 32768], a multiple of 4; needs
  * time-contiguous tensors, i.e. xin_st == u_st == out_st == 1);
  * m2_filter_spectrum_floats() is the number of float32 the spectrum of one filter takes.
  * k (device, float32): (d_model, m2_filter_row_len(seq_len)) as written by m2_hyena_filter.

@@ -1,9 +1,10 @@
 // Fused gated long convolution on tcgen05 tensor cores for long rows (kernel family 2):
 // bf16 activations stored time-contiguous ((B, channels, L) layout), transform length
-// N = 32 * N2 * N3 = 4096 (1024 < L <= 2048) or 16384 (4096 < L <= 8192).
+// N = 32 * N2 * N3 = 4096 (1024 < L <= 2048), 16384 (4096 < L <= 8192) or 65536
+// (16384 < L <= 32768).
 //
-// One (batch row, channel) sequence is processed at a time by a "slot" of four warps; a CTA
-// holds several slots that run independently (own barriers, own TMEM columns, own shared-
+// One (batch row, channel) sequence is processed at a time by a "slot" of four warps (sixteen
+// for N = 65536, where one sequence fills the SM); a CTA holds several slots that run independently (own barriers, own TMEM columns, own shared-
 // memory region) so that one slot's loads and stage hand-offs overlap the others' work.
 //
 // The real FFT of length N is evaluated at the odd frequencies k + 1/2 (negacyclic form,
@@ -16,7 +17,8 @@
 //   x T2[n3, k2] = w^{32 n3 k2}, rows -> (k1, k2)
 //   F3  rows (k1, k2):      Z[., k3]    = sum_{n3} W_N3^{n3 k3} B2
 //   x (G + bias), then the three inverse stages in mirror order; I1 yields only the L kept
-//   outputs y[R n1 + r], n1 < 16.
+//   outputs y[R n1 + r], n1 < 16.  The inverse DFT stages reuse the forward matrices on
+//   conjugated data (IDFT(x) = conj DFT(conj x)), so each radix needs one matrix only.
 //
 // Every stage is a batched real GEMM with M = 128 rows per tile taken from inside the
 // sequence itself, fp16 operands in un-swizzled core-matrix shared memory, constant DFT
@@ -28,135 +30,161 @@
 // Computation replaced: bert/src/mm/monarch_mixer_sequence_mixer.py:109-149 and
 // bert/src/mm/hyena_utils.py:16-42, :219-248 of the reference.
 #include "tc_common.cuh"
+#include <cooperative_groups.h>
 
 namespace m2 {
 namespace lcl {
 
 constexpr float S1 = 0.25f;
 __host__ __device__ constexpr float stage_scale(int n) {   // 2^-ceil(log2(n)/2)
-  return n >= 64 ? 0.125f : n >= 32 ? 0.125f : n >= 16 ? 0.25f : n >= 8 ? 0.25f : 0.5f;
+  return n >= 32 ? 0.125f : n >= 8 ? 0.25f : 0.5f;
 }
+__host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
-template <int N2_, int N3_>
+// N2, N3: radices of the second and third stage (the first is 32); SLOTS: independent
+// sequences in flight per CTA; TS: warps per TMEM lane quarter inside a slot (they split
+// the row tiles of every stage among themselves).
+template <int N2_, int N3_, int SLOTS_, int TS_>
 struct Geo {
-  static constexpr int N2 = N2_, N3 = N3_;
+  static constexpr int N2 = N2_, N3 = N3_, SLOTS = SLOTS_, TS = TS_;
   static constexpr int R = N2 * N3;             // rows of stage 1 = N / 32
   static constexpr int N = 32 * R;
+  static constexpr int LG = (N == 4096) ? 12 : (N == 16384) ? 14 : 16;
   static constexpr int K2 = 2 * N2, K3 = 2 * N3;
-  static constexpr int TR = R / 128;            // row tiles of F1 / I1
-  static constexpr int T2T = 16 * N3 / 128;     // row tiles of F2 / I2
-  static constexpr int T3T = 16 * N2 / 128;     // row tiles of F3 / I3
-  static constexpr int DATA_BYTES = 64 * R;     // half spectrum as fp16 complex = every stage's operand set
-  static constexpr int COLS = (TR * 32 > T2T * K2 ? (TR * 32 > T3T * K3 ? TR * 32 : T3T * K3)
-                                                  : (T2T * K2 > T3T * K3 ? T2T * K2 : T3T * K3));
-  static constexpr int SLOTS = (R >= 512) ? 4 : 4;
+  static constexpr int TR = R / 128;            // row tiles of the first / last stage
+  static constexpr int T2T = 16 * N3 / 128;     // row tiles of the DFT_N2 stages
+  static constexpr int T3T = 16 * N2 / 128;     // row tiles of the DFT_N3 stages
+  static constexpr int G2 = N2 / 8, G3 = N3 / 8;             // 8-row groups per k1
+  static constexpr int TPS = 128 * TS;          // threads per slot
+  static constexpr int THREADS = SLOTS * TPS;
+  static constexpr bool SPLIT_T1 = R > 512;     // twiddle table of stage 1 as a product of two small ones
+  // operand layouts: core matrices of 8 rows x 16 bytes; LBO = stride between K chunks,
+  // SBO = stride between 8-row groups, TILE = 128 rows.  The padded strides spread the
+  // scattered 4-byte stores of the re-layout steps over the shared-memory banks.
+  static constexpr int A1_LBO = 128, A1_SBO = 2 * 128 + 16, A1_TILE = 16 * A1_SBO;            // K = 16
+  static constexpr int A2_LBO = 144, A2_SBO = (K2 / 8) * 144, A2_TILE = 16 * A2_SBO;          // K = K2
+  static constexpr int A3_LBO = 144, A3_SBO = (K3 / 8) * 144 + 16, A3_TILE = 16 * A3_SBO;     // K = K3
+  static constexpr int A6_LBO = 128, A6_SBO = 4 * 128, A6_TILE = 16 * A6_SBO;                 // K = 32
+  static constexpr int DATA_BYTES =
+      ((cmax(cmax(TR * A1_TILE, T2T * A2_TILE), cmax(cmax(T3T * A3_TILE, TR * A6_TILE), 64 * R)) + 127) / 128) * 128;
+  static constexpr int COLS = cmax(TR * 32, cmax(T2T * K2, T3T * K3));
   static constexpr int TCOLS = (SLOTS * COLS <= 32) ? 32 : (SLOTS * COLS <= 64) ? 64 : (SLOTS * COLS <= 128) ? 128
                                : (SLOTS * COLS <= 256) ? 256 : 512;
   static constexpr float S2 = stage_scale(N2), S3 = stage_scale(N3);
   static constexpr float KAPPA = (2.0f / N) / ((S1 * S2 * S3) * (S1 * S2 * S3));
-  // header of the spectrum table (bytes): constant matrices and twiddle tables
+  // header of the spectrum table (bytes): constant matrices (un-padded core-matrix layout)
+  // and twiddle tables
   static constexpr int F1_OFF = 0;                       // [32 x 16]
   static constexpr int I1_OFF = F1_OFF + 1024;           // [16 x 32]
   static constexpr int F2_OFF = I1_OFF + 1024;           // [K2 x K2]
-  static constexpr int I2_OFF = F2_OFF + K2 * K2 * 2;
-  static constexpr int F3_OFF = I2_OFF + K2 * K2 * 2;    // [K3 x K3]
-  static constexpr int I3_OFF = F3_OFF + K3 * K3 * 2;
-  static constexpr int T1_OFF = I3_OFF + K3 * K3 * 2;    // half2 [16][R]
-  static constexpr int T2A_OFF = T1_OFF + 64 * R;        // half2 [N2][N3]  (k2 major)
+  static constexpr int F3_OFF = F2_OFF + K2 * K2 * 2;    // [K3 x K3]
+  static constexpr int T1_OFF = F3_OFF + K3 * K3 * 2;    // half2 [16][R], or [16][N2] then [16][N3] when split
+  static constexpr int T1_BYTES = SPLIT_T1 ? 64 * (N2 + N3) : 64 * R;
+  static constexpr int T2A_OFF = T1_OFF + T1_BYTES;      // half2 [N2][N3]  (k2 major)
   static constexpr int T2B_OFF = T2A_OFF + 4 * R;        // half2 [N3][N2]  (n3 major)
   static constexpr int HDR_BYTES = T2B_OFF + 4 * R;
   static constexpr int HDR_FLOATS = HDR_BYTES / 4;
-  static constexpr int THREADS = SLOTS * 128;
-  static constexpr int SMEM = SLOTS * DATA_BYTES + HDR_BYTES + 16 * SLOTS * 8 + 64 + 128;
+  static constexpr int SMEM = SLOTS * DATA_BYTES + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
   static_assert(R % 128 == 0 && (16 * N3) % 128 == 0 && (16 * N2) % 128 == 0, "row tiles must be full");
   static_assert(SLOTS * COLS <= 512, "accumulators exceed tensor memory");
+  static_assert(TR % TS == 0 && T2T % TS == 0 && T3T % TS == 0, "tile split must divide every stage");
+  static_assert((R / 4) % TPS == 0 || TPS % (R / 4) == 0, "load mapping");
+  static_assert(SMEM <= 227 * 1024, "shared memory");
 };
 
-// byte offset of element (row, k) in a K-major un-swizzled tile set with K columns:
-// 128-row tiles, 8-row groups of K/8 core matrices, 16 bytes per row of a core matrix
+// byte offset of element (row, k) of a constant matrix with K columns (un-padded layout)
 template <int K>
-__host__ __device__ constexpr int op_off(int row, int k) {
-  return (row >> 7) * (128 * K * 2) + ((row & 127) >> 3) * (K * 16) + (k >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2;
+__host__ __device__ constexpr int mat_off(int row, int k) {
+  return (row >> 3) * (K * 16) + (k >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2;
 }
 
 // ---------------------------------------------------------------------------------------
 // Spectrum table (kind 2): [HDR_FLOATS floats: matrices + twiddles] then per channel
-// G[(k1 N2 + k2)][k3] as half2, multiplied by KAPPA.  Built with an N-point complex FFT in
-// shared memory of g[n] w^{n/2} (g = the filter with its wrapped half negated).
+// G[(k1 N2 + k2)][k3] as half2, multiplied by KAPPA.
 // ---------------------------------------------------------------------------------------
 template <typename G>
-__global__ void __launch_bounds__(512)
-spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D) {
+__device__ void write_header(float* spec, int tid, int nt) {
   constexpr int N = G::N, N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  const int tid = threadIdx.x, nt = blockDim.x;
-  if (blockIdx.x == (unsigned)D) {
-    __half* m = reinterpret_cast<__half*>(spec);
-    for (int idx = tid; idx < 16 * 16; idx += nt) {            // F1 rows 2k1+ri, I1 columns 2k1+ri
-      const int k1 = idx / 16, n1 = idx % 16;
+  __half* m = reinterpret_cast<__half*>(spec);
+  for (int idx = tid; idx < 16 * 16; idx += nt) {
+    // F1 rows 2k1+ri: W32^{n1 (k1+1/2)}.  I1 columns 2k1+ri act on the CONJUGATE of the last
+    // inverse stage's input: y = sum cos * Qr + sin * Qi.
+    const int k1 = idx / 16, n1 = idx % 16;
+    double sn, cs;
+    sincospi(2.0 * n1 * (k1 + 0.5) / 32.0, &sn, &cs);
+    m[(G::F1_OFF + mat_off<16>(2 * k1, n1)) / 2] = __double2half(S1 * cs);
+    m[(G::F1_OFF + mat_off<16>(2 * k1 + 1, n1)) / 2] = __double2half(-S1 * sn);
+    m[(G::I1_OFF + mat_off<32>(n1, 2 * k1)) / 2] = __double2half(S1 * cs);
+    m[(G::I1_OFF + mat_off<32>(n1, 2 * k1 + 1)) / 2] = __double2half(S1 * sn);
+  }
+  for (int idx = tid; idx < N2 * N2; idx += nt) {            // forward DFT_N2 in real form
+    const int ko = idx / N2, ni = idx % N2;
+    double sn, cs;
+    sincospi(2.0 * ((ko * ni) % N2) / N2, &sn, &cs);
+    const double c = G::S2 * cs, s = G::S2 * sn;             // w = c - i s
+    __half* f = m + G::F2_OFF / 2;
+    f[mat_off<K2>(2 * ko, 2 * ni) / 2] = __double2half(c);
+    f[mat_off<K2>(2 * ko, 2 * ni + 1) / 2] = __double2half(s);
+    f[mat_off<K2>(2 * ko + 1, 2 * ni) / 2] = __double2half(-s);
+    f[mat_off<K2>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
+  }
+  for (int idx = tid; idx < N3 * N3; idx += nt) {            // forward DFT_N3
+    const int ko = idx / N3, ni = idx % N3;
+    double sn, cs;
+    sincospi(2.0 * ((ko * ni) % N3) / N3, &sn, &cs);
+    const double c = G::S3 * cs, s = G::S3 * sn;
+    __half* f = m + G::F3_OFF / 2;
+    f[mat_off<K3>(2 * ko, 2 * ni) / 2] = __double2half(c);
+    f[mat_off<K3>(2 * ko, 2 * ni + 1) / 2] = __double2half(s);
+    f[mat_off<K3>(2 * ko + 1, 2 * ni) / 2] = __double2half(-s);
+    f[mat_off<K3>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
+  }
+  __half2* t1 = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T1_OFF);
+  if (G::SPLIT_T1) {
+    for (int idx = tid; idx < 16 * N2; idx += nt) {          // Ta[k1][n2] = w^{N3 n2 (k1 + 1/2)}
+      const int k1 = idx / N2, n2 = idx % N2;
       double sn, cs;
-      sincospi(2.0 * n1 * (k1 + 0.5) / 32.0, &sn, &cs);
-      m[(G::F1_OFF + op_off<16>(2 * k1, n1)) / 2] = __double2half(S1 * cs);
-      m[(G::F1_OFF + op_off<16>(2 * k1 + 1, n1)) / 2] = __double2half(-S1 * sn);
-      m[(G::I1_OFF + op_off<32>(n1, 2 * k1)) / 2] = __double2half(S1 * cs);
-      m[(G::I1_OFF + op_off<32>(n1, 2 * k1 + 1)) / 2] = __double2half(-S1 * sn);
+      sincospi(2.0 * N3 * n2 * (k1 + 0.5) / N, &sn, &cs);
+      t1[idx] = __floats2half2_rn((float)cs, (float)(-sn));
     }
-    for (int idx = tid; idx < N2 * N2; idx += nt) {            // DFT_N2, forward and inverse, real form
-      const int ko = idx / N2, ni = idx % N2;
+    for (int idx = tid; idx < 16 * N3; idx += nt) {          // Tb[k1][n3] = w^{n3 (k1 + 1/2)}
+      const int k1 = idx / N3, n3 = idx % N3;
       double sn, cs;
-      sincospi(2.0 * ((ko * ni) % N2) / N2, &sn, &cs);
-      const double c = G::S2 * cs, s = G::S2 * sn;             // forward w = c - i s, inverse w = c + i s
-      __half* f = m + G::F2_OFF / 2;
-      f[op_off<K2>(2 * ko, 2 * ni) / 2] = __double2half(c);
-      f[op_off<K2>(2 * ko, 2 * ni + 1) / 2] = __double2half(s);
-      f[op_off<K2>(2 * ko + 1, 2 * ni) / 2] = __double2half(-s);
-      f[op_off<K2>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
-      __half* g = m + G::I2_OFF / 2;
-      g[op_off<K2>(2 * ko, 2 * ni) / 2] = __double2half(c);
-      g[op_off<K2>(2 * ko, 2 * ni + 1) / 2] = __double2half(-s);
-      g[op_off<K2>(2 * ko + 1, 2 * ni) / 2] = __double2half(s);
-      g[op_off<K2>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
+      sincospi(2.0 * n3 * (k1 + 0.5) / N, &sn, &cs);
+      t1[16 * N2 + idx] = __floats2half2_rn((float)cs, (float)(-sn));
     }
-    for (int idx = tid; idx < N3 * N3; idx += nt) {            // DFT_N3
-      const int ko = idx / N3, ni = idx % N3;
-      double sn, cs;
-      sincospi(2.0 * ((ko * ni) % N3) / N3, &sn, &cs);
-      const double c = G::S3 * cs, s = G::S3 * sn;
-      __half* f = m + G::F3_OFF / 2;
-      f[op_off<K3>(2 * ko, 2 * ni) / 2] = __double2half(c);
-      f[op_off<K3>(2 * ko, 2 * ni + 1) / 2] = __double2half(s);
-      f[op_off<K3>(2 * ko + 1, 2 * ni) / 2] = __double2half(-s);
-      f[op_off<K3>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
-      __half* g = m + G::I3_OFF / 2;
-      g[op_off<K3>(2 * ko, 2 * ni) / 2] = __double2half(c);
-      g[op_off<K3>(2 * ko, 2 * ni + 1) / 2] = __double2half(-s);
-      g[op_off<K3>(2 * ko + 1, 2 * ni) / 2] = __double2half(s);
-      g[op_off<K3>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
-    }
-    __half2* t1 = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T1_OFF);
-    for (int idx = tid; idx < 16 * R; idx += nt) {             // T1[k1][r] = w^{r (k1 + 1/2)}
+  } else {
+    for (int idx = tid; idx < 16 * R; idx += nt) {           // T1[k1][r] = w^{r (k1 + 1/2)}
       const int k1 = idx / R, r = idx % R;
       double sn, cs;
       sincospi(2.0 * r * (k1 + 0.5) / N, &sn, &cs);
       t1[idx] = __floats2half2_rn((float)cs, (float)(-sn));
     }
-    __half2* t2a = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T2A_OFF);
-    __half2* t2b = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T2B_OFF);
-    for (int idx = tid; idx < R; idx += nt) {                  // T2 = w^{32 n3 k2} in both index orders
-      const int k2 = idx / N3, n3 = idx % N3;
-      double sn, cs;
-      sincospi(2.0 * 32.0 * n3 * k2 / N, &sn, &cs);
-      const __half2 v = __floats2half2_rn((float)cs, (float)(-sn));
-      t2a[k2 * N3 + n3] = v;
-      t2b[n3 * N2 + k2] = v;
-    }
-    return;
   }
-  // ---- one channel: N-point complex FFT (decimation in frequency) of g[n] w^{n/2} ----
+  __half2* t2a = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T2A_OFF);
+  __half2* t2b = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T2B_OFF);
+  for (int idx = tid; idx < R; idx += nt) {                  // T2 = w^{32 n3 k2} in both index orders
+    const int k2 = idx / N3, n3 = idx % N3;
+    double sn, cs;
+    sincospi(2.0 * 32.0 * n3 * k2 / N, &sn, &cs);
+    const __half2 v = __floats2half2_rn((float)cs, (float)(-sn));
+    t2a[k2 * N3 + n3] = v;
+    t2b[n3 * N2 + k2] = v;
+  }
+}
+
+// One CTA per channel: N-point complex FFT (decimation in frequency) in shared memory of
+// g[n] w^{n/2}, g = the filter with its wrapped half negated; bins gathered in table order.
+template <typename G>
+__global__ void __launch_bounds__(512)
+spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D) {
+  constexpr int N = G::N, N2 = G::N2, N3 = G::N3;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  if (blockIdx.x == (unsigned)D) { write_header<G>(spec, tid, nt); return; }
   float2* s = reinterpret_cast<float2*>(smem_raw);
   const int c = blockIdx.x;
   const float* row = kfilt + (size_t)c * N;
-  constexpr int lg = (N == 4096) ? 12 : (N == 16384) ? 14 : 16;
   for (int n = tid; n < N; n += nt) {
     double sn, cs;
     sincospi((double)n / N, &sn, &cs);                         // w^{n/2} = cos(pi n / N) - i sin(pi n / N)
@@ -181,9 +209,94 @@ spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
   for (int idx = tid; idx < N / 2; idx += nt) {
     const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
     const int k = k1 + 32 * k2 + 32 * N2 * k3;
-    const int p = (int)(__brev((unsigned)k) >> (32 - lg));
+    const int p = (int)(__brev((unsigned)k) >> (32 - G::LG));
     Gt[idx] = __floats2half2_rn(s[p].x * G::KAPPA, s[p].y * G::KAPPA);
   }
+}
+
+// N = 65536: the transform no longer fits one CTA.  The real filter is packed as
+// z[m] = g[2m] + i g[2m+1] (M = N/2 points), transformed at odd frequencies by a cluster of
+// two CTAs (each holds half of the M points; only the first decimation-in-frequency stage
+// crosses halves and it reads its inputs straight from global memory), and un-packed with
+//   E[k] = (Z[k] + conj Z[M-1-k]) / 2,  O[k] = (Z[k] - conj Z[M-1-k]) / 2i,
+//   G[k] = E[k] + w^{k+1/2} O[k],   G[k+M] = E[k] - w^{k+1/2} O[k],
+// where the partner bin M-1-k always lives in the other CTA (read through distributed
+// shared memory).
+template <typename G>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512)
+spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D) {
+  namespace cg = cooperative_groups;
+  constexpr int N = G::N, M = N / 2, Mh = M / 2, N2 = G::N2, N3 = G::N3, LGM = G::LG - 1;
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float2* s = reinterpret_cast<float2*>(smem_raw);            // local half: positions q*Mh + [0, Mh)
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int q = (int)cluster.block_rank();
+  const int c = blockIdx.x >> 1;
+  if (c == D) {
+    if (q == 0) write_header<G>(spec, tid, nt);
+    cluster.sync();
+    cluster.sync();
+    return;
+  }
+  const float* row = kfilt + (size_t)c * N;
+  // packed, pre-twisted input x[m] = z[m] W_M^{m/2}; first stage pairs m and m + Mh
+  for (int i = tid; i < Mh; i += nt) {
+    float2 x[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int m = i + e * Mh;
+      const double sg = (2 * m < N / 2) ? 1.0 : -1.0;          // wrapped half of the filter negated
+      const double zr = sg * (double)row[2 * m], zi = sg * (double)row[2 * m + 1];
+      double sn, cs;
+      sincospi((double)m / M, &sn, &cs);                       // W_M^{m/2} = cos(pi m / M) - i sin(pi m / M)
+      x[e] = make_float2((float)(zr * cs + zi * sn), (float)(zi * cs - zr * sn));
+    }
+    if (q == 0) {
+      s[i] = make_float2(x[0].x + x[1].x, x[0].y + x[1].y);
+    } else {
+      float sn, cs;
+      sincospif((float)i / (float)Mh, &sn, &cs);               // W_M^{i}
+      const float dx = x[0].x - x[1].x, dy = x[0].y - x[1].y;
+      s[i] = make_float2(dx * cs + dy * sn, dy * cs - dx * sn);
+    }
+  }
+  __syncthreads();
+  for (int h = Mh / 2; h >= 1; h >>= 1) {
+    for (int j = tid; j < Mh / 2; j += nt) {
+      const int g = j / h, pos = j % h;
+      float2* base = s + g * 2 * h + pos;
+      float sn, cs;
+      sincospif((float)pos / (float)h, &sn, &cs);
+      const float2 a = base[0], b = base[h];
+      const float dx = a.x - b.x, dy = a.y - b.y;
+      base[0] = make_float2(a.x + b.x, a.y + b.y);
+      base[h] = make_float2(dx * cs + dy * sn, dy * cs - dx * sn);
+    }
+    __syncthreads();
+  }
+  cluster.sync();
+  // bin kappa of the M-point transform sits at global position rev_M(kappa): CTA = kappa & 1
+  const float2* other = cluster.map_shared_rank(s, q ^ 1);
+  __half2* Gt = reinterpret_cast<__half2*>(spec + G::HDR_FLOATS) + (size_t)c * (N / 2);
+  for (int idx = tid; idx < N / 2; idx += nt) {
+    const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
+    const int k = k1 + 32 * k2 + 32 * N2 * k3;
+    const int kap = k & (M - 1);
+    if ((kap & 1) != q) continue;
+    const int pk = (int)(__brev((unsigned)kap) >> (32 - LGM)) - q * Mh;
+    const int pm = (int)(__brev((unsigned)(M - 1 - kap)) >> (32 - LGM)) - (q ^ 1) * Mh;
+    const float2 Zk = s[pk], Zp = other[pm];
+    const float2 E = make_float2(0.5f * (Zk.x + Zp.x), 0.5f * (Zk.y - Zp.y));
+    const float2 O = make_float2(0.5f * (Zk.y + Zp.y), -0.5f * (Zk.x - Zp.x));     // (Zk - conj Zp) / 2i
+    double snd, csd;
+    sincospi(2.0 * (kap + 0.5) / N, &snd, &csd);               // w^{kap + 1/2} = cos - i sin
+    const float cs = (float)csd, sn = (float)snd;
+    const float2 wO = make_float2(O.x * cs + O.y * sn, O.y * cs - O.x * sn);
+    const float sg = (k >= M) ? -1.f : 1.f;
+    Gt[idx] = __floats2half2_rn((E.x + sg * wO.x) * G::KAPPA, (E.y + sg * wO.y) * G::KAPPA);
+  }
+  cluster.sync();
 }
 
 // ---------------------------------------------------------------------------------------
@@ -221,17 +334,9 @@ __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr));
-}
-
-// (a + i b)(c + i d) and (a + i b) conj(c + i d)
 __device__ __forceinline__ float2 cmulf(float2 x, float2 w) { return make_float2(x.x * w.x - x.y * w.y, x.x * w.y + x.y * w.x); }
-__device__ __forceinline__ float2 cmulcf(float2 x, float2 w) { return make_float2(x.x * w.x + x.y * w.y, x.y * w.x - x.x * w.y); }
 
-// depthwise 3-tap conv over 4 consecutive time steps of one channel; in[0..1] = x[t0-2], x[t0-1]
+// depthwise 3-tap conv over 4 consecutive time steps of one channel
 struct Taps { float w0, w1, w2, b; };
 __device__ __forceinline__ Taps load_taps(const float* sw, const float* sb, int ch) {
   Taps T;
@@ -254,6 +359,8 @@ __device__ __forceinline__ void load6(const __nv_bfloat16* row, int t0, int L, f
   x6[2] = bf_lo(v.x); x6[3] = bf_hi(v.x); x6[4] = bf_lo(v.y); x6[5] = bf_hi(v.y);
 }
 
+// MMAs of one stage: 0 F1, 1 DFT_N2, 2 DFT_N3, 3 DFT_N3 (on conjugated data = inverse),
+// 4 DFT_N2 (inverse), 5 I1
 template <typename G>
 __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t data, uint32_t hdr) {
   constexpr int K2 = G::K2, K3 = G::K3;
@@ -262,32 +369,30 @@ __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t dat
     const uint64_t dB = tc::smem_desc_k_nosw(hdr + G::F1_OFF, 128, 16 * 16);
 #pragma unroll
     for (int t = 0; t < G::TR; ++t)
-      tc::mma_ss(tm + 32 * t, tc::smem_desc_k_nosw(data + t * 4096, 128, 16 * 16), dB, id, 0);
+      tc::mma_ss(tm + 32 * t, tc::smem_desc_k_nosw(data + t * G::A1_TILE, G::A1_LBO, G::A1_SBO), dB, id, 0);
   } else if (stage == 1 || stage == 4) {
     constexpr uint32_t id = tc::make_idesc(128, K2, 0);
-    const uint32_t mb = hdr + (stage == 1 ? G::F2_OFF : G::I2_OFF);
 #pragma unroll
     for (int t = 0; t < G::T2T; ++t)
 #pragma unroll
       for (int s = 0; s < K2 / 16; ++s)
-        tc::mma_ss(tm + K2 * t, tc::smem_desc_k_nosw(data + t * (128 * K2 * 2) + s * 256, 128, K2 * 16),
-                   tc::smem_desc_k_nosw(mb + s * 256, 128, K2 * 16), id, s ? 1u : 0u);
+        tc::mma_ss(tm + K2 * t, tc::smem_desc_k_nosw(data + t * G::A2_TILE + s * 2 * G::A2_LBO, G::A2_LBO, G::A2_SBO),
+                   tc::smem_desc_k_nosw(hdr + G::F2_OFF + s * 256, 128, K2 * 16), id, s ? 1u : 0u);
   } else if (stage == 2 || stage == 3) {
     constexpr uint32_t id = tc::make_idesc(128, K3, 0);
-    const uint32_t mb = hdr + (stage == 2 ? G::F3_OFF : G::I3_OFF);
 #pragma unroll
     for (int t = 0; t < G::T3T; ++t)
 #pragma unroll
       for (int s = 0; s < K3 / 16; ++s)
-        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * (128 * K3 * 2) + s * 256, 128, K3 * 16),
-                   tc::smem_desc_k_nosw(mb + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
+        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * G::A3_TILE + s * 2 * G::A3_LBO, G::A3_LBO, G::A3_SBO),
+                   tc::smem_desc_k_nosw(hdr + G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
   } else {
     constexpr uint32_t id = tc::make_idesc(128, 16, 0);
 #pragma unroll
     for (int t = 0; t < G::TR; ++t)
 #pragma unroll
       for (int s = 0; s < 2; ++s)
-        tc::mma_ss(tm + 16 * t, tc::smem_desc_k_nosw(data + t * 8192 + s * 256, 128, 32 * 16),
+        tc::mma_ss(tm + 16 * t, tc::smem_desc_k_nosw(data + t * G::A6_TILE + s * 2 * G::A6_LBO, G::A6_LBO, G::A6_SBO),
                    tc::smem_desc_k_nosw(hdr + G::I1_OFF + s * 256, 128, 32 * 16), id, s ? 1u : 0u);
   }
 }
@@ -295,12 +400,12 @@ __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t dat
 template <typename G, typename TU>
 __global__ void __launch_bounds__(G::THREADS, 1)
 longconv_tcl_kernel(const Params P) {
-  constexpr int N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3;
-  constexpr int CH = R / 4;                      // 4-wide time chunks per n1 block
-  constexpr int GROUPS = (128 * 4) / R > 0 ? (128 * 4) / R : 1;   // n1 groups when R < 512
-  constexpr int NP = 16 / GROUPS;                // n1 values per thread in the load / store phases
-  constexpr int CPT = (CH * GROUPS) / 128;       // chunks per thread (1 unless R > 512)
-  static_assert(CPT == 1, "this kernel covers R <= 512");
+  constexpr int N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3, TS = G::TS, TPS = G::TPS;
+  constexpr int CH = R / 4;                                  // 4-wide time chunks per n1 block
+  constexpr int GROUPS = (TPS > CH) ? TPS / CH : 1;          // n1 groups when a slot has more threads than chunks
+  constexpr int NP = 16 / GROUPS;                            // n1 values per thread and chunk in the load / store phases
+  constexpr int CPT = (CH > TPS) ? CH / TPS : 1;             // chunks per thread
+  static_assert(NP >= 4 && NP % 4 == 0, "n1 group must be a multiple of 4");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
   unsigned char* hdrb = smem + G::SLOTS * G::DATA_BYTES;
@@ -309,13 +414,15 @@ longconv_tcl_kernel(const Params P) {
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int slot = warp >> 2;
-  const int l = (warp & 3) * 32 + lane;          // TMEM lane = row within every 128-row tile
+  const int slot = tid / TPS;
+  const int sl = tid % TPS;                      // thread index inside the slot
+  const int l = sl & 127;                        // TMEM lane = row within every 128-row tile
+  const int ts = sl >> 7;                        // which share of the row tiles this thread handles
   if (tid == 0) {
     for (int s = 0; s < G::SLOTS; ++s) {
-      tc::mbar_init(bars + 3 * s, 128);
+      tc::mbar_init(bars + 3 * s, TPS);
       tc::mbar_init(bars + 3 * s + 1, 1);
-      tc::mbar_init(bars + 3 * s + 2, 128);
+      tc::mbar_init(bars + 3 * s + 2, TPS);
     }
     *abort_flag = 0;
     tc::mbar_fence_init();
@@ -342,16 +449,14 @@ longconv_tcl_kernel(const Params P) {
   float* Y = reinterpret_cast<float*>(smem + slot * G::DATA_BYTES);
   const uint32_t hdr = tc::smem_u32(hdrb);
   const uint32_t t1s = hdr + G::T1_OFF, t2a = hdr + G::T2A_OFF, t2b = hdr + G::T2B_OFF;
-  // load / store phase mapping: chunk of 4 consecutive r, NP consecutive n1
-  const int pc = l % CH, pg = l / CH;
-  const int r0 = 4 * pc, n1_0 = pg * NP;
+  const uint32_t lrow = (uint32_t)((l >> 3) * 1 /* x SBO */), lsub = (uint32_t)((l & 7) * 16);
   uint32_t ph_ops = 0, ph_mma = 0, ph_w = 0;
   bool ok = true;
 
 #define LCL_STAGE(stage_)                                                                             \
   tc::fence_proxy_async_smem();                                                                       \
   tc::mbar_arrive(bar_ops);                                                                           \
-  if (l == 0) {                                                                                       \
+  if (sl == 0) {                                                                                      \
     if (tc::mbar_wait(bar_ops, ph_ops, abort_flag, tc::ST_TIMEOUT_MMA)) {                             \
       tc::tc_fence_after();                                                                           \
       issue_stage<G>(stage_, tm, data, hdr);                                                          \
@@ -377,7 +482,10 @@ longconv_tcl_kernel(const Params P) {
 
     for (int f = 0; f < P.nf && ok; ++f) {
       // ---------------- F1 operands: a[R n1 + r] as fp16 at (row r, k = n1) ----------------
-      {
+#pragma unroll 1
+      for (int cc = 0; cc < CPT; ++cc) {
+        const int pc = (sl % CH) + cc * TPS, pg = (CH >= TPS) ? 0 : sl / CH;
+        const int r0 = 4 * pc, n1_0 = pg * NP;
         uint32_t hv[4][NP / 2];                              // [j = r - r0][n1 pair]
         if (f == 0) {
           const Taps Tx = load_taps(P.sw, P.sb, ch), Tv = load_taps(P.sw, P.sb, 2 * P.D + ch);
@@ -421,17 +529,25 @@ longconv_tcl_kernel(const Params P) {
           }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 4; ++j) {
+          const int r = r0 + j;
+          const uint32_t ro = data + (r >> 7) * G::A1_TILE + ((r & 127) >> 3) * G::A1_SBO + (r & 7) * 16;
 #pragma unroll
-          for (int q = 0; q < NP / 4; ++q)
-            sts64(data + op_off<16>(r0 + j, n1_0 + 4 * q), hv[j][2 * q], hv[j][2 * q + 1]);
+          for (int q = 0; q < NP / 4; ++q) {
+            const int k = n1_0 + 4 * q;
+            sts64(ro + (k >> 3) * G::A1_LBO + (k & 7) * 2, hv[j][2 * q], hv[j][2 * q + 1]);
+          }
+        }
       }
       LCL_STAGE(0)
 
       // ---------------- hop 1: x T1, rows (n2, n3) -> rows (k1, n3), k = (n2, ri) ----------------
 #pragma unroll 1
-      for (int t = 0; t < G::TR; ++t) {
+      for (int t = ts; t < G::TR; t += TS) {
         const int r = 128 * t + l, n2 = r / N3, n3 = r % N3;
+        // thread part of the destination: row group / row of n3, K position of n2
+        const uint32_t dst = data + (n3 >> 3) * G::A2_SBO + (n3 & 7) * 16 + (n2 >> 2) * G::A2_LBO + (n2 & 3) * 4;
+        const uint32_t tw = G::SPLIT_T1 ? 0u : t1s + r * 4;
 #pragma unroll
         for (int hq = 0; hq < 2; ++hq) {
           uint32_t z[16];
@@ -439,10 +555,13 @@ longconv_tcl_kernel(const Params P) {
           tc::tmem_ld_wait();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
+            constexpr int KPT = 128 / N3;                    // k1 values per 128-row tile of the destination
             const int k1 = 8 * hq + kk;
-            const float2 w = unpack_h2(lds32(t1s + (k1 * R + r) * 4));
+            float2 w;
+            if (G::SPLIT_T1) w = cmulf(unpack_h2(lds32(t1s + (k1 * N2 + n2) * 4)), unpack_h2(lds32(t1s + (16 * N2 + k1 * N3 + n3) * 4)));
+            else w = unpack_h2(lds32(tw + k1 * R * 4));
             const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(data + op_off<K2>(k1 * N3 + n3, 2 * n2), pack_h2(y.x, y.y));
+            sts32(dst + (k1 / KPT) * G::A2_TILE + (k1 % KPT) * G::G3 * G::A2_SBO, pack_h2(y.x, y.y));
           }
         }
       }
@@ -451,9 +570,13 @@ longconv_tcl_kernel(const Params P) {
 
       // ---------------- hop 2: x T2, rows (k1, n3) -> rows (k1, k2), k = (n3, ri) ----------------
 #pragma unroll 1
-      for (int t = 0; t < G::T2T; ++t) {
+      for (int t = ts; t < G::T2T; t += TS) {
+        constexpr int KPT = 128 / N2 > 0 ? 128 / N2 : 1;     // k1 values per 128-row tile of the destination (N2 <= 128)
         const int rho = 128 * t + l, k1 = rho / N3, n3 = rho % N3;
-#pragma unroll 1
+        const uint32_t dst = data + (k1 / KPT) * G::A3_TILE + (k1 % KPT) * G::G2 * G::A3_SBO +
+                             (n3 >> 2) * G::A3_LBO + (n3 & 3) * 4;
+        const uint32_t tw = t2a + n3 * 4;
+#pragma unroll
         for (int c0 = 0; c0 < K2; c0 += 16) {
           uint32_t z[16];
           tc::tmem_ld16(tml + K2 * t + c0, z);
@@ -461,23 +584,24 @@ longconv_tcl_kernel(const Params P) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const int k2 = c0 / 2 + kk;
-            const float2 w = unpack_h2(lds32(t2a + (k2 * N3 + n3) * 4));
+            const float2 w = unpack_h2(lds32(tw + k2 * N3 * 4));
             const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(data + op_off<K3>(k1 * N2 + k2, 2 * n3), pack_h2(y.x, y.y));
+            sts32(dst + (k2 >> 3) * G::A3_SBO + (k2 & 7) * 16, pack_h2(y.x, y.y));
           }
         }
       }
       tc::tc_fence_before();
       LCL_STAGE(2)
 
-      // ---------------- hop 3: x (G + bias); rows (k1, k2) keep their place, k = (k3, ri) ----------------
+      // ---------------- hop 3: conj(Z (G + bias)); rows (k1, k2) keep their place, k = (k3, ri) ----------------
       {
         const uint32_t* Gt = reinterpret_cast<const uint32_t*>(P.spec[f] + G::HDR_FLOATS) + (size_t)ch * (G::N / 2);
         const float bk = __ldg(P.bias[f] + ch) * G::KAPPA;
 #pragma unroll 1
-        for (int t = 0; t < G::T3T; ++t) {
+        for (int t = ts; t < G::T3T; t += TS) {
           const int rho = 128 * t + l;
-#pragma unroll 1
+          const uint32_t dst = data + t * G::A3_TILE + (l >> 3) * G::A3_SBO + (l & 7) * 16;
+#pragma unroll
           for (int c0 = 0; c0 < K3; c0 += 16) {
             uint32_t z[16];
             tc::tmem_ld16(tml + K3 * t + c0, z);
@@ -491,21 +615,25 @@ longconv_tcl_kernel(const Params P) {
               float2 g = unpack_h2(gw[kk]);
               g.x += bk;
               const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), g);
-              o[kk] = pack_h2(y.x, y.y);
+              o[kk] = pack_h2(y.x, -y.y);
             }
-            sts128(data + op_off<K3>(rho, c0), o[0], o[1], o[2], o[3]);
-            sts128(data + op_off<K3>(rho, c0 + 8), o[4], o[5], o[6], o[7]);
+            sts128(dst + (c0 >> 3) * G::A3_LBO, o[0], o[1], o[2], o[3]);
+            sts128(dst + ((c0 >> 3) + 1) * G::A3_LBO, o[4], o[5], o[6], o[7]);
           }
         }
       }
       tc::tc_fence_before();
       LCL_STAGE(3)
 
-      // ---------------- hop 4: x conj T2, rows (k1, k2) -> rows (k1, n3), k = (k2, ri) ----------------
+      // ---------------- hop 4: x T2, rows (k1, k2) -> rows (k1, n3), k = (k2, ri) ----------------
 #pragma unroll 1
-      for (int t = 0; t < G::T3T; ++t) {
+      for (int t = ts; t < G::T3T; t += TS) {
+        constexpr int KPT = 128 / N3;
         const int rho = 128 * t + l, k1 = rho / N2, k2 = rho % N2;
-#pragma unroll 1
+        const uint32_t dst = data + (k1 / KPT) * G::A2_TILE + (k1 % KPT) * G::G3 * G::A2_SBO +
+                             (k2 >> 2) * G::A2_LBO + (k2 & 3) * 4;
+        const uint32_t tw = t2b + k2 * 4;
+#pragma unroll
         for (int c0 = 0; c0 < K3; c0 += 16) {
           uint32_t z[16];
           tc::tmem_ld16(tml + K3 * t + c0, z);
@@ -513,20 +641,25 @@ longconv_tcl_kernel(const Params P) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const int n3 = c0 / 2 + kk;
-            const float2 w = unpack_h2(lds32(t2b + (n3 * N2 + k2) * 4));
-            const float2 y = cmulcf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(data + op_off<K2>(k1 * N3 + n3, 2 * k2), pack_h2(y.x, y.y));
+            const float2 w = unpack_h2(lds32(tw + n3 * N2 * 4));
+            const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
+            sts32(dst + (n3 >> 3) * G::A2_SBO + (n3 & 7) * 16, pack_h2(y.x, y.y));
           }
         }
       }
       tc::tc_fence_before();
       LCL_STAGE(4)
 
-      // ---------------- hop 5: x conj T1, rows (k1, n3) -> rows r = (n2, n3), k = (k1, ri) ----------------
+      // ---------------- hop 5: x T1, rows (k1, n3) -> rows r = (n2, n3), k = (k1, ri) ----------------
 #pragma unroll 1
-      for (int t = 0; t < G::T2T; ++t) {
+      for (int t = ts; t < G::T2T; t += TS) {
+        constexpr int NPT = 128 / N3;                        // n2 values per 128-row tile of the destination
         const int rho = 128 * t + l, k1 = rho / N3, n3 = rho % N3;
-#pragma unroll 1
+        const uint32_t dst = data + (n3 >> 3) * G::A6_SBO + (n3 & 7) * 16 + (k1 >> 2) * G::A6_LBO + (k1 & 3) * 4;
+        const uint32_t tw = G::SPLIT_T1 ? t1s + (k1 * N2) * 4 : t1s + (k1 * R + n3) * 4;
+        float2 wb = make_float2(1.f, 0.f);
+        if (G::SPLIT_T1) wb = unpack_h2(lds32(t1s + (16 * N2 + k1 * N3 + n3) * 4));
+#pragma unroll
         for (int c0 = 0; c0 < K2; c0 += 16) {
           uint32_t z[16];
           tc::tmem_ld16(tml + K2 * t + c0, z);
@@ -534,10 +667,11 @@ longconv_tcl_kernel(const Params P) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk) {
             const int n2 = c0 / 2 + kk;
-            const int r = n2 * N3 + n3;
-            const float2 w = unpack_h2(lds32(t1s + (k1 * R + r) * 4));
-            const float2 y = cmulcf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(data + op_off<32>(r, 2 * k1), pack_h2(y.x, y.y));
+            float2 w;
+            if (G::SPLIT_T1) w = cmulf(unpack_h2(lds32(tw + n2 * 4)), wb);
+            else w = unpack_h2(lds32(tw + n2 * N3 * 4));
+            const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
+            sts32(dst + (n2 / NPT) * G::A6_TILE + (n2 % NPT) * G::G3 * G::A6_SBO, pack_h2(y.x, y.y));
           }
         }
       }
@@ -546,7 +680,7 @@ longconv_tcl_kernel(const Params P) {
 
       // ---------------- hop 6: y[R n1 + r] (float32) into shared memory in time order ----------------
 #pragma unroll 1
-      for (int t = 0; t < G::TR; ++t) {
+      for (int t = ts; t < G::TR; t += TS) {
         uint32_t z[16];
         tc::tmem_ld16(tml + 16 * t, z);
         tc::tmem_ld_wait();
@@ -557,38 +691,43 @@ longconv_tcl_kernel(const Params P) {
       LCL_BARRIER()
 
       // ---------------- epilogue: gate / residual add; 8-byte stores along time ----------------
-      if (f == 0) {
-        const Taps T2 = load_taps(P.sw, P.sb, P.D + ch);
+#pragma unroll 1
+      for (int cc = 0; cc < CPT; ++cc) {
+        const int pc = (sl % CH) + cc * TPS, pg = (CH >= TPS) ? 0 : sl / CH;
+        const int r0 = 4 * pc, n1_0 = pg * NP;
+        if (f == 0) {
+          const Taps T2 = load_taps(P.sw, P.sb, P.D + ch);
 #pragma unroll
-        for (int i = 0; i < NP; ++i) {
-          const int t0 = R * (n1_0 + i) + r0;
-          if (t0 < P.L) {
-            float x6[6], c2[4];
-            load6(x2row, t0, P.L, x6);
-            conv4(T2, x6, c2);
-            const float4 y = *reinterpret_cast<const float4*>(Y + t0);
-            const float yv[4] = {y.x, y.y, y.z, y.w};
-            float o[4];
+          for (int i = 0; i < NP; ++i) {
+            const int t0 = R * (n1_0 + i) + r0;
+            if (t0 < P.L) {
+              float x6[6], c2[4];
+              load6(x2row, t0, P.L, x6);
+              conv4(T2, x6, c2);
+              const float4 y = *reinterpret_cast<const float4*>(Y + t0);
+              const float yv[4] = {y.x, y.y, y.z, y.w};
+              float o[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) o[j] = bf16r(yv[j]) * c2[j];      // (conv + bias term) cast, then the gate
-            *reinterpret_cast<uint2*>(orow + t0) = make_uint2(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]));
-          }
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < NP; ++i) {
-          const int t0 = R * (n1_0 + i) + r0;
-          if (t0 < P.L) {
-            const float4 y = *reinterpret_cast<const float4*>(Y + t0);
-            float yv[4] = {y.x, y.y, y.z, y.w};
-            if (sizeof(TU) == 2) {                           // bf16 layer input: yu is cast to bf16 first
-#pragma unroll
-              for (int j = 0; j < 4; ++j) yv[j] = bf16r(yv[j]);
+              for (int j = 0; j < 4; ++j) o[j] = bf16r(yv[j]) * c2[j];      // (conv + bias term) cast, then the gate
+              *reinterpret_cast<uint2*>(orow + t0) = make_uint2(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]));
             }
-            uint2* po = reinterpret_cast<uint2*>(orow + t0);
-            const uint2 prev = *po;                          // y * x2 written by this thread for f == 0
-            *po = make_uint2(pack_bf2(bf_lo(prev.x) + yv[0], bf_hi(prev.x) + yv[1]),
-                             pack_bf2(bf_lo(prev.y) + yv[2], bf_hi(prev.y) + yv[3]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NP; ++i) {
+            const int t0 = R * (n1_0 + i) + r0;
+            if (t0 < P.L) {
+              const float4 y = *reinterpret_cast<const float4*>(Y + t0);
+              float yv[4] = {y.x, y.y, y.z, y.w};
+              if (sizeof(TU) == 2) {                           // bf16 layer input: yu is cast to bf16 first
+#pragma unroll
+                for (int j = 0; j < 4; ++j) yv[j] = bf16r(yv[j]);
+              }
+              uint2* po = reinterpret_cast<uint2*>(orow + t0);
+              const uint2 prev = *po;                          // y * x2 written by this thread for f == 0
+              *po = make_uint2(pack_bf2(bf_lo(prev.x) + yv[0], bf_hi(prev.x) + yv[1]),
+                               pack_bf2(bf_lo(prev.y) + yv[2], bf_hi(prev.y) + yv[3]));
+            }
           }
         }
       }
@@ -597,6 +736,7 @@ longconv_tcl_kernel(const Params P) {
   }
 #undef LCL_STAGE
 #undef LCL_BARRIER
+  (void)lrow; (void)lsub;
 
   __syncthreads();
   if (warp == 0) {
@@ -605,15 +745,23 @@ longconv_tcl_kernel(const Params P) {
   }
 }
 
-using Geo4k = Geo<16, 8>;
-using Geo16k = Geo<32, 16>;
+using Geo4k = Geo<16, 8, 4, 1>;
+using Geo16k = Geo<32, 16, 4, 1>;
+using Geo64k = Geo<64, 32, 1, 4>;
 
 template <typename G>
 static int launch_spectrum(int D, const float* k, float* spec, cudaStream_t st) {
-  auto kern = spectrum_kind2_kernel<G>;
-  const size_t smem = (size_t)G::N * sizeof(float2);
-  M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  kern<<<D + 1, 512, smem, st>>>(k, spec, D);
+  if (G::N <= 16384) {
+    auto kern = spectrum_kind2_kernel<G>;
+    const size_t smem = (size_t)G::N * sizeof(float2);
+    M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<D + 1, 512, smem, st>>>(k, spec, D);
+  } else {
+    auto kern = spectrum_kind2_cluster_kernel<G>;
+    const size_t smem = (size_t)(G::N / 4) * sizeof(float2);
+    M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<2 * (D + 1), 512, smem, st>>>(k, spec, D);
+  }
   M2_LAUNCH_CHECK("spectrum_kind2_kernel");
   return M2_OK;
 }
@@ -638,25 +786,28 @@ static int launch_conv(const Params& P, cudaStream_t st) {
 // supply time-contiguous tensors
 int longconv_tcl_supported(int seq_len, m2_dtype act_dtype) {
   if (act_dtype != M2_BF16 || seq_len % 4 != 0) return 0;
-  return (seq_len > 1024 && seq_len <= 2048) || (seq_len > 4096 && seq_len <= 8192);
+  return (seq_len > 1024 && seq_len <= 2048) || (seq_len > 4096 && seq_len <= 8192) ||
+         (seq_len > 16384 && seq_len <= 32768);
 }
 
 size_t spectrum_kind2_floats(int D, int L) {
   if (L <= 2048) return (size_t)lcl::Geo4k::HDR_FLOATS + (size_t)(lcl::Geo4k::N / 2) * D;
-  return (size_t)lcl::Geo16k::HDR_FLOATS + (size_t)(lcl::Geo16k::N / 2) * D;
+  if (L <= 8192) return (size_t)lcl::Geo16k::HDR_FLOATS + (size_t)(lcl::Geo16k::N / 2) * D;
+  return (size_t)lcl::Geo64k::HDR_FLOATS + (size_t)(lcl::Geo64k::N / 2) * D;
 }
 
 int spectrum_kind2_launch(int D, int L, const float* k, float* spec, cudaStream_t st) {
   M2_REQUIRE(longconv_tcl_supported(L, M2_BF16), M2_ERR_UNSUPPORTED,
-             "m2_filter_spectrum: kind 2 covers 1024 < seq_len <= 2048 and 4096 < seq_len <= 8192 (multiples of 4)");
+             "m2_filter_spectrum: kind 2 covers seq_len in (1024, 2048], (4096, 8192], (16384, 32768], multiples of 4");
   if (L <= 2048) return lcl::launch_spectrum<lcl::Geo4k>(D, k, spec, st);
-  return lcl::launch_spectrum<lcl::Geo16k>(D, k, spec, st);
+  if (L <= 8192) return lcl::launch_spectrum<lcl::Geo16k>(D, k, spec, st);
+  return lcl::launch_spectrum<lcl::Geo64k>(D, k, spec, st);
 }
 
 int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
   using namespace lcl;
   M2_REQUIRE(longconv_tcl_supported(a->seq_len, a->act_dtype), M2_ERR_UNSUPPORTED,
-             "m2_longconv_fwd: kind 2 needs bf16 activations and 1024 < seq_len <= 2048 or 4096 < seq_len <= 8192");
+             "m2_longconv_fwd: kind 2 needs bf16 activations and seq_len in (1024, 2048], (4096, 8192] or (16384, 32768]");
   M2_REQUIRE(a->xin_st == 1 && a->out_st == 1 && (a->n_filters == 1 || a->u_st == 1), M2_ERR_UNSUPPORTED,
              "m2_longconv_fwd: kind 2 needs time-contiguous tensors ((batch, channel, time) layout)");
   M2_REQUIRE(a->xin_sc % 4 == 0 && a->xin_sb % 4 == 0 && a->out_sc % 4 == 0 && a->out_sb % 4 == 0 &&
@@ -676,9 +827,9 @@ int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
     M2_REQUIRE(m2_aligned(a->u, ua) && a->u_sc % 4 == 0 && a->u_sb % 4 == 0, M2_ERR_ALIGN,
                "m2_longconv_fwd: kind 2 needs rows of u aligned to four elements");
   }
-  const bool small = a->seq_len <= 2048;
-  if (small) return ubf ? launch_conv<Geo4k, __nv_bfloat16>(P, st) : launch_conv<Geo4k, float>(P, st);
-  return ubf ? launch_conv<Geo16k, __nv_bfloat16>(P, st) : launch_conv<Geo16k, float>(P, st);
+  if (a->seq_len <= 2048) return ubf ? launch_conv<Geo4k, __nv_bfloat16>(P, st) : launch_conv<Geo4k, float>(P, st);
+  if (a->seq_len <= 8192) return ubf ? launch_conv<Geo16k, __nv_bfloat16>(P, st) : launch_conv<Geo16k, float>(P, st);
+  return ubf ? launch_conv<Geo64k, __nv_bfloat16>(P, st) : launch_conv<Geo64k, float>(P, st);
 }
 
 }  // namespace m2
