@@ -54,6 +54,58 @@ __device__ __forceinline__ float2 cmul_conj(float2 a, float2 b) {  // a * conj(b
   return make_float2(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
 }
 
+// ---- packed float32 pairs (sm_100 f32x2 arithmetic: two FMAs per instruction) ----------
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+  f32x2 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+  f32x2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ f32x2 f2_splat(float v) { return f2_pack(v, v); }
+
+// gelu(x) = x Phi(x) for two values at once, with erf from the rational approximation
+// erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2), t = 1 / (1 + p z)
+// (Abramowitz & Stegun 7.1.26, absolute error 1.5e-7): x >= 0 gives x (1 - q/2), x < 0 gives
+// x q/2 with q = erfc(|x| / sqrt 2).  The result is meant to be rounded to bf16 next; it
+// differs from the exact-erf value by far less than a bf16 rounding step.
+__device__ __forceinline__ void gelu_pair(float x0, float x1, float& y0, float& y1) {
+  const f32x2 x = f2_pack(x0, x1);
+  const f32x2 ax = f2_pack(fabsf(x0), fabsf(x1));
+  float d0, d1;
+  f2_unpack(f2_fma(ax, f2_splat(0.3275911f * 0.70710678118654752f), f2_splat(1.0f)), d0, d1);
+  float t0, t1;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t0) : "f"(d0));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(t1) : "f"(d1));
+  const f32x2 t = f2_pack(t0, t1);
+  f32x2 s = f2_fma(t, f2_splat(1.061405429f), f2_splat(-1.453152027f));
+  s = f2_fma(s, t, f2_splat(1.421413741f));
+  s = f2_fma(s, t, f2_splat(-0.284496736f));
+  s = f2_fma(s, t, f2_splat(0.254829592f));
+  s = f2_mul(s, t);
+  float w0, w1;
+  f2_unpack(f2_mul(f2_mul(x, x), f2_splat(-0.5f * 1.4426950408889634f)), w0, w1);   // -z^2 log2(e)
+  float e0, e1;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(w0));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(w1));
+  float h0, h1;
+  f2_unpack(f2_mul(f2_mul(s, f2_pack(e0, e1)), f2_splat(0.5f)), h0, h1);            // q / 2
+  y0 = x0 * (x0 >= 0.f ? 1.0f - h0 : h0);
+  y1 = x1 * (x1 >= 0.f ? 1.0f - h1 : h1);
+}
+
 __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }

@@ -199,8 +199,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (GLU) {
             const uint32_t g = pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1]));
             const uint32_t n = pack_bf16(__uint_as_float(b[j]), __uint_as_float(b[j + 1]));
-            v0 = bf16r(gelu_erf(__uint_as_float(g << 16))) * __uint_as_float(n << 16);
-            v1 = bf16r(gelu_erf(__uint_as_float(g & 0xFFFF0000u))) * __uint_as_float(n & 0xFFFF0000u);
+            float a0, a1;
+            gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
+            const uint32_t act = pack_bf16(a0, a1);           // GELU output cast to bf16
+            v0 = __uint_as_float(act << 16) * __uint_as_float(n << 16);
+            v1 = __uint_as_float(act & 0xFFFF0000u) * __uint_as_float(n & 0xFFFF0000u);
           } else {
             v0 = bf16r(__uint_as_float(a[j]));
             v1 = bf16r(__uint_as_float(a[j + 1]));

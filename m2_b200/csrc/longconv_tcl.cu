@@ -746,7 +746,7 @@ longconv_tcl_kernel(const Params P) {
 }
 
 using Geo4k = Geo<16, 8, 4, 1>;
-using Geo16k = Geo<32, 16, 4, 1>;
+using Geo16k = Geo<32, 16, 4, 2>;
 using Geo64k = Geo<64, 32, 1, 4>;
 
 template <typename G>
