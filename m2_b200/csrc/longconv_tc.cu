@@ -153,25 +153,27 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
   asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 
-// depthwise 3-tap conv of a channel pair at one time step; window holds x[t-2], x[t-1]
-struct Taps { float w0[2], w1[2], w2[2], b[2]; };
+// depthwise 3-tap conv of a channel pair at one time step, both channels at once in packed
+// float32 pairs; wa, wb hold x[t-2], x[t-1]
+struct Taps { f32x2 w0, w1, w2, b; };
 __device__ __forceinline__ void load_taps(Taps& T, const float* sw, const float* sb, int ch) {
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-    T.w0[e] = bf16r(__ldg(sw + 3 * (ch + e)));
-    T.w1[e] = bf16r(__ldg(sw + 3 * (ch + e) + 1));
-    T.w2[e] = bf16r(__ldg(sw + 3 * (ch + e) + 2));
-    T.b[e] = bf16r(__ldg(sb + ch + e));
-  }
+  T.w0 = f2_pack(bf16r(__ldg(sw + 3 * ch)), bf16r(__ldg(sw + 3 * ch + 3)));
+  T.w1 = f2_pack(bf16r(__ldg(sw + 3 * ch + 1)), bf16r(__ldg(sw + 3 * ch + 4)));
+  T.w2 = f2_pack(bf16r(__ldg(sw + 3 * ch + 2)), bf16r(__ldg(sw + 3 * ch + 5)));
+  T.b = f2_pack(bf16r(__ldg(sb + ch)), bf16r(__ldg(sb + ch + 1)));
+}
+__device__ __forceinline__ f32x2 bf2_to_f2(uint32_t u) { return f2_pack(bf_lo(u), bf_hi(u)); }
+__device__ __forceinline__ uint32_t f2_to_bf2(f32x2 v) {
+  float lo, hi;
+  f2_unpack(v, lo, hi);
+  return pack_bf2(lo, hi);
 }
 // returns the bf16-rounded conv outputs of both channels packed as bf16x2 and slides the window
-__device__ __forceinline__ uint32_t conv_step(const Taps& T, float (&win)[2][2], uint32_t xpair) {
-  const float x0 = bf_lo(xpair), x1 = bf_hi(xpair);
-  const float c0 = fmaf(T.w2[0], x0, fmaf(T.w1[0], win[0][1], fmaf(T.w0[0], win[0][0], T.b[0])));
-  const float c1 = fmaf(T.w2[1], x1, fmaf(T.w1[1], win[1][1], fmaf(T.w0[1], win[1][0], T.b[1])));
-  win[0][0] = win[0][1]; win[0][1] = x0;
-  win[1][0] = win[1][1]; win[1][1] = x1;
-  return pack_bf2(c0, c1);
+__device__ __forceinline__ uint32_t conv_step(const Taps& T, f32x2& wa, f32x2& wb, uint32_t xpair) {
+  const f32x2 x = bf2_to_f2(xpair);
+  const f32x2 c = f2_fma(T.w2, x, f2_fma(T.w1, wb, f2_fma(T.w0, wa, T.b)));
+  wa = wb; wb = x;
+  return f2_to_bf2(c);
 }
 
 // MMAs of one stage, issued by a single thread once every operand tile is in shared memory.
@@ -302,46 +304,25 @@ longconv_tc128_kernel(const Params P) {
           Taps Tx, Tv;
           load_taps(Tx, P.sw, P.sb, ch);
           load_taps(Tv, P.sw, P.sb, 2 * P.D + ch);
-          float wx[2][2], wv[2][2];
-          uint32_t lx[2][8], lv[2][8];                     // double-buffered loads: chunk i+1 in flight during chunk i
+          // every load of the pass is issued before the first is consumed
+          uint32_t lx[34], lv[34];
 #pragma unroll
-          for (int hh = 0; hh < 2; ++hh) {
-            const int t = t_begin - 2 + hh;
-            uint32_t px = 0, pv = 0;
-            if (t >= 0) {
-              px = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
-              pv = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
-            }
-            wx[0][hh] = bf_lo(px); wx[1][hh] = bf_hi(px);
-            wv[0][hh] = bf_lo(pv); wv[1][hh] = bf_hi(pv);
-          }
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int t = t_begin + j;
-            lx[0][j] = lv[0][j] = 0;
-            if (t < P.L) {
-              lx[0][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
-              lv[0][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
+          for (int j = 0; j < 34; ++j) {
+            const int t = t_begin - 2 + j;
+            lx[j] = lv[j] = 0;
+            if (t >= 0 && t < P.L) {
+              lx[j] = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
+              lv[j] = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
             }
           }
+          f32x2 xa = bf2_to_f2(lx[0]), xbw = bf2_to_f2(lx[1]), va = bf2_to_f2(lv[0]), vbw = bf2_to_f2(lv[1]);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            if (i < 3) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int t = t_begin + 8 * (i + 1) + j;
-                lx[(i + 1) & 1][j] = lv[(i + 1) & 1][j] = 0;
-                if (t < P.L) {
-                  lx[(i + 1) & 1][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + (long long)t * P.xst));
-                  lv[(i + 1) & 1][j] = __ldg(reinterpret_cast<const uint32_t*>(xb + 2 * P.D + (long long)t * P.xst));
-                }
-              }
-            }
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const uint32_t cx = conv_step(Tx, wx, lx[i & 1][j]);
-              const uint32_t cv = conv_step(Tv, wv, lv[i & 1][j]);
-              const uint32_t pr = pack_bf2(bf_lo(cv) * bf_lo(cx), bf_hi(cv) * bf_hi(cx));
+              const uint32_t cx = conv_step(Tx, xa, xbw, lx[2 + 8 * i + j]);
+              const uint32_t cv = conv_step(Tv, va, vbw, lv[2 + 8 * i + j]);
+              const uint32_t pr = f2_to_bf2(f2_mul(bf2_to_f2(cv), bf2_to_f2(cx)));
               const bool live = (t_begin + 8 * i + j) < P.L;
               const float a0 = live ? bf_lo(pr) : 0.f, a1 = live ? bf_hi(pr) : 0.f;
               if ((i & 1) == 0) {
@@ -532,14 +513,14 @@ longconv_tc128_kernel(const Params P) {
         if (f == 0) {
           Taps T2;
           load_taps(T2, P.sw, P.sb, P.D + ch);
-          float w2[2][2] = {{bf_lo(gl[0]), bf_lo(gl[1])}, {bf_hi(gl[0]), bf_hi(gl[1])}};
+          f32x2 ga = bf2_to_f2(gl[0]), gb = bf2_to_f2(gl[1]);
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             const int t = t_begin + j;
-            const uint32_t c2 = conv_step(T2, w2, gl[j + 2]);
+            const uint32_t c2 = conv_step(T2, ga, gb, gl[j + 2]);
             const float2 y = Y2[t * (CT / 2) + pi];
             const uint32_t yr = pack_bf2(y.x, y.y);          // conv + bias term, cast to bf16
-            const uint32_t res = pack_bf2(bf_lo(yr) * bf_lo(c2), bf_hi(yr) * bf_hi(c2));
+            const uint32_t res = f2_to_bf2(f2_mul(bf2_to_f2(yr), bf2_to_f2(c2)));
             if (t < P.L) *reinterpret_cast<uint32_t*>(ob + (long long)t * P.ost) = res;
           }
         } else {
