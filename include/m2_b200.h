@@ -29,7 +29,7 @@ extern "C" {
 
 #define M2_B200_ABI_VERSION 1
 
-typedef enum { M2_F32 = 0, M2_BF16 = 1 } m2_dtype;
+typedef enum { M2_F32 = 0, M2_BF16 = 1, M2_F16 = 2 /* only where an entry point says so */ } m2_dtype;
 
 typedef enum {
   M2_OK = 0,
@@ -91,13 +91,24 @@ int m2_hyena_filter(const m2_filter_args* args, void* stream);
  * d_model a multiple of 128, channel-contiguous tensors), 2 = tcgen05 tensor cores for long rows
  * (bf16, seq_len in (1024, 2048], (4096, 8192] or (16384, 32768], a multiple of 4; needs
  * time-contiguous tensors, i.e. xin_st == u_st == out_st == 1);
+ * 3 = tcgen05 Toeplitz GEMMs with the batch as the M dimension (bf16, 16 <= seq_len <= 128, a
+ * multiple of 8, batch >= 64; time-contiguous tensors, the residual input as fp16 from
+ * m2_time_major_f16).  m2_longconv_kind() never returns 3; m2_longconv_kind_batch() does when
+ * the batch is large enough to fill the 128-row tiles.
  * m2_filter_spectrum_floats() is the number of float32 the spectrum of one filter takes.
+ * m2_filter_spectrum_bias() is m2_filter_spectrum() with the convolution's bias term (the
+ * `+ u * bias` of fftconv_ref, bert/src/mm/hyena_utils.py:35-36; float32 (d_model), device, or
+ * NULL) folded into the table: required for kind 3, whose m2_longconv_fwd call then takes
+ * bias = NULL; rejected for the other kinds, which take the bias in m2_longconv_fwd.
  * k (device, float32): (d_model, m2_filter_row_len(seq_len)) as written by m2_hyena_filter.
  * ------------------------------------------------------------------------------------- */
 int    m2_longconv_kind(int seq_len, m2_dtype act_dtype, int d_model);
 size_t m2_filter_spectrum_floats(int kind, int d_model, int seq_len);
 int    m2_filter_spectrum(int kind, int d_model, int seq_len, const float* k, float* spec_out,
                           void* stream);
+int    m2_longconv_kind_batch(int batch, int seq_len, m2_dtype act_dtype, int d_model);
+int    m2_filter_spectrum_bias(int kind, int d_model, int seq_len, const float* k, const float* bias,
+                               float* spec_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Fused gated long convolution: everything between in_linear and out_linear.
@@ -131,10 +142,29 @@ typedef struct {
   const float* short_w;     /* device (3*d_model, 3): short_filter.weight */
   const float* short_b;     /* device (3*d_model):    short_filter.bias */
   const float* spec[2];     /* device, from m2_filter_spectrum (filter_fn, filter_fn2) */
-  const float* bias[2];     /* device (d_model): filter_fn.bias, filter_fn2.bias */
+  const float* bias[2];     /* device (d_model): filter_fn.bias, filter_fn2.bias (NULL for kind 3) */
+  int yu_bf16;              /* kind 3 only: != 0 rounds the residual convolution to bf16 before the
+                               final add, as the reference does when the layer input is bf16 (the
+                               other kinds infer this from u_dtype) */
 } m2_longconv_args;
 
 int m2_longconv_fwd(const m2_longconv_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------
+ * dst[c, b, t] = fp16(src[b, t, c]) (saturating): the time-contiguous fp16 copy of the raw
+ * layer input that kind 3 of m2_longconv_fwd loads as a tensor-core operand.  Part of the
+ * `u.transpose(-1, -2)` layout change of bert/src/mm/monarch_mixer_sequence_mixer.py:109.
+ *   src (batch, seq_len, d_model) of src_dtype (M2_F32 or M2_BF16) with strides in elements;
+ *   dst fp16, element (c, b, t) at dst[c*dst_sc + b*dst_sb + t].
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int batch, seq_len, d_model;
+  m2_dtype src_dtype;
+  const void* src; long long src_sb, src_st, src_sc;
+  void* dst;       long long dst_sb, dst_sc;
+} m2_time_major_args;
+
+int m2_time_major_f16(const m2_time_major_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Block-diagonal linear:  out[:, k*q:(k+1)*q] = x[:, k*p:(k+1)*p] @ w[k]^T (+ bias).
@@ -185,6 +215,10 @@ int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);
  * out_bf16 (optional, may be NULL): a second copy of the result rounded to bf16, row stride
  * ld_bf16 -- what the next layer's in_linear reads under autocast (its cast of the float32
  * LayerNorm output), written here instead of by a separate cast pass.
+ * out_tm_f16 (optional, may be NULL): a third copy as fp16 laid out time-major, row r = b *
+ * seq_len + t, column c at out_tm_f16[c*tm_sc + b*tm_sb + t] -- what m2_time_major_f16 would
+ * make of `out`, the residual-filter operand of kind 3 of m2_longconv_fwd.  Needs the same
+ * shapes as out_bf16, seq_len a multiple of 8 that divides m, tm_sb and tm_sc multiples of 8.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int m, n;
@@ -195,6 +229,7 @@ typedef struct {
   float eps;
   void* out; long long ldo;
   void* out_bf16; long long ld_bf16;
+  void* out_tm_f16; long long tm_sb, tm_sc; int seq_len;
 } m2_add_layernorm_args;
 
 int m2_add_layernorm_fwd(const m2_add_layernorm_args* args, void* stream);

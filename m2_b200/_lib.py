@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libm2b200.so")
 ABI_VERSION = 1
 
-M2_F32, M2_BF16 = 0, 1
+M2_F32, M2_BF16, M2_F16 = 0, 1, 2
 
 c_float_p = C.POINTER(C.c_float)
 
@@ -39,6 +39,15 @@ class LongconvArgs(C.Structure):
         ("out", C.c_void_p), ("out_sb", C.c_longlong), ("out_st", C.c_longlong), ("out_sc", C.c_longlong),
         ("short_w", C.c_void_p), ("short_b", C.c_void_p),
         ("spec", C.c_void_p * 2), ("bias", C.c_void_p * 2),
+        ("yu_bf16", C.c_int),
+    ]
+
+
+class TimeMajorArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int), ("seq_len", C.c_int), ("d_model", C.c_int), ("src_dtype", C.c_int),
+        ("src", C.c_void_p), ("src_sb", C.c_longlong), ("src_st", C.c_longlong), ("src_sc", C.c_longlong),
+        ("dst", C.c_void_p), ("dst_sb", C.c_longlong), ("dst_sc", C.c_longlong),
     ]
 
 
@@ -67,6 +76,7 @@ class AddLayernormArgs(C.Structure):
         ("weight", C.c_void_p), ("bias", C.c_void_p), ("eps", C.c_float),
         ("out", C.c_void_p), ("ldo", C.c_longlong),
         ("out_bf16", C.c_void_p), ("ld_bf16", C.c_longlong),
+        ("out_tm_f16", C.c_void_p), ("tm_sb", C.c_longlong), ("tm_sc", C.c_longlong), ("seq_len", C.c_int),
     ]
 
 
@@ -80,7 +90,10 @@ SYMBOLS = {
     "m2_longconv_kind": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "m2_filter_spectrum_floats": (C.c_size_t, [C.c_int, C.c_int, C.c_int]),
     "m2_filter_spectrum": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "m2_longconv_kind_batch": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
+    "m2_filter_spectrum_bias": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "m2_longconv_fwd": (C.c_int, [C.POINTER(LongconvArgs), C.c_void_p]),
+    "m2_time_major_f16": (C.c_int, [C.POINTER(TimeMajorArgs), C.c_void_p]),
     "m2_blockdiag_fwd": (C.c_int, [C.POINTER(BlockdiagArgs), C.c_void_p]),
     "m2_blockdiag_glu_fwd": (C.c_int, [C.POINTER(GluArgs), C.c_void_p]),
     "m2_add_layernorm_fwd": (C.c_int, [C.POINTER(AddLayernormArgs), C.c_void_p]),

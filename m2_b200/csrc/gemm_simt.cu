@@ -148,12 +148,14 @@ add_layernorm_kernel(const TI* a, long long lda, const TI* b, long long ldb, con
 // Vectorised variant: one warp per row, the row held in registers (n a multiple of 256 up to
 // 2048, 16-byte aligned rows); optional second output rounded to bf16.
 template <typename TO, int VI>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* b, long long ldb,
                           const float* __restrict__ w, const float* __restrict__ bias, float eps, TO* out,
-                          long long ldo, __nv_bfloat16* out2, long long ld2, int m) {
+                          long long ldo, __nv_bfloat16* out2, long long ld2, int m,
+                          __half* out_tm, long long tm_sb, long long tm_sc, int seq_len) {
+  extern __shared__ __half ln_tile[];   // [rows of the block][n] fp16, only with out_tm
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= m) return;
+  if (warp >= m) return;               // never taken with out_tm: m is a multiple of the block's rows
   const uint4* pa = reinterpret_cast<const uint4*>(a + (long long)warp * lda);
   const uint4* pb = reinterpret_cast<const uint4*>(b + (long long)warp * ldb);
   float v[VI][8];
@@ -205,6 +207,34 @@ add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bflo
           make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
     if (out2) *reinterpret_cast<uint4*>(out2 + (long long)warp * ld2 + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    if (out_tm) {
+      uint32_t hk[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __half2 h = __floats2half2_rn(fminf(fmaxf(y[2 * j], -65504.f), 65504.f), fminf(fmaxf(y[2 * j + 1], -65504.f), 65504.f));
+        hk[j] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(ln_tile + (size_t)(threadIdx.x >> 5) * n + c0) = make_uint4(hk[0], hk[1], hk[2], hk[3]);
+    }
+  }
+  if (out_tm) {
+    // rows of the block are consecutive time steps of one sequence: write each channel's
+    // run of them (16 or 32 contiguous bytes) into the time-major copy
+    __syncthreads();
+    const int rows = blockDim.x >> 5;
+    const long long row0 = (long long)blockIdx.x * rows;
+    __half* dst = out_tm + (row0 / seq_len) * tm_sb + (row0 % seq_len);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      for (int r0 = 0; r0 < rows; r0 += 8) {
+        uint32_t q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const __half2 h = __halves2half2(ln_tile[(size_t)(r0 + 2 * j) * n + c], ln_tile[(size_t)(r0 + 2 * j + 1) * n + c]);
+          q[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(dst + (long long)c * tm_sc + r0) = make_uint4(q[0], q[1], q[2], q[3]);
+      }
+    }
   }
 }
 
@@ -285,11 +315,24 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
                    m2_aligned(a->a, 16) && m2_aligned(a->b, 16) && m2_aligned(a->out, 16) && a->ldo % 8 == 0 &&
                    m2_aligned(a->weight, 16) && m2_aligned(a->bias, 16) &&
                    (a->out_bf16 == nullptr || (m2_aligned(a->out_bf16, 16) && a->ld_bf16 % 8 == 0));
+  if (a->out_tm_f16) {
+    M2_REQUIRE(vec, M2_ERR_UNSUPPORTED,
+               "m2_add_layernorm_fwd: the time-major copy needs bf16 inputs, n a multiple of 256 (<= 2048) and 16-byte aligned rows");
+    M2_REQUIRE(a->seq_len > 0 && a->seq_len % 8 == 0 && a->m % a->seq_len == 0, M2_ERR_ARG,
+               "m2_add_layernorm_fwd: the time-major copy needs m = batch * seq_len rows with seq_len a multiple of 8");
+    M2_REQUIRE(m2_aligned(a->out_tm_f16, 16) && a->tm_sb % 8 == 0 && a->tm_sc % 8 == 0, M2_ERR_ALIGN,
+               "m2_add_layernorm_fwd: the time-major copy needs 16-byte aligned rows");
+  }
   if (vec) {
-    const int blocks = (a->m + 7) / 8;
-#define M2_LNW(TO, VI) add_layernorm_warp_kernel<TO, VI><<<blocks, 256, 0, st>>>( \
+    const int rows = a->out_tm_f16 ? (a->seq_len % 16 == 0 ? 16 : 8) : 8;
+    const int blocks = (a->m + rows - 1) / rows;
+    const size_t tile = a->out_tm_f16 ? (size_t)rows * a->n * 2 : 0;
+#define M2_LNW(TO, VI) do { \
+      if (tile > 48 * 1024) M2_CUDA(cudaFuncSetAttribute(add_layernorm_warp_kernel<TO, VI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile)); \
+      add_layernorm_warp_kernel<TO, VI><<<blocks, 32 * rows, tile, st>>>( \
       (const __nv_bfloat16*)a->a, a->lda, (const __nv_bfloat16*)a->b, a->ldb, a->weight, a->bias, a->eps, \
-      (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m)
+      (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m, \
+      (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len); } while (0)
 #define M2_LNW_VI(TO) switch (a->n / 256) { case 1: M2_LNW(TO, 1); break; case 2: M2_LNW(TO, 2); break; \
       case 3: M2_LNW(TO, 3); break; case 4: M2_LNW(TO, 4); break; case 5: M2_LNW(TO, 5); break; \
       case 6: M2_LNW(TO, 6); break; case 7: M2_LNW(TO, 7); break; default: M2_LNW(TO, 8); break; }
@@ -299,7 +342,7 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
     M2_LAUNCH_CHECK("add_layernorm_warp_kernel");
     return M2_OK;
   }
-  M2_REQUIRE(a->out_bf16 == nullptr, M2_ERR_UNSUPPORTED,
+  M2_REQUIRE(a->out_bf16 == nullptr && a->out_tm_f16 == nullptr, M2_ERR_UNSUPPORTED,
              "m2_add_layernorm_fwd: the bf16 copy needs bf16 inputs, n a multiple of 256 (<= 2048) and 16-byte aligned rows");
   const size_t smem = (size_t)a->n * sizeof(float);
   const int threads = a->n >= 1024 ? 256 : 128;

@@ -5,6 +5,7 @@
 #include "longconv_simt.cu"
 #include "longconv_tc.cu"
 #include "longconv_tcl.cu"
+#include "longconv_tz.cu"
 #include "longconv.cu"
 #include "gemm_tc.cu"
 #include "gemm_simt.cu"

@@ -56,9 +56,16 @@ class BertGatedLinearUnitMLP(nn.Module):
             # (with the bias column its GEMM uses) instead of leaving it to a separate cast pass
             from .sequence_mixer import make_augmented
             aug = make_augmented(x2.shape[0], x.shape[-1], x.device)
+        tm = None
+        if aug is not None and ops.longconv_kind_batch(x.shape[0], x.shape[1], torch.bfloat16, x.shape[2]) == 3:
+            # a following mixer of this shape runs the Toeplitz-GEMM convolution, which reads the
+            # layer input as a time-major fp16 operand: written here too
+            tm = torch.empty((x.shape[2], x.shape[0], x.shape[1]), dtype=torch.float16, device=x.device)
         y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,
-                                  self.layernorm.eps, out_dtype, bf16_copy=aug)
+                                  self.layernorm.eps, out_dtype, bf16_copy=aug, tm_copy=tm)
         y = y.reshape(x.shape)
         if aug is not None:
             y._m2_aug = aug
+        if tm is not None:
+            y._m2_tm = tm
         return y

@@ -177,10 +177,13 @@ class HyenaFilter(OptimModule):
     def spectrum(self, L, bf16_rounding, kind):
         key = ("s", int(L), bool(bf16_rounding), int(kind))
         ver = self._version_key()
+        if kind == 3:   # this table holds the bias too
+            ver = ver + ((self.bias.data_ptr(), self.bias._version, bool(self.use_bias)),)
         hit = self._cache.get(key)
         if hit is not None and hit[0] == ver:
             return hit[1]
-        spec = ops.filter_spectrum(self.time_filter(L, bf16_rounding), L, kind)
+        spec = ops.filter_spectrum(self.time_filter(L, bf16_rounding), L, kind,
+                                   bias=self.conv_bias() if kind == 3 else None)
         self._cache[key] = (ver, spec)
         return spec
 

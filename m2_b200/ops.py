@@ -7,7 +7,7 @@ import ctypes as C
 import torch
 
 from . import _lib
-from ._lib import M2_BF16, M2_F32
+from ._lib import M2_BF16, M2_F16, M2_F32
 
 
 LAUNCHES = 0          # kernels of this library launched since the counter was last reset
@@ -56,6 +56,8 @@ def _dt(t: torch.Tensor) -> int:
         return M2_F32
     if t.dtype == torch.bfloat16:
         return M2_BF16
+    if t.dtype == torch.float16:
+        return M2_F16
     raise TypeError(f"m2_b200 supports float32 and bfloat16 tensors, got {t.dtype}")
 
 
@@ -127,23 +129,51 @@ def longconv_kind(seq_len: int, act_dtype: torch.dtype, d_model: int) -> int:
                                        int(d_model))
 
 
-def filter_spectrum(k: torch.Tensor, seq_len: int, kind: int) -> torch.Tensor:
-    """Spectrum table of one filter for kernel family `kind` (float32, opaque layout)."""
+def longconv_kind_batch(batch: int, seq_len: int, act_dtype: torch.dtype, d_model: int) -> int:
+    return _lib.lib().m2_longconv_kind_batch(int(batch), int(seq_len),
+                                             M2_BF16 if act_dtype == torch.bfloat16 else M2_F32, int(d_model))
+
+
+def filter_spectrum(k: torch.Tensor, seq_len: int, kind: int, bias=None) -> torch.Tensor:
+    """Spectrum table of one filter for kernel family `kind` (float32, opaque layout).
+    Kind 3 folds the convolution's bias term into the table: pass it here."""
     _need_cuda(k)
     assert k.dtype == torch.float32 and k.is_contiguous()
     d_model = k.shape[0]
     n = _lib.lib().m2_filter_spectrum_floats(kind, d_model, int(seq_len))
     spec = torch.empty(n, dtype=torch.float32, device=k.device)
-    _launch("m2_filter_spectrum", k, _lib.lib().m2_filter_spectrum, kind, d_model, int(seq_len),
-            k.data_ptr(), spec.data_ptr())
+    if kind == 3:
+        b = _f32c(bias) if bias is not None else None
+        _launch("m2_filter_spectrum", k, _lib.lib().m2_filter_spectrum_bias, kind, d_model, int(seq_len),
+                k.data_ptr(), b.data_ptr() if b is not None else None, spec.data_ptr())
+    else:
+        assert bias is None, "only kind 3 folds the bias into the spectrum"
+        _launch("m2_filter_spectrum", k, _lib.lib().m2_filter_spectrum, kind, d_model, int(seq_len),
+                k.data_ptr(), spec.data_ptr())
     return spec
 
 
-def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding, out=None):
+def time_major_f16(u: torch.Tensor, out=None) -> torch.Tensor:
+    """fp16 copy of u (B, L, D) laid out (D, B, L): the residual-filter operand of kind 3."""
+    _need_cuda(u)
+    B, L, D = u.shape
+    if out is None:
+        out = torch.empty((D, B, L), dtype=torch.float16, device=u.device)
+    assert out.dtype == torch.float16 and out.shape == (D, B, L) and out.stride(2) == 1
+    a = _lib.TimeMajorArgs()
+    a.batch, a.seq_len, a.d_model, a.src_dtype = B, L, D, _dt(u)
+    a.src, (a.src_sb, a.src_st, a.src_sc) = u.data_ptr(), u.stride()
+    a.dst, a.dst_sc, a.dst_sb = out.data_ptr(), out.stride(0), out.stride(1)
+    _launch("m2_time_major_f16", u, _lib.lib().m2_time_major_f16, C.byref(a))
+    return out
+
+
+def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding, out=None, yu_bf16=False):
     """Fused short conv + gates + long convolution(s).
 
     xin (B, L, 3D) in_linear output (any strides with a unit stride along L or channels),
-    u (B, L, D) raw layer input or None, specs/biases: one entry per filter.  Returns
+    u (B, L, D) raw layer input or None, specs/biases: one entry per filter (kind 3: biases
+    None, they are inside its spectra, and u an fp16 view from time_major_f16).  Returns
     (B, L, D) in xin's dtype.
     """
     _need_cuda(xin)
@@ -152,7 +182,7 @@ def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding
     nf = len(specs)
     if out is None:
         out = torch.empty((B, L, D), dtype=xin.dtype, device=xin.device)
-    keep = [_f32c(short_w.reshape(D3, -1)), _f32c(short_b)] + [_f32c(b) for b in biases]
+    keep = [_f32c(short_w.reshape(D3, -1)), _f32c(short_b)] + [_f32c(b) for b in (biases or [])]
     if keep[0].shape[1] != 3:
         raise RuntimeError("m2_b200: short_filter must have kernel_size 3")
     a = _lib.LongconvArgs()
@@ -165,9 +195,11 @@ def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding
         a.u, (a.u_sb, a.u_st, a.u_sc) = u.data_ptr(), u.stride()
     a.out, (a.out_sb, a.out_st, a.out_sc) = out.data_ptr(), out.stride()
     a.short_w, a.short_b = keep[0].data_ptr(), keep[1].data_ptr()
+    a.yu_bf16 = int(bool(yu_bf16))
     for i in range(nf):
         a.spec[i] = specs[i].data_ptr()
-        a.bias[i] = keep[2 + i].data_ptr()
+        if biases:
+            a.bias[i] = keep[2 + i].data_ptr()
     _launch("m2_longconv_fwd", xin, _lib.lib().m2_longconv_fwd, C.byref(a))
     return out
 
@@ -209,9 +241,11 @@ def blockdiag_glu_fwd(x2d, wg, inter):
     return h
 
 
-def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None):
+def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm_copy=None):
     """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype.  bf16_copy:
-    optional (m, >= n) bf16 tensor that receives the result rounded to bf16."""
+    optional (m, >= n) bf16 tensor that receives the result rounded to bf16.  tm_copy: optional
+    (n, B, L) fp16 tensor with B * L = m that receives the result time-major (see
+    time_major_f16)."""
     _need_cuda(a2d, b2d)
     if a2d.stride(-1) != 1:
         a2d = a2d.contiguous()
@@ -231,6 +265,10 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None):
     if bf16_copy is not None:
         assert bf16_copy.dtype == torch.bfloat16 and bf16_copy.stride(-1) == 1 and bf16_copy.shape[0] == m
         a.out_bf16, a.ld_bf16 = bf16_copy.data_ptr(), bf16_copy.stride(0)
+    if tm_copy is not None:
+        assert tm_copy.dtype == torch.float16 and tm_copy.dim() == 3 and tm_copy.stride(2) == 1
+        assert tm_copy.shape[0] == n and tm_copy.shape[1] * tm_copy.shape[2] == m
+        a.out_tm_f16, a.tm_sc, a.tm_sb, a.seq_len = tm_copy.data_ptr(), tm_copy.stride(0), tm_copy.stride(1), tm_copy.shape[2]
     _launch("m2_add_layernorm_fwd", a2d, _lib.lib().m2_add_layernorm_fwd, C.byref(a))
     return out
 

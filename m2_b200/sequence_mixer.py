@@ -128,6 +128,36 @@ class MonarchMixerSequenceMixing(nn.Module):
                              kind=2, bf16_rounding=True, out=y_t[:, :D].transpose(1, 2))
             return torch.matmul(y_t.transpose(1, 2), w_out.t())                  # (B, L, D)
 
+    def _forward_toeplitz(self, u, ures, specs):
+        """bf16 path for short sequences and large batches: the convolution kernel runs one
+        Toeplitz GEMM per channel with the batch as its M dimension, on channel-major
+        time-contiguous tensors -- in_linear writes (3D, B*L) and out_linear reads (D, B*L),
+        both single library GEMMs on transposed operands."""
+        B, L, D = u.shape
+        if not hasattr(self, "_aug_in"):
+            self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
+        w_in, w_out = self._aug_in.get(self.in_linear), self._aug_out.get(self.out_linear)
+        x_aug = augmented_input(u).reshape(B * L, D + _PAD)
+        with torch.autocast("cuda", enabled=False):
+            xin_t = torch.matmul(w_in, x_aug.t())                                # (3D, B*L)
+            u_t = None
+            if ures is not None:
+                u_t = getattr(ures, "_m2_tm", None)
+                if u_t is None or u_t.shape != (D, B, L) or u_t.device != u.device:
+                    u_t = ops.time_major_f16(ures)
+            buf = getattr(self, "_y_t", None)
+            if buf is None or buf.shape[1] != B * L or buf.device != u.device:
+                buf = torch.empty((D + _PAD, B * L), dtype=torch.bfloat16, device=u.device)
+                buf[D] = 1.0
+                buf[D + 1:] = 0.0
+                self._y_t = buf
+            ops.longconv_fwd(xin_t.view(3 * D, B, L).permute(1, 2, 0),
+                             u_t.permute(1, 2, 0) if u_t is not None else None,
+                             self.short_filter.weight, self.short_filter.bias, specs, None,
+                             kind=3, bf16_rounding=True, out=buf[:D].view(D, B, L).permute(1, 2, 0),
+                             yu_bf16=ures is not None and ures.dtype == torch.bfloat16)
+            return torch.matmul(buf.t(), w_out.t()).view(B, L, D)
+
     def forward(self, u, **kwargs):
         _check_forward_only(self, u)
         if not u.is_cuda:
@@ -148,9 +178,11 @@ class MonarchMixerSequenceMixing(nn.Module):
         filters = [self.filter_fn] + ([self.filter_fn2] if self.residual_long_conv else [])
         biases = [f.conv_bias() for f in filters]
         act_dtype = torch.bfloat16 if bf16 else u.dtype
-        kind = ops.longconv_kind(L, act_dtype, self.d_model)
+        kind = ops.longconv_kind_batch(u.size(0), L, act_dtype, self.d_model)
         specs = [f.spectrum(L, bf16, kind) for f in filters]
         ures = u_orig if self.residual_long_conv else None
+        if kind == 3:
+            return self._forward_toeplitz(u, ures, specs), None
         if kind == 2:
             return self._forward_long_rows(u, ures, specs, biases), None
         if bf16:

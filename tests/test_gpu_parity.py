@@ -411,3 +411,68 @@ def test_longconv_long_row_family(L, D, B, residual, u_bf16):
         errs += [O.parity_error(npy(outs[0]), ref), O.parity_error(npy(outs[1]), ref)]
     print("kind2-vs-kind0 / kind0-vs-oracle / kind2-vs-oracle:", ["%.3e" % e for e in errs])
     assert max(errs) < TOL_BF16, errs
+
+
+# ---- Toeplitz-GEMM family (batch as the M dimension, channel-major rows) against the CUDA-core family ----
+@pytest.mark.parametrize("L,D,B", [(128, 16, 130), (128, 8, 256), (104, 16, 64), (72, 8, 200), (64, 8, 128),
+                                   (16, 8, 64), (40, 8, 100)])
+@pytest.mark.parametrize("residual,u_bf16", [(True, False), (True, True), (False, False)])
+def test_longconv_toeplitz_family(L, D, B, residual, u_bf16):
+    cfg = dict(C.CASES["mixer_small"], L=L, l_max=128, D=D, B=B, order=32, residual=residual, seed=81)
+    m, sd = build_mixer(cfg, DEV)
+    g = torch.Generator().manual_seed(L + B)
+    xinT = (0.6 * torch.randn((3 * D, B, L), generator=g)).to(DEV).bfloat16()
+    uT = torch.randn((D, B, L), generator=g).to(DEV)
+    if u_bf16:
+        uT = uT.bfloat16()
+    xin, u = xinT.permute(1, 2, 0), uT.permute(1, 2, 0)      # (B, L, C) views of channel-major rows
+    assert ops.longconv_kind_batch(B, L, torch.bfloat16, D) == 3
+    assert ops.longconv_kind_batch(8, L, torch.bfloat16, D) != 3
+    filters = [m.filter_fn] + ([m.filter_fn2] if residual else [])
+    specs = [f.spectrum(L, True, 0) for f in filters]
+    out0 = ops.longconv_fwd(xin, u if residual else None, m.short_filter.weight, m.short_filter.bias, specs,
+                            [f.conv_bias() for f in filters], kind=0, bf16_rounding=True)
+    specs = [f.spectrum(L, True, 3) for f in filters]
+    out3 = torch.full((D, B, L), float("nan"), dtype=torch.bfloat16, device=DEV).permute(1, 2, 0)
+    u16 = ops.time_major_f16(u).permute(1, 2, 0) if residual else None
+    ops.longconv_fwd(xin, u16, m.short_filter.weight, m.short_filter.bias, specs, None, kind=3,
+                     bf16_rounding=True, out=out3, yu_bf16=u_bf16)
+    assert ops.device_status() == 0
+    assert torch.isfinite(out3.float()).all()
+    errs = [O.parity_error(npy(out3), npy(out0))]
+    if B * L * D <= 1 << 18:
+        taps = []
+        for f in filters:
+            k = npy(f.time_filter(L, True))
+            taps.append((k[:, :L], k[:, k.shape[1] - L:][:, ::-1], npy(f.bias)))
+        ref = O.mixer_core(npy(xin), npy(u), sd, bidirectional=True, residual_long_conv=residual,
+                           mode="bf16", u_is_bf16=u_bf16, filters=taps)
+        errs += [O.parity_error(npy(out0), ref), O.parity_error(npy(out3), ref)]
+    print("kind3-vs-kind0 / kind0-vs-oracle / kind3-vs-oracle:", ["%.3e" % e for e in errs])
+    assert max(errs) < TOL_BF16, errs
+
+
+def test_time_major_f16_copy():
+    g = torch.Generator().manual_seed(5)
+    for B, L, D, dt in [(3, 70, 100, torch.float32), (2, 128, 64, torch.bfloat16), (1, 8, 5, torch.float32)]:
+        u = (100 * torch.randn((B, L, D), generator=g)).to(DEV).to(dt)
+        u[0, 0, 0] = 1e6                                      # saturates instead of becoming inf
+        got = ops.time_major_f16(u)
+        ref = u.float().clamp(-65504, 65504).half().permute(2, 0, 1)
+        assert torch.equal(got, ref)
+
+
+@pytest.mark.parametrize("B,L,D", [(3, 16, 256), (2, 24, 768), (1, 128, 512)])
+def test_add_layernorm_time_major_copy(B, L, D):
+    g = torch.Generator().manual_seed(B + L)
+    a = torch.randn((B * L, D), generator=g).to(DEV).bfloat16()
+    b = torch.randn((B * L, D), generator=g).to(DEV).bfloat16()
+    w = torch.randn(D, generator=g).to(DEV)
+    bias = torch.randn(D, generator=g).to(DEV)
+    plain = ops.add_layernorm_fwd(a, b, w, bias, 1e-12, torch.float32)
+    tm = torch.full((D, B, L), float("nan"), dtype=torch.float16, device=DEV)
+    aug = torch.empty((B * L, D + 64), dtype=torch.bfloat16, device=DEV)
+    out = ops.add_layernorm_fwd(a, b, w, bias, 1e-12, torch.float32, bf16_copy=aug, tm_copy=tm)
+    assert torch.equal(out, plain)
+    assert torch.equal(aug[:, :D], plain.bfloat16())
+    assert torch.equal(tm, ops.time_major_f16(plain.view(B, L, D)))
