@@ -163,12 +163,13 @@ def time_cpu(w, sample_b, reps):
     return sample_b / dt, dt
 
 
-def config_of(name, w, n):
+def config_of(name, w, n, graph=True):
     return {"workload": f"{name}: {w['layers']}-layer M2-BERT encoder fwd (embeddings + mixer + BlockdiagLinear GLU MLP), "
                         f"d_model {w['D']}, L={w['L']}, batch {w['B']} per GPU, token ids uniform in [0,{VOCAB}), "
                         "random-init weights, bf16 autocast",
             "batch_per_gpu": w["B"], "global_batch": w["B"] * n, "seq_len": w["L"],
             "parallelism": f"batch-sharded x{n}, no data-path collective",
+            "launch": "one CUDA-graph replay per forward" if graph else "eager, one Python call per kernel",
             "l2": "explicit L2 flush (256 MiB write) between timed iterations"}
 
 
@@ -191,7 +192,7 @@ def run_reference(args, name, w):
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_of(name, w, args.gpus),
+            "config": config_of(name, w, args.gpus, graph=not args.no_graph),
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                              "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -206,6 +207,7 @@ def main():
     ap.add_argument("--workload", default="m2bert80m-L128", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
     args = ap.parse_args()
     name, w = args.workload, WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -233,17 +235,32 @@ def main():
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     stream = torch.cuda.current_stream(dev)
 
-    def step_resident():
+    def step_eager():
         with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             out, _ = model(ids_dev)
         return out
 
-    def step_e2e():
-        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-            ids = ids_host.to(dev, non_blocking=True)
-            out, _ = model(ids)
-            cls_host.copy_(out[:, 0].float(), non_blocking=True)
-        return out
+    if args.no_graph:
+        step_resident = step_eager
+
+        def step_e2e():
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                ids = ids_host.to(dev, non_blocking=True)
+                out, _ = model(ids)
+                cls_host.copy_(out[:, 0].float(), non_blocking=True)
+            return out
+    else:
+        # the public fixed-shape entry point: one captured forward, replayed per batch
+        from m2_b200.graph import GraphedForward
+        graphed = GraphedForward(model, ids_dev, warmup=max(args.warmup, 3))
+
+        def step_resident():
+            return graphed(graphed.static_in[0])[0]
+
+        def step_e2e():
+            out, _ = graphed(ids_host)                      # pinned host ids -> static device buffer
+            cls_host.copy_(out[:, 0], non_blocking=True)
+            return out
 
     def barrier():
         torch.cuda.synchronize(dev)
@@ -270,15 +287,22 @@ def main():
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ops.PROFILE = ops.LaunchProfile()
     ops.LAUNCHES = 0
     total_ms = timed(step_resident, args.steps)
     launches = ops.LAUNCHES
-    prof, ops.PROFILE = ops.PROFILE, None
     barrier()
     e2e_ms = timed(step_e2e, args.steps)
     barrier()
     clocks = sampler.stop() if rank == 0 else None
+    # per-kernel device times: a separate eager pass with an event pair around every launch of
+    # this library (the events would perturb the timed steps)
+    ops.PROFILE = ops.LaunchProfile()
+    prof_steps = 3
+    for _ in range(prof_steps):
+        flush.fill_(1)
+        step_eager()
+    torch.cuda.synchronize(dev)
+    prof, ops.PROFILE = ops.PROFILE, None
 
     t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -298,7 +322,7 @@ def main():
         roof = {"bound": "hbm", "kernel": "m2_longconv_fwd", "achieved": achieved, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
                 "traffic": None, "launch_ms": conv_ms, "algorithmic_bytes_per_launch": alg_bytes,
-                "kernel_ms_per_step": {k: prof.mean_ms(k) * prof.count(k) / args.steps for k in prof.names()}}
+                "kernel_ms_per_step": {k: prof.mean_ms(k) * prof.count(k) / prof_steps for k in prof.names()}}
         cpu = None
         if not args.no_cpu_baseline:
             sample_b = 32 if L <= 128 else 1
@@ -310,7 +334,7 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": config_of(name, w, world),
+                "config": config_of(name, w, world, graph=not args.no_graph),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": ids_host.numel() * 8,
                         "d2h_bytes_per_step": cls_host.numel() * 4},
                 "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}

@@ -214,7 +214,8 @@ int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);
  * bf16 tensor add does); out (m, n) of `out_dtype`; weight/bias float32 (n).
  * out_bf16 (optional, may be NULL): a second copy of the result rounded to bf16, row stride
  * ld_bf16 -- what the next layer's in_linear reads under autocast (its cast of the float32
- * LayerNorm output), written here instead of by a separate cast pass.
+ * LayerNorm output), written here instead of by a separate cast pass.  With out_bf16 given,
+ * out may be NULL: only the copies are written (a caller that feeds the next mixer from them).
  * out_tm_f16 (optional, may be NULL): a third copy as fp16 laid out time-major, row r = b *
  * seq_len + t, column c at out_tm_f16[c*tm_sc + b*tm_sb + t] -- what m2_time_major_f16 would
  * make of `out`, the residual-filter operand of kind 3 of m2_longconv_fwd.  Needs the same

@@ -13,9 +13,10 @@ from .hyena_filter import (ExponentialModulation, HyenaFilter, OptimModule,  # n
                            PositionalEmbedding, Sin)
 from .sequence_mixer import MonarchMixerSequenceMixing  # noqa: F401
 from .glu_mlp import BertGatedLinearUnitMLP  # noqa: F401
+from .graph import GraphedForward  # noqa: F401
 
 __all__ = [
     "MonarchMixerSequenceMixing", "HyenaFilter", "BlockdiagLinear", "StructuredLinear",
     "BertGatedLinearUnitMLP", "blockdiag_multiply", "Sin", "PositionalEmbedding",
-    "ExponentialModulation", "OptimModule",
+    "ExponentialModulation", "OptimModule", "GraphedForward",
 ]

@@ -54,6 +54,14 @@ __device__ __forceinline__ float2 cmul_conj(float2 a, float2 b) {  // a * conj(b
   return make_float2(a.x * b.x + a.y * b.y, a.y * b.x - a.x * b.y);
 }
 
+// One 32-byte store per thread (a full DRAM/L2 sector; two 16-byte stores of the same thread
+// reach L2 as two partial-sector writes).  p must be 32-byte aligned.
+__device__ __forceinline__ void stg256(void* p, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t a4,
+                                       uint32_t a5, uint32_t a6, uint32_t a7) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(p), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(a4), "r"(a5), "r"(a6), "r"(a7) : "memory");
+}
+
 // ---- packed float32 pairs (sm_100 f32x2 arithmetic: two FMAs per instruction) ----------
 typedef unsigned long long f32x2;
 __device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
@@ -76,10 +84,18 @@ __device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
 }
 __device__ __forceinline__ f32x2 f2_splat(float v) { return f2_pack(v, v); }
 
+// lane-wise product of two packed bf16 pairs, rounded to bf16 once (the exact product of two
+// bf16 values fits a float32, so this equals multiplying in float32 and rounding)
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
 // gelu(x) = x Phi(x) for two values at once, with erf from the rational approximation
 // erfc(z) = t (a1 + t (a2 + t (a3 + t (a4 + t a5)))) exp(-z^2), t = 1 / (1 + p z)
-// (Abramowitz & Stegun 7.1.26, absolute error 1.5e-7): x >= 0 gives x (1 - q/2), x < 0 gives
-// x q/2 with q = erfc(|x| / sqrt 2).  The result is meant to be rounded to bf16 next; it
+// (Abramowitz & Stegun 7.1.26, absolute error 1.5e-7), q = erfc(|x| / sqrt 2):
+// x Phi(x) = max(x, 0) - |x| q / 2.  The result is meant to be rounded to bf16 next; it
 // differs from the exact-erf value by far less than a bf16 rounding step.
 __device__ __forceinline__ void gelu_pair(float x0, float x1, float& y0, float& y1) {
   const f32x2 x = f2_pack(x0, x1);
@@ -100,10 +116,9 @@ __device__ __forceinline__ void gelu_pair(float x0, float x1, float& y0, float& 
   float e0, e1;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e0) : "f"(w0));
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e1) : "f"(w1));
-  float h0, h1;
-  f2_unpack(f2_mul(f2_mul(s, f2_pack(e0, e1)), f2_splat(0.5f)), h0, h1);            // q / 2
-  y0 = x0 * (x0 >= 0.f ? 1.0f - h0 : h0);
-  y1 = x1 * (x1 >= 0.f ? 1.0f - h1 : h1);
+  const f32x2 h = f2_mul(f2_mul(s, f2_pack(e0, e1)), f2_splat(-0.5f));              // -q / 2
+  // x Phi(x) = max(x, 0) - |x| q / 2 for either sign
+  f2_unpack(f2_fma(ax, h, f2_pack(fmaxf(x0, 0.f), fmaxf(x1, 0.f))), y0, y1);
 }
 
 __device__ __forceinline__ float gelu_erf(float x) {

@@ -152,10 +152,15 @@ __global__ void __launch_bounds__(512)
 add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* b, long long ldb,
                           const float* __restrict__ w, const float* __restrict__ bias, float eps, TO* out,
                           long long ldo, __nv_bfloat16* out2, long long ld2, int m,
-                          __half* out_tm, long long tm_sb, long long tm_sc, int seq_len) {
+                          __half* out_tm, long long tm_sb, long long tm_sc, int seq_len, int rpw) {
   extern __shared__ __half ln_tile[];   // [rows of the block][n] fp16, only with out_tm
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= m) return;               // never taken with out_tm: m is a multiple of the block's rows
+  const int wib = threadIdx.x >> 5, nw = blockDim.x >> 5, lane = threadIdx.x & 31;
+  constexpr int n = VI * 256;
+  // a warp normalises rpw rows (rpw > 1 only with out_tm, where m is a multiple of the block's rows)
+  for (int ri = 0; ri < rpw; ++ri) {
+  const int trow = ri * nw + wib;                                   // row within the block
+  const long long warp = (long long)blockIdx.x * nw * rpw + trow;   // row of the tensor
+  if (warp >= m) break;
   const uint4* pa = reinterpret_cast<const uint4*>(a + (long long)warp * lda);
   const uint4* pb = reinterpret_cast<const uint4*>(b + (long long)warp * ldb);
   float v[VI][8];
@@ -173,7 +178,6 @@ add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bflo
     }
   }
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const int n = VI * 256;
   const float mean = sum / n;
   float sq = 0.f;
 #pragma unroll
@@ -198,7 +202,9 @@ add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bflo
       __nv_bfloat162 h = __floats2bfloat162_rn(y[2 * j], y[2 * j + 1]);
       pk[j] = *reinterpret_cast<uint32_t*>(&h);
     }
-    if (sizeof(TO) == 4) {
+    if (out == nullptr) {
+      // only the copies are wanted
+    } else if (sizeof(TO) == 4) {
       float4* po = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (long long)warp * ldo + c0);
       po[0] = make_float4(y[0], y[1], y[2], y[3]);
       po[1] = make_float4(y[4], y[5], y[6], y[7]);
@@ -214,25 +220,43 @@ add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bflo
         __half2 h = __floats2half2_rn(fminf(fmaxf(y[2 * j], -65504.f), 65504.f), fminf(fmaxf(y[2 * j + 1], -65504.f), 65504.f));
         hk[j] = *reinterpret_cast<uint32_t*>(&h);
       }
-      *reinterpret_cast<uint4*>(ln_tile + (size_t)(threadIdx.x >> 5) * n + c0) = make_uint4(hk[0], hk[1], hk[2], hk[3]);
+      *reinterpret_cast<uint4*>(ln_tile + (size_t)trow * n + c0) = make_uint4(hk[0], hk[1], hk[2], hk[3]);
     }
   }
+  }
   if (out_tm) {
-    // rows of the block are consecutive time steps of one sequence: write each channel's
-    // run of them (16 or 32 contiguous bytes) into the time-major copy
+    // rows of the block are consecutive time steps of one sequence: write each channel's run
+    // of them (16 to 128 contiguous bytes) into the time-major copy, two channels per thread
     __syncthreads();
-    const int rows = blockDim.x >> 5;
+    const int rows = nw * rpw;
     const long long row0 = (long long)blockIdx.x * rows;
     __half* dst = out_tm + (row0 / seq_len) * tm_sb + (row0 % seq_len);
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
-      for (int r0 = 0; r0 < rows; r0 += 8) {
-        uint32_t q[4];
+    const uint32_t* tile32 = reinterpret_cast<const uint32_t*>(ln_tile);
+    const bool wide = (rows % 16 == 0) && ((reinterpret_cast<uintptr_t>(dst) & 31) == 0) && (tm_sc % 16 == 0);
+    for (int cp = threadIdx.x; cp < n / 2; cp += blockDim.x) {
+      __half* d0 = dst + (long long)(2 * cp) * tm_sc;
+      __half* d1 = d0 + tm_sc;
+      for (int r0 = 0; r0 < rows; r0 += 16) {
+        uint32_t lo[8], hi[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const __half2 h = __halves2half2(ln_tile[(size_t)(r0 + 2 * j) * n + c], ln_tile[(size_t)(r0 + 2 * j + 1) * n + c]);
-          q[j] = *reinterpret_cast<const uint32_t*>(&h);
+        for (int j = 0; j < 8; ++j) {
+          if (r0 + 2 * j < rows) {
+            const uint32_t w0 = tile32[(size_t)(r0 + 2 * j) * (n / 2) + cp], w1 = tile32[(size_t)(r0 + 2 * j + 1) * (n / 2) + cp];
+            lo[j] = __byte_perm(w0, w1, 0x5410);                    // channel 2 cp at rows r, r + 1
+            hi[j] = __byte_perm(w0, w1, 0x7632);                    // channel 2 cp + 1
+          }
         }
-        *reinterpret_cast<uint4*>(dst + (long long)c * tm_sc + r0) = make_uint4(q[0], q[1], q[2], q[3]);
+        if (wide) {                                                 // whole 32-byte sectors
+          stg256(d0 + r0, lo[0], lo[1], lo[2], lo[3], lo[4], lo[5], lo[6], lo[7]);
+          stg256(d1 + r0, hi[0], hi[1], hi[2], hi[3], hi[4], hi[5], hi[6], hi[7]);
+        } else {
+          *reinterpret_cast<uint4*>(d0 + r0) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+          *reinterpret_cast<uint4*>(d1 + r0) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+          if (r0 + 8 < rows) {
+            *reinterpret_cast<uint4*>(d0 + r0 + 8) = make_uint4(lo[4], lo[5], lo[6], lo[7]);
+            *reinterpret_cast<uint4*>(d1 + r0 + 8) = make_uint4(hi[4], hi[5], hi[6], hi[7]);
+          }
+        }
       }
     }
   }
@@ -308,7 +332,8 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
   M2_REQUIRE(a->m >= 0 && a->n > 0, M2_ERR_ARG, "m2_add_layernorm_fwd: bad sizes m=%d n=%d", a->m, a->n);
   M2_REQUIRE(a->n <= 12288, M2_ERR_UNSUPPORTED, "m2_add_layernorm_fwd: n > 12288");
   if (a->m == 0) return M2_OK;
-  M2_REQUIRE(a->a && a->b && a->weight && a->bias && a->out, M2_ERR_ARG, "m2_add_layernorm_fwd: NULL tensor pointer");
+  M2_REQUIRE(a->a && a->b && a->weight && a->bias && (a->out || a->out_bf16), M2_ERR_ARG,
+             "m2_add_layernorm_fwd: NULL tensor pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   M2_REQUIRE(a->out_bf16 == nullptr || a->ld_bf16 >= a->n, M2_ERR_ARG, "m2_add_layernorm_fwd: ld_bf16 smaller than the row");
   const bool vec = a->in_dtype == M2_BF16 && a->n % 256 == 0 && a->n <= 2048 && a->lda % 8 == 0 && a->ldb % 8 == 0 &&
@@ -324,15 +349,22 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
                "m2_add_layernorm_fwd: the time-major copy needs 16-byte aligned rows");
   }
   if (vec) {
-    const int rows = a->out_tm_f16 ? (a->seq_len % 16 == 0 ? 16 : 8) : 8;
+    // with the time-major copy a block covers 16 (or 8) consecutive steps of one sequence, so a
+    // channel's run of them is one 32-byte sector
+    int rows = 8, threads = 256, rpw = 1;
+    if (a->out_tm_f16) {
+      rows = a->seq_len % 16 == 0 ? 16 : 8;
+      threads = rows >= 16 ? 512 : 256;
+      rpw = rows / (threads / 32);
+    }
     const int blocks = (a->m + rows - 1) / rows;
     const size_t tile = a->out_tm_f16 ? (size_t)rows * a->n * 2 : 0;
 #define M2_LNW(TO, VI) do { \
       if (tile > 48 * 1024) M2_CUDA(cudaFuncSetAttribute(add_layernorm_warp_kernel<TO, VI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile)); \
-      add_layernorm_warp_kernel<TO, VI><<<blocks, 32 * rows, tile, st>>>( \
+      add_layernorm_warp_kernel<TO, VI><<<blocks, threads, tile, st>>>( \
       (const __nv_bfloat16*)a->a, a->lda, (const __nv_bfloat16*)a->b, a->ldb, a->weight, a->bias, a->eps, \
       (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m, \
-      (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len); } while (0)
+      (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len, rpw); } while (0)
 #define M2_LNW_VI(TO) switch (a->n / 256) { case 1: M2_LNW(TO, 1); break; case 2: M2_LNW(TO, 2); break; \
       case 3: M2_LNW(TO, 3); break; case 4: M2_LNW(TO, 4); break; case 5: M2_LNW(TO, 5); break; \
       case 6: M2_LNW(TO, 6); break; case 7: M2_LNW(TO, 7); break; default: M2_LNW(TO, 8); break; }
@@ -342,7 +374,7 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
     M2_LAUNCH_CHECK("add_layernorm_warp_kernel");
     return M2_OK;
   }
-  M2_REQUIRE(a->out_bf16 == nullptr && a->out_tm_f16 == nullptr, M2_ERR_UNSUPPORTED,
+  M2_REQUIRE(a->out != nullptr && a->out_bf16 == nullptr && a->out_tm_f16 == nullptr, M2_ERR_UNSUPPORTED,
              "m2_add_layernorm_fwd: the bf16 copy needs bf16 inputs, n a multiple of 256 (<= 2048) and 16-byte aligned rows");
   const size_t smem = (size_t)a->n * sizeof(float);
   const int threads = a->n >= 1024 ? 256 : 128;

@@ -58,7 +58,7 @@ constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int SMEM_BUDGET = 200 * 1024;
 
 struct Params {
-  int M, p, q, nb_out, pair_off, ntn, ntm, ksteps, total_tiles, out_cols;
+  int M, p, q, nb_out, pair_off, ntn, ntm, ksteps, total_tiles, out_cols, wide_out;
   void* out; long long ldo;
   const float* bias;
 };
@@ -201,9 +201,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint32_t n = pack_bf16(__uint_as_float(b[j]), __uint_as_float(b[j + 1]));
             float a0, a1;
             gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
-            const uint32_t act = pack_bf16(a0, a1);           // GELU output cast to bf16
-            v0 = __uint_as_float(act << 16) * __uint_as_float(n << 16);
-            v1 = __uint_as_float(act & 0xFFFF0000u) * __uint_as_float(n & 0xFFFF0000u);
+            packed[j >> 1] = bf2_mul(pack_bf16(a0, a1), n);   // GELU output cast to bf16, times the linear half
+            continue;
           } else {
             v0 = bf16r(__uint_as_float(a[j]));
             v1 = bf16r(__uint_as_float(a[j + 1]));
@@ -215,10 +214,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           packed[j >> 1] = pack_bf16(v0, v1);
         }
         if (row < P.M) {
-          uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+          if (P.wide_out) {                     // one full 32-byte sector per thread
+            stg256(orow + c0, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>(orow + c0);
 #pragma unroll
-          for (int v = 0; v < 2; ++v)
-            dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+            for (int v = 0; v < 2; ++v)
+              dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          }
         }
       }
       tc::tc_fence_before();
@@ -295,6 +298,7 @@ int blockdiag_tc_launch(const m2_blockdiag_args* a, cudaStream_t st) {
   P.ntn = a->q / bn; P.ntm = (a->m + BM - 1) / BM; P.ksteps = a->p / BK;
   P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->out_features;
   P.out = a->out; P.ldo = a->ldo; P.bias = a->bias;
+  P.wide_out = m2_aligned(a->out, 32) && a->ldo % 16 == 0 && a->q % 16 == 0;   // 32-byte stores are legal
   switch (bn) {
     case 256: return launch<256, false>(tmA, tmB, P, st);
     case 192: return launch<192, false>(tmA, tmB, P, st);
@@ -316,6 +320,7 @@ int glu_tc_launch(const m2_glu_args* a, cudaStream_t st) {
   P.ntn = q / 128; P.ntm = (a->m + BM - 1) / BM; P.ksteps = p / BK;
   P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->inter;
   P.out = a->h; P.ldo = a->ldh; P.bias = nullptr;
+  P.wide_out = m2_aligned(a->h, 32) && a->ldh % 16 == 0 && q % 16 == 0;
   return launch<128, true>(tmA, tmB, P, st);
 }
 

@@ -113,19 +113,26 @@ time_major_f16_kernel(const TS* __restrict__ src, long long ssb, long long sst, 
   __shared__ __half tile[64][66];
   const int t0 = blockIdx.x * 64, c0 = blockIdx.y * 64, b = blockIdx.z;
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
-  for (int tl = ty; tl < 64; tl += 4) {
-    float v = 0.f;
-    if (t0 + tl < L && c0 + tx < D) v = ld_as_float(src + b * ssb + (long long)(t0 + tl) * sst + (long long)(c0 + tx) * ssc);
-    tile[tl][tx] = __float2half_rn(fminf(fmaxf(v, -65504.f), 65504.f));
+  float v[16];                                             // all loads of the thread in flight at once
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int tl = ty + 4 * i;
+    v[i] = 0.f;
+    if (t0 + tl < L && c0 + tx < D) v[i] = ld_as_float(src + b * ssb + (long long)(t0 + tl) * sst + (long long)(c0 + tx) * ssc);
   }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) tile[ty + 4 * i][tx] = __float2half_rn(fminf(fmaxf(v[i], -65504.f), 65504.f));
   __syncthreads();
-  for (int cl = ty; cl < 64; cl += 4)
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int cl = ty + 4 * i;
     if (t0 + tx < L && c0 + cl < D) dst[(long long)(c0 + cl) * dsc + b * dsb + t0 + tx] = tile[tx][cl];
+  }
 }
 
 // ---------------------------------------------------------------------------------------
 struct Params {
-  int B, L, D, nf, nbt, units, nsub, yu_bf16;
+  int B, L, D, nf, nbt, units, nsub, yu_bf16, wide_out;
   const float* sw; const float* sb;
   const float* spec[2];
   __nv_bfloat16* out; long long osb, osc;
@@ -334,7 +341,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           xa = x0; xb = x1;
           const uint32_t g = pack_bf2(c0, c1);                                          // short conv output, bf16
           const uint32_t y = pack_bf2(__uint_as_float(d1[2 * i]) * is1, __uint_as_float(d1[2 * i + 1]) * is1);
-          const uint32_t res = pack_bf2(bf_lo(y) * bf_lo(g), bf_hi(y) * bf_hi(g));      // y * x2, bf16
+          const uint32_t res = bf2_mul(y, g);                                           // y * x2, bf16
           if (P.nf == 2) {
             float u0 = __uint_as_float(d2[2 * i]) * is2, u1 = __uint_as_float(d2[2 * i + 1]) * is2;
             if (P.yu_bf16) { const uint32_t ur = pack_bf2(u0, u1); u0 = bf_lo(ur); u1 = bf_hi(ur); }
@@ -345,9 +352,13 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
         if (b < P.B) {
           if (t0 + 16 <= P.L) {
-            uint4* dst = reinterpret_cast<uint4*>(orow + t0);
-            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            if (P.wide_out) {
+              stg256(orow + t0, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(orow + t0);
+              dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+              dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+            }
           } else {                                        // L is a multiple of 8: one full half remains
             *reinterpret_cast<uint4*>(orow + t0) = make_uint4(o[0], o[1], o[2], o[3]);
           }
@@ -400,8 +411,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           float cx0, cv0, cx1, cv1;
           f2_unpack(c0, cx0, cv0);
           f2_unpack(c1, cx1, cv1);
-          const uint32_t g0 = pack_bf2(cx0, cv0), g1 = pack_bf2(cx1, cv1);   // short conv outputs, bf16
-          const uint32_t pr = pack_bf2(bf_lo(g0) * bf_hi(g0), bf_lo(g1) * bf_hi(g1));   // v * x1, bf16
+          const uint32_t pr = bf2_mul(pack_bf2(cx0, cx1), pack_bf2(cv0, cv1));   // bf16 conv outputs, v * x1 in bf16
           float a0 = bf_lo(pr), a1 = bf_hi(pr);
           if (tbase + 2 * i >= P.L) a0 = 0.f;             // the long convolution sees zeros past L
           if (tbase + 2 * i + 1 >= P.L) a1 = 0.f;
@@ -493,6 +503,7 @@ int longconv_tz_launch(const m2_longconv_args* a, cudaStream_t st) {
   P.sw = a->short_w; P.sb = a->short_b;
   P.spec[0] = a->spec[0]; P.spec[1] = a->spec[1];
   P.out = (__nv_bfloat16*)a->out; P.osb = a->out_sb; P.osc = a->out_sc;
+  P.wide_out = m2_aligned(a->out, 32) && a->out_sb % 16 == 0 && a->out_sc % 16 == 0;   // 32-byte stores are legal
 
   CUtensorMap tmX, tmU;
   {

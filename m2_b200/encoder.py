@@ -99,9 +99,9 @@ class M2BertLayer(nn.Module):
             hyena_training_additions=config.hyena_training_additions)
         self.mlp = BertGatedLinearUnitMLP(config)
 
-    def forward(self, hidden_states):
+    def forward(self, hidden_states, copies_only=False):
         mixed, _ = self.attention(hidden_states)
-        return self.mlp(mixed)
+        return self.mlp(mixed, copies_only=copies_only)
 
 
 class M2BertEncoder(nn.Module):
@@ -113,8 +113,13 @@ class M2BertEncoder(nn.Module):
         # the mask does not enter the Monarch-Mixer layers (the reference passes it to the
         # layer, which ignores it on this branch); padded positions are mixed like any other
         outs = []
-        for layer in self.layer:
-            hidden_states = layer(hidden_states)
+        for i, layer in enumerate(self.layer):
+            # between two of these layers only the next mixer reads the hidden state, through the
+            # copies the MLP's LayerNorm writes for it; the float32 tensor is materialised when
+            # somebody else will see it (last layer, or every layer on request)
+            inner = (i + 1 < len(self.layer) and not output_all_encoded_layers
+                     and not self.layer[i + 1].attention.hyena_training_additions)
+            hidden_states = layer(hidden_states, copies_only=inner)
             if output_all_encoded_layers:
                 outs.append(hidden_states)
         if not output_all_encoded_layers:

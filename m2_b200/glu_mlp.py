@@ -34,7 +34,11 @@ class BertGatedLinearUnitMLP(nn.Module):
         self.dropout = nn.Dropout(config.hidden_dropout_prob)
         self.layernorm = nn.LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
 
-    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+    def forward(self, hidden_states: torch.Tensor, copies_only: bool = False) -> torch.Tensor:
+        """copies_only (used by M2BertEncoder between layers): when the next mixer of this shape
+        reads nothing but the bf16 and time-major fp16 copies of the output, skip the float32
+        tensor and return the bf16 copy as the hidden state (tagged with the dtype the
+        reference's tensor would have, which decides one rounding point in the mixer)."""
         from .sequence_mixer import _check_forward_only
         _check_forward_only(self, hidden_states)
         if self.training and self.dropout.p > 0:
@@ -61,9 +65,14 @@ class BertGatedLinearUnitMLP(nn.Module):
             # a following mixer of this shape runs the Toeplitz-GEMM convolution, which reads the
             # layer input as a time-major fp16 operand: written here too
             tm = torch.empty((x.shape[2], x.shape[0], x.shape[1]), dtype=torch.float16, device=x.device)
+        skip = copies_only and tm is not None
         y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,
-                                  self.layernorm.eps, out_dtype, bf16_copy=aug, tm_copy=tm)
-        y = y.reshape(x.shape)
+                                  self.layernorm.eps, None if skip else out_dtype, bf16_copy=aug, tm_copy=tm)
+        if skip:
+            y = aug[:, :x.shape[-1]].view(x.shape[0], x.shape[1], x.shape[2])
+            y._m2_src_dtype = out_dtype
+        else:
+            y = y.reshape(x.shape)
         if aug is not None:
             y._m2_aug = aug
         if tm is not None:

@@ -245,7 +245,7 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm
     """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype.  bf16_copy:
     optional (m, >= n) bf16 tensor that receives the result rounded to bf16.  tm_copy: optional
     (n, B, L) fp16 tensor with B * L = m that receives the result time-major (see
-    time_major_f16)."""
+    time_major_f16).  out_dtype=None writes only the copies and returns None."""
     _need_cuda(a2d, b2d)
     if a2d.stride(-1) != 1:
         a2d = a2d.contiguous()
@@ -253,7 +253,7 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm
         b2d = b2d.contiguous()
     m, n = a2d.shape
     assert b2d.shape == a2d.shape and b2d.dtype == a2d.dtype
-    out = torch.empty((m, n), dtype=out_dtype, device=a2d.device)
+    out = torch.empty((m, n), dtype=out_dtype, device=a2d.device) if out_dtype is not None else None
     w, bb = _f32c(weight), _f32c(bias)
     a = _lib.AddLayernormArgs()
     a.m, a.n, a.in_dtype = m, n, _dt(a2d)
@@ -261,7 +261,11 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm
     a.a, a.lda = a2d.data_ptr(), max(a2d.stride(0), n)
     a.b, a.ldb = b2d.data_ptr(), max(b2d.stride(0), n)
     a.weight, a.bias, a.eps = w.data_ptr(), bb.data_ptr(), float(eps)
-    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    if out is not None:
+        a.out, a.ldo = out.data_ptr(), out.stride(0)
+    else:
+        assert bf16_copy is not None, "out_dtype=None (copies only) needs bf16_copy"
+        a.ldo = n
     if bf16_copy is not None:
         assert bf16_copy.dtype == torch.bfloat16 and bf16_copy.stride(-1) == 1 and bf16_copy.shape[0] == m
         a.out_bf16, a.ld_bf16 = bf16_copy.data_ptr(), bf16_copy.stride(0)

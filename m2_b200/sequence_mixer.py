@@ -155,7 +155,7 @@ class MonarchMixerSequenceMixing(nn.Module):
                              u_t.permute(1, 2, 0) if u_t is not None else None,
                              self.short_filter.weight, self.short_filter.bias, specs, None,
                              kind=3, bf16_rounding=True, out=buf[:D].view(D, B, L).permute(1, 2, 0),
-                             yu_bf16=ures is not None and ures.dtype == torch.bfloat16)
+                             yu_bf16=ures is not None and getattr(ures, "_m2_src_dtype", ures.dtype) == torch.bfloat16)
             return torch.matmul(buf.t(), w_out.t()).view(B, L, D)
 
     def forward(self, u, **kwargs):

@@ -274,17 +274,20 @@ def test_encoder_small_fp32_and_bf16():
     assert O.parity_error(npy(yb), npy(ref)) < TOL_BF16
 
 
-def test_encoder_80m_shape_bf16():
-    """Two 80M-shaped layers at the benchmark's L against the stock-op path.
+@pytest.mark.parametrize("B", [16, 64])
+def test_encoder_80m_shape_bf16(B):
+    """Two 80M-shaped layers at the benchmark's L against the stock-op path (batch 16 runs the
+    FFT tensor-core convolution, batch 64 the Toeplitz-GEMM one).
 
     The path's tolerance (2e-2) is a per-layer statement: each layer is checked on the SAME
     input the stock-op path saw.  Run free, the differences of layer 1 (single bf16 rounding
     flips of intermediates, which any two correct implementations show) are re-mixed by
     layer 2, so the stacked output is held to twice the per-layer bound.
     """
-    cfg = dict(kind="encoder", seed=43, B=16, L=128, D=768, I=3072, layers=2, vocab=30528, order=128)
+    cfg = dict(kind="encoder", seed=43, B=B, L=128, D=768, I=3072, layers=2, vocab=30528, order=128)
     model, sd = _encoder(cfg, DEV)
-    ids_t = torch.from_numpy(np.random.default_rng(1).integers(0, 30528, size=(16, 128))).to(DEV)
+    assert ops.longconv_kind_batch(B, 128, torch.bfloat16, 768) == (3 if B >= 64 else 1)
+    ids_t = torch.from_numpy(np.random.default_rng(1).integers(0, 30528, size=(B, 128))).to(DEV)
     sdt = to_torch(sd, DEV)
     with torch.autocast("cuda", dtype=torch.bfloat16):
         h_ref = T.embeddings_forward(sdt, ids_t)
@@ -301,6 +304,26 @@ def test_encoder_80m_shape_bf16():
             h_ref = nxt_ref
         y, _ = model(ids_t)
     assert O.parity_error(npy(y), npy(h_ref)) < 2 * TOL_BF16
+
+
+def test_graphed_forward_matches_eager():
+    """A captured forward replays the same kernels: bit-identical to the eager call, also on
+    new token ids copied into the static input."""
+    from m2_b200 import GraphedForward
+    cfg = dict(kind="encoder", seed=44, B=64, L=128, D=256, I=1024, layers=2, vocab=1000, order=32)
+    model, _ = _encoder(cfg, DEV)
+    rng = np.random.default_rng(2)
+    ids = [torch.from_numpy(rng.integers(0, 1000, size=(64, 128))).to(DEV) for _ in range(2)]
+    graphed = GraphedForward(model, ids[0])
+    assert graphed.launches_per_replay > 0
+    for t in ids:
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            want, _ = model(t)
+        got, _ = graphed(t)
+        assert torch.equal(got, want)
+    with pytest.raises(RuntimeError):
+        graphed(ids[0][:8])
+    assert ops.device_status() == 0
 
 
 # ---- error behaviour -----------------------------------------------------------------
