@@ -231,6 +231,9 @@ typedef struct {
   void* out; long long ldo;
   void* out_bf16; long long ld_bf16;
   void* out_tm_f16; long long tm_sb, tm_sc; int seq_len;
+  int bf16_pad_cols;   /* > 0: also write columns n .. n+bf16_pad_cols of each out_bf16 row as
+                          [1, 0, 0, ...] -- the constant column through which a following GEMM adds
+                          its bias (a multiple of 8, at most 256) */
 } m2_add_layernorm_args;
 
 int m2_add_layernorm_fwd(const m2_add_layernorm_args* args, void* stream);

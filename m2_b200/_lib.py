@@ -77,6 +77,7 @@ class AddLayernormArgs(C.Structure):
         ("out", C.c_void_p), ("ldo", C.c_longlong),
         ("out_bf16", C.c_void_p), ("ld_bf16", C.c_longlong),
         ("out_tm_f16", C.c_void_p), ("tm_sb", C.c_longlong), ("tm_sc", C.c_longlong), ("seq_len", C.c_int),
+        ("bf16_pad_cols", C.c_int),
     ]
 
 

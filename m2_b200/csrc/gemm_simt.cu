@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(512)
 add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* b, long long ldb,
                           const float* __restrict__ w, const float* __restrict__ bias, float eps, TO* out,
                           long long ldo, __nv_bfloat16* out2, long long ld2, int m,
-                          __half* out_tm, long long tm_sb, long long tm_sc, int seq_len, int rpw) {
+                          __half* out_tm, long long tm_sb, long long tm_sc, int seq_len, int rpw, int pad2) {
   extern __shared__ __half ln_tile[];   // [rows of the block][n] fp16, only with out_tm
   const int wib = threadIdx.x >> 5, nw = blockDim.x >> 5, lane = threadIdx.x & 31;
   constexpr int n = VI * 256;
@@ -177,6 +177,8 @@ add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bflo
       sum += v[i][2 * j] + v[i][2 * j + 1];
     }
   }
+  if (out2 && lane * 8 < pad2)      // columns n .. n + pad2 of the bf16 copy: [1, 0, 0, ...]
+    *reinterpret_cast<uint4*>(out2 + (long long)warp * ld2 + n + lane * 8) = make_uint4(lane == 0 ? 0x3F80u : 0u, 0u, 0u, 0u);
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   const float mean = sum / n;
   float sq = 0.f;
@@ -336,6 +338,9 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
              "m2_add_layernorm_fwd: NULL tensor pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   M2_REQUIRE(a->out_bf16 == nullptr || a->ld_bf16 >= a->n, M2_ERR_ARG, "m2_add_layernorm_fwd: ld_bf16 smaller than the row");
+  M2_REQUIRE(a->bf16_pad_cols >= 0 && a->bf16_pad_cols % 8 == 0 && a->bf16_pad_cols <= 256 &&
+             (a->bf16_pad_cols == 0 || (a->out_bf16 && a->ld_bf16 >= a->n + a->bf16_pad_cols)), M2_ERR_ARG,
+             "m2_add_layernorm_fwd: bf16_pad_cols must be a multiple of 8 (<= 256) that fits the rows of out_bf16");
   const bool vec = a->in_dtype == M2_BF16 && a->n % 256 == 0 && a->n <= 2048 && a->lda % 8 == 0 && a->ldb % 8 == 0 &&
                    m2_aligned(a->a, 16) && m2_aligned(a->b, 16) && m2_aligned(a->out, 16) && a->ldo % 8 == 0 &&
                    m2_aligned(a->weight, 16) && m2_aligned(a->bias, 16) &&
@@ -364,7 +369,7 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
       add_layernorm_warp_kernel<TO, VI><<<blocks, threads, tile, st>>>( \
       (const __nv_bfloat16*)a->a, a->lda, (const __nv_bfloat16*)a->b, a->ldb, a->weight, a->bias, a->eps, \
       (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m, \
-      (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len, rpw); } while (0)
+      (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len, rpw, a->bf16_pad_cols); } while (0)
 #define M2_LNW_VI(TO) switch (a->n / 256) { case 1: M2_LNW(TO, 1); break; case 2: M2_LNW(TO, 2); break; \
       case 3: M2_LNW(TO, 3); break; case 4: M2_LNW(TO, 4); break; case 5: M2_LNW(TO, 5); break; \
       case 6: M2_LNW(TO, 6); break; case 7: M2_LNW(TO, 7); break; default: M2_LNW(TO, 8); break; }

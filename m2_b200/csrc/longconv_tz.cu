@@ -40,7 +40,12 @@ constexpr int RAW_BYTES = TB * RAW_ROW;        // 10 KB
 constexpr int OP_BYTES = TB * TW * 2;          // 8 KB: [128 x 32] fp16 operand in core-matrix order
 constexpr int OP_LBO = TB * 16, OP_SBO = 128;  // K-adjacent core matrices 2 KB apart, row groups 128 B
 constexpr int STAGE_BYTES = 2 * RAW_BYTES + OP_BYTES;
-constexpr int NST = 4, NA1 = 3, NX2 = 4;
+#ifndef TZ_NST
+#define TZ_NST 4
+#define TZ_NA1 3
+#define TZ_XSETS 1
+#endif
+constexpr int NST = TZ_NST, NA1 = TZ_NA1, XSETS = TZ_XSETS, NX2 = 4 * XSETS;   // x2 slots: XSETS units of four
 constexpr int STRIP_ROWS = 240;
 constexpr int STRIP_BYTES = STRIP_ROWS * 32;   // 16 fp16 per row
 constexpr int STRIP_FLOATS = STRIP_BYTES / 4;
@@ -163,6 +168,17 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
+// Role timing for kernel tuning: built only with -DM2_TZ_TIMING; one thread per role adds the
+// clock cycles it spent in each phase to a device array.
+#ifdef M2_TZ_TIMING
+__device__ unsigned long long g_tz_cycles[16];
+#define TZ_T0() long long tz_prev_ = clock64()
+#define TZ_MARK(cond, i) do { if (cond) { long long n_ = clock64(); atomicAdd(&g_tz_cycles[i], (unsigned long long)(n_ - tz_prev_)); tz_prev_ = n_; } } while (0)
+#else
+#define TZ_T0() do {} while (0)
+#define TZ_MARK(cond, i) do {} while (0)
+#endif
+
 // warp-uniform bounded wait: every lane polls, the warp leaves together
 #define TZ_WAIT(bar, parity, why) \
   if (!__all_sync(0xffffffffu, tc::mbar_wait((bar), (parity), abort_flag, (why)))) break
@@ -247,33 +263,41 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       for (int unit = u_first; unit < u_last && ok; ++unit, ++ui) {
         const int c = unit / P.nbt, b0 = (unit % P.nbt) * TB;
         for (int j = 0; j < P.nsub; ++j) {
-          if (!tc::mbar_wait(x2_empty + j, (ui & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          tc::mbar_expect_tx(x2_full + j, RAW_BYTES);
-          tc::tma_load_3d(smem + OFF_X2 + j * RAW_BYTES, &tmX, x2_full + j, TW * j - HALO, b0, P.D + c);
+          const int sl = 4 * (ui % XSETS) + j;             // units rotate through the slot sets
+          if (!tc::mbar_wait(x2_empty + sl, ((ui / XSETS) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          tc::mbar_expect_tx(x2_full + sl, RAW_BYTES);
+          tc::tma_load_3d(smem + OFF_X2 + sl * RAW_BYTES, &tmX, x2_full + sl, TW * j - HALO, b0, P.D + c);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------- MMA issuer -------------------------
     if (lane == 0) {
+      // both operands fp16: kind::f16 with a bf16 A and an fp16 B is an illegal instruction on
+      // sm_100a, so v*x1 (bf16 by the reference's arithmetic) is converted, exactly, to fp16
       constexpr uint32_t idesc = tc::make_idesc(TB, 128, 0);
       int it = 0, epoch = -1, prev_c = -1, ui = 0;
       bool ok = true;
+      TZ_T0();
       for (int unit = u_first; unit < u_last && ok; ++unit, ++ui) {
         const int c = unit / P.nbt;
         if (c != prev_c) {
           prev_c = c; ++epoch;
           if (!tc::mbar_wait(strip_full + (epoch & 1), (epoch >> 1) & 1, abort_flag, tc::ST_TIMEOUT_TMA)) break;
         }
+        TZ_MARK(true, 0);
         const int p = epoch & 1, acc = ui & 1;
         if (!tc::mbar_wait(tmem_empty + acc, ((ui >> 1) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) break;
+        TZ_MARK(true, 1);
         tc::tc_fence_after();
         const uint32_t tacc = tmem_base + acc * 256;
         const uint32_t strip0 = tc::smem_u32(smem + OFF_STRIP + (2 * p) * STRIP_BYTES);
         for (int j = 0; j < P.nsub; ++j, ++it) {
           const int s = it % NST, a = it % NA1;
           if (!tc::mbar_wait(full_main + s, (it / NST) & 1, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
+          TZ_MARK(true, 2);
           if (!tc::mbar_wait(a1_full + a, (it / NA1) & 1, abort_flag, tc::ST_TIMEOUT_MMA)) { ok = false; break; }
+          TZ_MARK(true, 3);
           tc::tc_fence_after();
           const uint32_t a1 = tc::smem_u32(smem + OFF_A1 + a * OP_BYTES);
           const uint32_t uop = tc::smem_u32(smem + s * STAGE_BYTES + 2 * RAW_BYTES);
@@ -289,6 +313,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           }
           tc::mma_commit(empty_main + s);
           tc::mma_commit(a1_empty + a);
+          TZ_MARK(true, 4);
         }
         if (!ok) break;
         tc::mma_commit(tmem_full + acc);
@@ -301,6 +326,8 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int hh = (warp - CTRL_WARPS) >> 2;             // which half of the time axis
     const int r = quarter * 32 + lane;
     int ui = 0;
+    const bool tz_me = (warp == CTRL_WARPS && lane == 0);
+    TZ_T0();
     for (int unit = u_first; unit < u_last; ++unit, ++ui) {
       const int c = unit / P.nbt, b = (unit % P.nbt) * TB + r;
       const int acc = ui & 1;
@@ -309,7 +336,9 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const int ch = P.D + c;
       const float w0 = bf16r(__ldg(P.sw + 3 * ch)), w1 = bf16r(__ldg(P.sw + 3 * ch + 1)),
                   w2 = bf16r(__ldg(P.sw + 3 * ch + 2)), wb = bf16r(__ldg(P.sb + ch));
+      TZ_MARK(tz_me, 5);
       TZ_WAIT(tmem_full + acc, (ui >> 1) & 1, tc::ST_TIMEOUT_EPI);
+      TZ_MARK(tz_me, 6);
       tc::tc_fence_after();
       const uint32_t tacc = tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* orow = P.out + (long long)c * P.osc + (long long)b * P.osb;
@@ -318,9 +347,11 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       for (int k = 0; k < 4; ++k) {
         const int t0 = 64 * hh + 16 * k;
         if (t0 >= P.L) break;
-        const int j = t0 / TW, toff = t0 % TW;
+        const int j = 4 * (ui % XSETS) + t0 / TW, toff = t0 % TW;   // x2 slot
         if ((k & 1) == 0) {
-          if (!__all_sync(0xffffffffu, tc::mbar_wait(x2_full + j, ui & 1, abort_flag, tc::ST_TIMEOUT_TMA))) { ok = false; break; }
+          TZ_MARK(tz_me, 5);
+          if (!__all_sync(0xffffffffu, tc::mbar_wait(x2_full + j, (ui / XSETS) & 1, abort_flag, tc::ST_TIMEOUT_TMA))) { ok = false; break; }
+          TZ_MARK(tz_me, 7);
         }
         uint32_t d1[16], d2[16];
         tc::tmem_ld16(tacc + t0, d1);
@@ -382,6 +413,8 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int r = (pw & 3) * 32 + lane, h = pw >> 2;      // batch row, which 16 of the stage's 32 steps
     int it = 0;
     bool ok = true;
+    const bool tz_me = (pw == 0 && lane == 0);
+    TZ_T0();
     for (int unit = u_first; unit < u_last && ok; ++unit) {
       const int c = unit / P.nbt;
       const int cv = 2 * P.D + c;
@@ -392,7 +425,9 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const f32x2 wb = f2_pack(bf16r(__ldg(P.sb + c)), bf16r(__ldg(P.sb + cv)));
       for (int j = 0; j < P.nsub; ++j, ++it) {
         const int s = it % NST, a = it % NA1;
+        TZ_MARK(tz_me, 8);
         if (!__all_sync(0xffffffffu, tc::mbar_wait(full_main + s, (it / NST) & 1, abort_flag, tc::ST_TIMEOUT_TMA))) { ok = false; break; }
+        TZ_MARK(tz_me, 9);
         const uint32_t xrow = tc::smem_u32(smem + s * STAGE_BYTES) + r * RAW_ROW + h * 32;
         const uint32_t hx = lds32(xrow + 12), hv = lds32(xrow + RAW_BYTES + 12);
         const uint4 x0 = lds128(xrow + 16), x1 = lds128(xrow + 32);
@@ -412,12 +447,18 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           f2_unpack(c0, cx0, cv0);
           f2_unpack(c1, cx1, cv1);
           const uint32_t pr = bf2_mul(pack_bf2(cx0, cx1), pack_bf2(cv0, cv1));   // bf16 conv outputs, v * x1 in bf16
-          float a0 = bf_lo(pr), a1 = bf_hi(pr);
-          if (tbase + 2 * i >= P.L) a0 = 0.f;             // the long convolution sees zeros past L
-          if (tbase + 2 * i + 1 >= P.L) a1 = 0.f;
-          aw[i] = pack_h2_sat(a0, a1);
+          aw[i] = pack_h2_sat(bf_lo(pr), bf_hi(pr));
         }
+        if (tbase + 16 > P.L) {                           // the long convolution sees zeros past L
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (tbase + 2 * i >= P.L) aw[i] = 0u;
+            else if (tbase + 2 * i + 1 >= P.L) aw[i] &= 0x0000ffffu;
+          }
+        }
+        TZ_MARK(tz_me, 8);
         if (!__all_sync(0xffffffffu, tc::mbar_wait(a1_empty + a, ((it / NA1) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY))) { ok = false; break; }
+        TZ_MARK(tz_me, 10);
         const uint32_t dst = tc::smem_u32(smem + OFF_A1 + a * OP_BYTES) + (2 * h) * OP_LBO + r * 16;
         sts128(dst, aw[0], aw[1], aw[2], aw[3]);
         sts128(dst + OP_LBO, aw[4], aw[5], aw[6], aw[7]);
@@ -449,6 +490,16 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 #undef TZ_WAIT
 
 }  // namespace tz
+
+#ifdef M2_TZ_TIMING
+extern "C" int m2_debug_tz_cycles(unsigned long long* out, int reset) {
+  unsigned long long z[16] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, tz::g_tz_cycles, sizeof(z));
+  if (reset) cudaMemcpyToSymbol(tz::g_tz_cycles, z, sizeof(z));
+  return 0;
+}
+#endif
 
 int longconv_tz_supported(int batch, int seq_len, m2_dtype act_dtype) {
   return act_dtype == M2_BF16 && seq_len >= 16 && seq_len <= 128 && seq_len % 8 == 0 && batch >= 64;

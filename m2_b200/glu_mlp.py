@@ -58,8 +58,8 @@ class BertGatedLinearUnitMLP(nn.Module):
         if dt == torch.bfloat16 and x.dim() == 3 and x.shape[-1] % 256 == 0 and x.shape[-1] <= 2048:
             # the next layer's in_linear reads this output cast to bf16: write that copy here
             # (with the bias column its GEMM uses) instead of leaving it to a separate cast pass
-            from .sequence_mixer import make_augmented
-            aug = make_augmented(x2.shape[0], x.shape[-1], x.device)
+            from .sequence_mixer import _PAD
+            aug = torch.empty((x2.shape[0], x.shape[-1] + _PAD), dtype=torch.bfloat16, device=x.device)
         tm = None
         if aug is not None and ops.longconv_kind_batch(x.shape[0], x.shape[1], torch.bfloat16, x.shape[2]) == 3:
             # a following mixer of this shape runs the Toeplitz-GEMM convolution, which reads the
@@ -67,7 +67,8 @@ class BertGatedLinearUnitMLP(nn.Module):
             tm = torch.empty((x.shape[2], x.shape[0], x.shape[1]), dtype=torch.float16, device=x.device)
         skip = copies_only and tm is not None
         y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,
-                                  self.layernorm.eps, None if skip else out_dtype, bf16_copy=aug, tm_copy=tm)
+                                  self.layernorm.eps, None if skip else out_dtype, bf16_copy=aug, tm_copy=tm,
+                                  fill_pad=aug is not None)
         if skip:
             y = aug[:, :x.shape[-1]].view(x.shape[0], x.shape[1], x.shape[2])
             y._m2_src_dtype = out_dtype

@@ -241,7 +241,7 @@ def blockdiag_glu_fwd(x2d, wg, inter):
     return h
 
 
-def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm_copy=None):
+def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm_copy=None, fill_pad=False):
     """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype.  bf16_copy:
     optional (m, >= n) bf16 tensor that receives the result rounded to bf16.  tm_copy: optional
     (n, B, L) fp16 tensor with B * L = m that receives the result time-major (see
@@ -269,6 +269,8 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm
     if bf16_copy is not None:
         assert bf16_copy.dtype == torch.bfloat16 and bf16_copy.stride(-1) == 1 and bf16_copy.shape[0] == m
         a.out_bf16, a.ld_bf16 = bf16_copy.data_ptr(), bf16_copy.stride(0)
+        if fill_pad:     # columns n.. of the copy become [1, 0, 0, ...] (see sequence_mixer.make_augmented)
+            a.bf16_pad_cols = bf16_copy.shape[1] - n
     if tm_copy is not None:
         assert tm_copy.dtype == torch.float16 and tm_copy.dim() == 3 and tm_copy.stride(2) == 1
         assert tm_copy.shape[0] == n and tm_copy.shape[1] * tm_copy.shape[2] == m

@@ -494,8 +494,13 @@ def test_add_layernorm_time_major_copy(B, L, D):
     bias = torch.randn(D, generator=g).to(DEV)
     plain = ops.add_layernorm_fwd(a, b, w, bias, 1e-12, torch.float32)
     tm = torch.full((D, B, L), float("nan"), dtype=torch.float16, device=DEV)
-    aug = torch.empty((B * L, D + 64), dtype=torch.bfloat16, device=DEV)
-    out = ops.add_layernorm_fwd(a, b, w, bias, 1e-12, torch.float32, bf16_copy=aug, tm_copy=tm)
+    aug = torch.full((B * L, D + 64), float("nan"), dtype=torch.bfloat16, device=DEV)
+    out = ops.add_layernorm_fwd(a, b, w, bias, 1e-12, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=True)
     assert torch.equal(out, plain)
     assert torch.equal(aug[:, :D], plain.bfloat16())
+    assert bool((aug[:, D] == 1).all()) and bool((aug[:, D + 1:] == 0).all())   # the bias column and its padding
     assert torch.equal(tm, ops.time_major_f16(plain.view(B, L, D)))
+    # copies only: no float32 output at all
+    aug2, tm2 = torch.empty_like(aug), torch.empty_like(tm)
+    assert ops.add_layernorm_fwd(a, b, w, bias, 1e-12, None, bf16_copy=aug2, tm_copy=tm2, fill_pad=True) is None
+    assert torch.equal(aug2, aug) and torch.equal(tm2, tm)
