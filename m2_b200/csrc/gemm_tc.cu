@@ -186,30 +186,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const int col0 = kb * P.q + nt * BN;
       const uint32_t tacc = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* orow = out + (long long)row * P.ldo + col0;
+      if constexpr (GLU) {
+        // two register sets: the next 16 columns are on their way from tensor memory while the
+        // GELU of the current ones runs (the store keeps the arithmetic ahead of the wait)
+        constexpr int NCH = CW / 16;
+        uint32_t a[2][16], b[2][16];
+        tc::tmem_ld16(tacc + chalf * CW, a[0]);
+        tc::tmem_ld16(tacc + BN + chalf * CW, b[0]);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < NCH; ++ch) {
+          const int cur = ch & 1, c0 = chalf * CW + 16 * ch;
+          if (ch + 1 < NCH) {
+            tc::tmem_ld16(tacc + c0 + 16, a[cur ^ 1]);
+            tc::tmem_ld16(tacc + BN + c0 + 16, b[cur ^ 1]);
+          }
+          uint32_t packed[8];
+#pragma unroll
+          for (int j = 0; j < 16; j += 2) {
+            const uint32_t g = pack_bf16(__uint_as_float(a[cur][j]), __uint_as_float(a[cur][j + 1]));
+            const uint32_t n = pack_bf16(__uint_as_float(b[cur][j]), __uint_as_float(b[cur][j + 1]));
+            float a0, a1;
+            gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
+            packed[j >> 1] = bf2_mul(pack_bf16(a0, a1), n);   // GELU output cast to bf16, times the linear half
+          }
+          if (row < P.M) {
+            if (P.wide_out) {                   // one full 32-byte sector per thread
+              stg256(orow + c0, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+              dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+              dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            }
+          }
+          if (ch + 1 < NCH) tc::tmem_ld_wait();
+        }
+      } else {
 #pragma unroll 1
       for (int c0 = chalf * CW; c0 < (chalf + 1) * CW; c0 += 16) {
-        uint32_t a[16], b[16];
+        uint32_t a[16];
         tc::tmem_ld16(tacc + c0, a);
-        if (GLU) tc::tmem_ld16(tacc + BN + c0, b);
         tc::tmem_ld_wait();
         uint32_t packed[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
-          float v0, v1;
-          if (GLU) {
-            const uint32_t g = pack_bf16(__uint_as_float(a[j]), __uint_as_float(a[j + 1]));
-            const uint32_t n = pack_bf16(__uint_as_float(b[j]), __uint_as_float(b[j + 1]));
-            float a0, a1;
-            gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
-            packed[j >> 1] = bf2_mul(pack_bf16(a0, a1), n);   // GELU output cast to bf16, times the linear half
-            continue;
-          } else {
-            v0 = bf16r(__uint_as_float(a[j]));
-            v1 = bf16r(__uint_as_float(a[j + 1]));
-            if (P.bias) {
-              v0 += bf16r(__ldg(P.bias + col0 + c0 + j));
-              v1 += bf16r(__ldg(P.bias + col0 + c0 + j + 1));
-            }
+          float v0 = bf16r(__uint_as_float(a[j]));
+          float v1 = bf16r(__uint_as_float(a[j + 1]));
+          if (P.bias) {
+            v0 += bf16r(__ldg(P.bias + col0 + c0 + j));
+            v1 += bf16r(__ldg(P.bias + col0 + c0 + j + 1));
           }
           packed[j >> 1] = pack_bf16(v0, v1);
         }
@@ -223,6 +248,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               dst[v] = make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
           }
         }
+      }
       }
       tc::tc_fence_before();
       tc::mbar_arrive(tempty + buf);
