@@ -15,9 +15,9 @@
 // A persistent CTA (one per SM) walks units of (channel, 128 batch rows), time in four stages
 // of 32 steps:
 //   warp 0      TMA: raw x1 / v rows (with an 8-column halo so the 3-tap conv sees t-2, t-1; the
-//               halo of the first stage starts at t = -8 and reads the causal zeros) and the
-//               fp16 residual input, already in core-matrix order through a 4-D box
-//   warp 2      TMA: raw x2 rows for the epilogue
+//               halo of the first stage starts at t = -8 and reads the causal zeros), filter strips
+//   warp 2      TMA: the fp16 residual input in 64-step tiles (128-byte swizzled rows, the MMA's
+//               K-major operand layout) and raw x2 rows for the epilogue
 //   warps 11-18 short conv on x1 and v, v*x1 with the reference's bf16 rounding points, fp16
 //               A-operand tile (generic proxy -> fence -> mbarrier)
 //   warp 1      one thread issues the MMAs of both filters into one of two TMEM accumulator sets
@@ -39,24 +39,23 @@ constexpr int RAW_ROW = (TW + HALO) * 2;       // 80 bytes: rows 16 (mod 128) ap
 constexpr int RAW_BYTES = TB * RAW_ROW;        // 10 KB
 constexpr int OP_BYTES = TB * TW * 2;          // 8 KB: [128 x 32] fp16 operand in core-matrix order
 constexpr int OP_LBO = TB * 16, OP_SBO = 128;  // K-adjacent core matrices 2 KB apart, row groups 128 B
-constexpr int STAGE_BYTES = 2 * RAW_BYTES + OP_BYTES;
-#ifndef TZ_NST
-#define TZ_NST 4
-#define TZ_NA1 3
-#define TZ_XSETS 1
-#endif
-constexpr int NST = TZ_NST, NA1 = TZ_NA1, XSETS = TZ_XSETS, NX2 = 4 * XSETS;   // x2 slots: XSETS units of four
+constexpr int STAGE_BYTES = 2 * RAW_BYTES;     // raw x1 and v rows of one stage
+constexpr int U_BYTES = TB * 128;              // [128 rows x 64 steps] fp16, 128-byte swizzled rows (TMA box)
+constexpr int NST = 4, NA1 = 3, XSETS = 1, NX2 = 4 * XSETS, NU = 3;   // x2 slots: XSETS units of four
 constexpr int STRIP_ROWS = 240;
 constexpr int STRIP_BYTES = STRIP_ROWS * 32;   // 16 fp16 per row
 constexpr int STRIP_FLOATS = STRIP_BYTES / 4;
 constexpr int STRIP_LBO = 128, STRIP_SBO = 256;
 
-constexpr int OFF_A1 = NST * STAGE_BYTES;
+constexpr int OFF_U = NST * STAGE_BYTES;       // every offset is a multiple of 1024 (swizzle anchor of the U tiles)
+constexpr int OFF_A1 = OFF_U + NU * U_BYTES;
 constexpr int OFF_X2 = OFF_A1 + NA1 * OP_BYTES;
 constexpr int OFF_STRIP = OFF_X2 + NX2 * RAW_BYTES;
 constexpr int OFF_BAR = OFF_STRIP + 4 * STRIP_BYTES;
-constexpr int NBARS = 2 * NST + 2 * NA1 + 2 * NX2 + 4 + 4;
-constexpr int SMEM_BYTES = OFF_BAR + NBARS * 8 + 16 + 128;
+constexpr int NBARS = 2 * NST + 2 * NU + 2 * NA1 + 2 * NX2 + 4 + 4;
+constexpr int SMEM_BYTES = OFF_BAR + NBARS * 8 + 16 + 1024;
+static_assert(OFF_U % 1024 == 0 && U_BYTES % 1024 == 0, "U tiles must sit on 1024-byte boundaries");
+static_assert(SMEM_BYTES <= 232448, "shared memory budget");
 
 constexpr int CTRL_WARPS = 3, EPI_WARPS = 8, P_WARPS = 8;
 constexpr int THREADS = 32 * (CTRL_WARPS + EPI_WARPS + P_WARPS);
@@ -186,11 +185,13 @@ __device__ unsigned long long g_tz_cycles[16];
 __global__ void __launch_bounds__(THREADS, 1)
 longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmU, const Params P) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
-  uint64_t* full_main = bars;                  // stage landed (TMA bytes)
-  uint64_t* empty_main = full_main + NST;      // 8 worker warps + 1 MMA commit
-  uint64_t* a1_full = empty_main + NST;        // 8 worker warps
+  uint64_t* full_main = bars;                  // raw x1 / v rows of the stage landed (TMA bytes)
+  uint64_t* empty_main = full_main + NST;      // raw rows consumed: 8 worker warps
+  uint64_t* u_full = empty_main + NST;         // 64 steps of the residual operand landed (only the MMA thread waits)
+  uint64_t* u_empty = u_full + NU;             // ... consumed: 1 MMA commit
+  uint64_t* a1_full = u_empty + NU;            // 8 worker warps
   uint64_t* a1_empty = a1_full + NA1;          // 1 MMA commit
   uint64_t* x2_full = a1_empty + NA1;          // TMA bytes
   uint64_t* x2_empty = x2_full + NX2;          // 4 epilogue warps
@@ -203,7 +204,8 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < NST; ++s) { tc::mbar_init(full_main + s, 1); tc::mbar_init(empty_main + s, P_WARPS + 1); }
+    for (int s = 0; s < NST; ++s) { tc::mbar_init(full_main + s, 1); tc::mbar_init(empty_main + s, P_WARPS); }
+    for (int s = 0; s < NU; ++s) { tc::mbar_init(u_full + s, 1); tc::mbar_init(u_empty + s, 1); }
     for (int a = 0; a < NA1; ++a) { tc::mbar_init(a1_full + a, P_WARPS); tc::mbar_init(a1_empty + a, 1); }
     for (int j = 0; j < NX2; ++j) { tc::mbar_init(x2_full + j, 1); tc::mbar_init(x2_empty + j, EPI_WARPS / 2); }
     for (int p = 0; p < 2; ++p) {
@@ -233,6 +235,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     if (lane == 0) {
       int it = 0, epoch = -1, prev_c = -1;
       bool ok = true;
+      TZ_T0();
       for (int unit = u_first; unit < u_last && ok; ++unit) {
         const int c = unit / P.nbt, b0 = (unit % P.nbt) * TB;
         if (c != prev_c) {
@@ -246,12 +249,13 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
         for (int j = 0; j < P.nsub; ++j, ++it) {
           const int s = it % NST;
+          TZ_MARK(true, 11);
           if (!tc::mbar_wait(empty_main + s, ((it / NST) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          TZ_MARK(true, 12);
           unsigned char* st = smem + s * STAGE_BYTES;
-          tc::mbar_expect_tx(full_main + s, 2 * RAW_BYTES + (P.nf == 2 ? OP_BYTES : 0));
+          tc::mbar_expect_tx(full_main + s, 2 * RAW_BYTES);
           tc::tma_load_3d(st, &tmX, full_main + s, TW * j - HALO, b0, c);
           tc::tma_load_3d(st + RAW_BYTES, &tmX, full_main + s, TW * j - HALO, b0, 2 * P.D + c);
-          if (P.nf == 2) tc::tma_load_4d(st + 2 * RAW_BYTES, &tmU, full_main + s, 0, b0, (TW / 8) * j, c);
         }
       }
     }
@@ -259,9 +263,19 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     // ------------------------- TMA: raw x2 rows for the epilogue -------------------------
     if (lane == 0) {
       bool ok = true;
-      int ui = 0;
+      int ui = 0, it = 0;
       for (int unit = u_first; unit < u_last && ok; ++unit, ++ui) {
         const int c = unit / P.nbt, b0 = (unit % P.nbt) * TB;
+        // the residual operand of the unit in tiles of 64 steps, rows of 128 bytes (a 16-byte-row
+        // box in core-matrix order would cost the TMA unit eight times the requests) ...
+        for (int k = 0; k < (P.nsub + 1) / 2 && P.nf == 2; ++k, ++it) {
+          const int s = it % NU;
+          if (!tc::mbar_wait(u_empty + s, ((it / NU) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          tc::mbar_expect_tx(u_full + s, U_BYTES);
+          tc::tma_load_3d(smem + OFF_U + s * U_BYTES, &tmU, u_full + s, 64 * k, b0, c);
+        }
+        if (!ok) break;
+        // ... then the x2 rows its epilogue reads
         for (int j = 0; j < P.nsub; ++j) {
           const int sl = 4 * (ui % XSETS) + j;             // units rotate through the slot sets
           if (!tc::mbar_wait(x2_empty + sl, ((ui / XSETS) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
@@ -276,7 +290,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       // both operands fp16: kind::f16 with a bf16 A and an fp16 B is an illegal instruction on
       // sm_100a, so v*x1 (bf16 by the reference's arithmetic) is converted, exactly, to fp16
       constexpr uint32_t idesc = tc::make_idesc(TB, 128, 0);
-      int it = 0, epoch = -1, prev_c = -1, ui = 0;
+      int it = 0, ut = 0, epoch = -1, prev_c = -1, ui = 0;
       bool ok = true;
       TZ_T0();
       for (int unit = u_first; unit < u_last && ok; ++unit, ++ui) {
@@ -294,13 +308,15 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         const uint32_t strip0 = tc::smem_u32(smem + OFF_STRIP + (2 * p) * STRIP_BYTES);
         for (int j = 0; j < P.nsub; ++j, ++it) {
           const int s = it % NST, a = it % NA1;
-          if (!tc::mbar_wait(full_main + s, (it / NST) & 1, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
+          if (P.nf == 2 && (j & 1) == 0 &&
+              !tc::mbar_wait(u_full + ut % NU, (ut / NU) & 1, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
           TZ_MARK(true, 2);
           if (!tc::mbar_wait(a1_full + a, (it / NA1) & 1, abort_flag, tc::ST_TIMEOUT_MMA)) { ok = false; break; }
           TZ_MARK(true, 3);
           tc::tc_fence_after();
           const uint32_t a1 = tc::smem_u32(smem + OFF_A1 + a * OP_BYTES);
-          const uint32_t uop = tc::smem_u32(smem + s * STAGE_BYTES + 2 * RAW_BYTES);
+          // 64-step tile of the residual operand: K step q of it starts 32 q bytes into the swizzled rows
+          const uint64_t udesc = tc::smem_desc_k_sw128(tc::smem_u32(smem + OFF_U + (ut % NU) * U_BYTES)) + 4 * (j & 1);
 #pragma unroll
           for (int ks = 0; ks < TW / 16; ++ks) {
             const int kk = (TW / 16) * j + ks;
@@ -308,10 +324,10 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             tc::mma_ss(tacc, tc::smem_desc_k_nosw(a1 + ks * 2 * OP_LBO, OP_LBO, OP_SBO),
                        tc::smem_desc_k_nosw(strip0 + boff, STRIP_LBO, STRIP_SBO), idesc, kk ? 1u : 0u);
             if (P.nf == 2)
-              tc::mma_ss(tacc + 128, tc::smem_desc_k_nosw(uop + ks * 2 * OP_LBO, OP_LBO, OP_SBO),
+              tc::mma_ss(tacc + 128, udesc + 2 * ks,
                          tc::smem_desc_k_nosw(strip0 + STRIP_BYTES + boff, STRIP_LBO, STRIP_SBO), idesc, kk ? 1u : 0u);
           }
-          tc::mma_commit(empty_main + s);
+          if (P.nf == 2 && ((j & 1) || j == P.nsub - 1)) { tc::mma_commit(u_empty + ut % NU); ++ut; }
           tc::mma_commit(a1_empty + a);
           TZ_MARK(true, 4);
         }
@@ -478,6 +494,8 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     // give loads that were issued before the abort a bounded time to land
     for (int s = 0; s < NST; ++s)
       for (uint32_t i = 0; i < 4096 && !tc::mbar_try_wait(full_main + s, 0) && !tc::mbar_try_wait(full_main + s, 1); ++i) {}
+    for (int s = 0; s < NU; ++s)
+      for (uint32_t i = 0; i < 4096 && !tc::mbar_try_wait(u_full + s, 0) && !tc::mbar_try_wait(u_full + s, 1); ++i) {}
     for (int j = 0; j < NX2; ++j)
       for (uint32_t i = 0; i < 4096 && !tc::mbar_try_wait(x2_full + j, 0) && !tc::mbar_try_wait(x2_full + j, 1); ++i) {}
   }
@@ -518,13 +536,13 @@ int spectrum_kind3_launch(int D, int L, const float* k, const float* bias, float
 }
 
 static int tz_encode(CUtensorMap* map, CUtensorMapDataType dt, int rank, const void* base, const cuuint64_t* dims,
-                     const cuuint64_t* strides, const cuuint32_t* box) {
+                     const cuuint64_t* strides, const cuuint32_t* box, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_NONE) {
   m2_encode_tiled_fn enc;
   int rc = m2_get_encode_fn(&enc);
   if (rc) return rc;
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(map, dt, rank, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                   swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return m2_set_error(M2_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
   return M2_OK;
 }
@@ -565,12 +583,11 @@ int longconv_tz_launch(const m2_longconv_args* a, cudaStream_t st) {
     if (rc) return rc;
   }
   if (P.nf == 2) {
-    // (8 steps, batch row, group of 8 steps, channel): a box lands as [step group][row][8 steps],
-    // the core-matrix order of an un-swizzled K-major operand
-    const cuuint64_t dims[4] = {8, (cuuint64_t)P.B, (cuuint64_t)P.L / 8, (cuuint64_t)P.D};
-    const cuuint64_t strides[3] = {(cuuint64_t)a->u_sb * 2, 16, (cuuint64_t)a->u_sc * 2};
-    const cuuint32_t box[4] = {8, TB, TW / 8, 1};
-    int rc = tz_encode(&tmU, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, a->u, dims, strides, box);
+    // rows of 64 steps (128 bytes) with the 128-byte swizzle: the K-major operand layout of the MMA
+    const cuuint64_t dims[3] = {(cuuint64_t)P.L, (cuuint64_t)P.B, (cuuint64_t)P.D};
+    const cuuint64_t strides[2] = {(cuuint64_t)a->u_sb * 2, (cuuint64_t)a->u_sc * 2};
+    const cuuint32_t box[3] = {64, TB, 1};
+    int rc = tz_encode(&tmU, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a->u, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   } else {
     tmU = tmX;
