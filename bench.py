@@ -319,9 +319,12 @@ def main():
         alg_bytes = 10.0 * B * D * L + 16.0 * D * L          # bf16 activations, two filters
         peak, peak_src = measured_peaks()
         achieved = alg_bytes / (conv_ms * 1e-3) / 1e9 if conv_ms else None
+        # DRAM bytes per launch of that kernel from the ncu captures summarised under profiles/
+        # (dram__bytes_read.sum + dram__bytes_write.sum); None where no capture of the shape exists
+        traffic = {"m2bert80m-L128": 247.2e6, "m2bert80m-L8192": 564e6}.get(name)
         roof = {"bound": "hbm", "kernel": "m2_longconv_fwd", "achieved": achieved, "peak": peak,
                 "peak_source": peak_src, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
-                "traffic": None, "launch_ms": conv_ms, "algorithmic_bytes_per_launch": alg_bytes,
+                "traffic": traffic, "launch_ms": conv_ms, "algorithmic_bytes_per_launch": alg_bytes,
                 "kernel_ms_per_step": {k: prof.mean_ms(k) * prof.count(k) / prof_steps for k in prof.names()}}
         cpu = None
         if not args.no_cpu_baseline:

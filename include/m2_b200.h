@@ -211,7 +211,9 @@ int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);
  * out = LayerNorm(a + b) over the last dimension (float32 statistics).
  * Replaces `self.layernorm(hidden_states + residual_connection)`, bert/src/bert_layers.py:506.
  * a, b (m, n) of `in_dtype` (the sum is rounded to bf16 first when in_dtype is M2_BF16, as a
- * bf16 tensor add does); out (m, n) of `out_dtype`; weight/bias float32 (n).
+ * bf16 tensor add does); out (m, n) of `out_dtype`; weight/bias float32 (n).  b may be NULL
+ * (plain LayerNorm(a), e.g. the embeddings' LayerNorm, bert/src/bert_layers.py:131-252) when n is
+ * a multiple of 256 up to 2048 and rows are 16-byte aligned.
  * out_bf16 (optional, may be NULL): a second copy of the result rounded to bf16, row stride
  * ld_bf16 -- what the next layer's in_linear reads under autocast (its cast of the float32
  * LayerNorm output), written here instead of by a separate cast pass.  With out_bf16 given,

@@ -147,9 +147,9 @@ add_layernorm_kernel(const TI* a, long long lda, const TI* b, long long ldb, con
 
 // Vectorised variant: one warp per row, the row held in registers (n a multiple of 256 up to
 // 2048, 16-byte aligned rows); optional second output rounded to bf16.
-template <typename TO, int VI>
+template <typename TI, typename TO, int VI>
 __global__ void __launch_bounds__(512)
-add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bfloat16* b, long long ldb,
+add_layernorm_warp_kernel(const TI* a, long long lda, const TI* b, long long ldb,
                           const float* __restrict__ w, const float* __restrict__ bias, float eps, TO* out,
                           long long ldo, __nv_bfloat16* out2, long long ld2, int m,
                           __half* out_tm, long long tm_sb, long long tm_sc, int seq_len, int rpw, int pad2) {
@@ -161,20 +161,34 @@ add_layernorm_warp_kernel(const __nv_bfloat16* a, long long lda, const __nv_bflo
   const int trow = ri * nw + wib;                                   // row within the block
   const long long warp = (long long)blockIdx.x * nw * rpw + trow;   // row of the tensor
   if (warp >= m) break;
-  const uint4* pa = reinterpret_cast<const uint4*>(a + (long long)warp * lda);
-  const uint4* pb = reinterpret_cast<const uint4*>(b + (long long)warp * ldb);
   float v[VI][8];
   float sum = 0.f;
+  if constexpr (sizeof(TI) == 2) {
+    const uint4* pa = reinterpret_cast<const uint4*>(a + (long long)warp * lda);
+    const uint4* pb = b ? reinterpret_cast<const uint4*>(b + (long long)warp * ldb) : nullptr;
 #pragma unroll
-  for (int i = 0; i < VI; ++i) {
-    const uint4 xa = __ldg(pa + i * 32 + lane), xb = __ldg(pb + i * 32 + lane);
-    const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
+    for (int i = 0; i < VI; ++i) {
+      const uint4 xa = __ldg(pa + i * 32 + lane), xb = pb ? __ldg(pb + i * 32 + lane) : make_uint4(0, 0, 0, 0);
+      const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      // bf16 + bf16 -> bf16 (the residual add of two bf16 tensors), then float32 statistics
-      v[i][2 * j] = bf16r(__uint_as_float(wa[j] << 16) + __uint_as_float(wb[j] << 16));
-      v[i][2 * j + 1] = bf16r(__uint_as_float(wa[j] & 0xffff0000u) + __uint_as_float(wb[j] & 0xffff0000u));
-      sum += v[i][2 * j] + v[i][2 * j + 1];
+      for (int j = 0; j < 4; ++j) {
+        // bf16 + bf16 -> bf16 (the residual add of two bf16 tensors), then float32 statistics
+        v[i][2 * j] = bf16r(__uint_as_float(wa[j] << 16) + __uint_as_float(wb[j] << 16));
+        v[i][2 * j + 1] = bf16r(__uint_as_float(wa[j] & 0xffff0000u) + __uint_as_float(wb[j] & 0xffff0000u));
+        sum += v[i][2 * j] + v[i][2 * j + 1];
+      }
+    }
+  } else {
+    const float4* pa = reinterpret_cast<const float4*>(a + (long long)warp * lda);
+    const float4* pb = b ? reinterpret_cast<const float4*>(b + (long long)warp * ldb) : nullptr;
+#pragma unroll
+    for (int i = 0; i < VI; ++i) {
+      const int q = (i * 32 + lane) * 2;
+      const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 a0 = __ldg(pa + q), a1 = __ldg(pa + q + 1), b0 = pb ? __ldg(pb + q) : z, b1 = pb ? __ldg(pb + q + 1) : z;
+      const float s8[8] = {a0.x + b0.x, a0.y + b0.y, a0.z + b0.z, a0.w + b0.w, a1.x + b1.x, a1.y + b1.y, a1.z + b1.z, a1.w + b1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { v[i][j] = s8[j]; sum += s8[j]; }
     }
   }
   if (out2 && lane * 8 < pad2)      // columns n .. n + pad2 of the bf16 copy: [1, 0, 0, ...]
@@ -334,20 +348,22 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
   M2_REQUIRE(a->m >= 0 && a->n > 0, M2_ERR_ARG, "m2_add_layernorm_fwd: bad sizes m=%d n=%d", a->m, a->n);
   M2_REQUIRE(a->n <= 12288, M2_ERR_UNSUPPORTED, "m2_add_layernorm_fwd: n > 12288");
   if (a->m == 0) return M2_OK;
-  M2_REQUIRE(a->a && a->b && a->weight && a->bias && (a->out || a->out_bf16), M2_ERR_ARG,
+  M2_REQUIRE(a->a && a->weight && a->bias && (a->out || a->out_bf16), M2_ERR_ARG,
              "m2_add_layernorm_fwd: NULL tensor pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   M2_REQUIRE(a->out_bf16 == nullptr || a->ld_bf16 >= a->n, M2_ERR_ARG, "m2_add_layernorm_fwd: ld_bf16 smaller than the row");
   M2_REQUIRE(a->bf16_pad_cols >= 0 && a->bf16_pad_cols % 8 == 0 && a->bf16_pad_cols <= 256 &&
              (a->bf16_pad_cols == 0 || (a->out_bf16 && a->ld_bf16 >= a->n + a->bf16_pad_cols)), M2_ERR_ARG,
              "m2_add_layernorm_fwd: bf16_pad_cols must be a multiple of 8 (<= 256) that fits the rows of out_bf16");
-  const bool vec = a->in_dtype == M2_BF16 && a->n % 256 == 0 && a->n <= 2048 && a->lda % 8 == 0 && a->ldb % 8 == 0 &&
+  const int epv = a->in_dtype == M2_BF16 ? 8 : 4;        // elements per 16 bytes of input
+  const bool vec = (a->in_dtype == M2_BF16 || (a->in_dtype == M2_F32 && a->out_dtype == M2_F32)) &&
+                   a->n % 256 == 0 && a->n <= 2048 && a->lda % epv == 0 && (!a->b || a->ldb % epv == 0) &&
                    m2_aligned(a->a, 16) && m2_aligned(a->b, 16) && m2_aligned(a->out, 16) && a->ldo % 8 == 0 &&
                    m2_aligned(a->weight, 16) && m2_aligned(a->bias, 16) &&
                    (a->out_bf16 == nullptr || (m2_aligned(a->out_bf16, 16) && a->ld_bf16 % 8 == 0));
   if (a->out_tm_f16) {
     M2_REQUIRE(vec, M2_ERR_UNSUPPORTED,
-               "m2_add_layernorm_fwd: the time-major copy needs bf16 inputs, n a multiple of 256 (<= 2048) and 16-byte aligned rows");
+               "m2_add_layernorm_fwd: the time-major copy needs n a multiple of 256 (<= 2048), 16-byte aligned rows and bf16 inputs (or float32 inputs with a float32 output)");
     M2_REQUIRE(a->seq_len > 0 && a->seq_len % 8 == 0 && a->m % a->seq_len == 0, M2_ERR_ARG,
                "m2_add_layernorm_fwd: the time-major copy needs m = batch * seq_len rows with seq_len a multiple of 8");
     M2_REQUIRE(m2_aligned(a->out_tm_f16, 16) && a->tm_sb % 8 == 0 && a->tm_sc % 8 == 0, M2_ERR_ALIGN,
@@ -364,10 +380,11 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
     }
     const int blocks = (a->m + rows - 1) / rows;
     const size_t tile = a->out_tm_f16 ? (size_t)rows * a->n * 2 : 0;
-#define M2_LNW(TO, VI) do { \
-      if (tile > 48 * 1024) M2_CUDA(cudaFuncSetAttribute(add_layernorm_warp_kernel<TO, VI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile)); \
-      add_layernorm_warp_kernel<TO, VI><<<blocks, threads, tile, st>>>( \
-      (const __nv_bfloat16*)a->a, a->lda, (const __nv_bfloat16*)a->b, a->ldb, a->weight, a->bias, a->eps, \
+#define M2_LNW(TO, VI) do { if (a->in_dtype == M2_F32) M2_LNW2(float, float, VI); else M2_LNW2(__nv_bfloat16, TO, VI); } while (0)
+#define M2_LNW2(TI, TO, VI) do { \
+      if (tile > 48 * 1024) M2_CUDA(cudaFuncSetAttribute(add_layernorm_warp_kernel<TI, TO, VI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile)); \
+      add_layernorm_warp_kernel<TI, TO, VI><<<blocks, threads, tile, st>>>( \
+      (const TI*)a->a, a->lda, (const TI*)a->b, a->ldb, a->weight, a->bias, a->eps, \
       (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m, \
       (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len, rpw, a->bf16_pad_cols); } while (0)
 #define M2_LNW_VI(TO) switch (a->n / 256) { case 1: M2_LNW(TO, 1); break; case 2: M2_LNW(TO, 2); break; \
@@ -376,11 +393,13 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
     if (a->out_dtype == M2_F32) { M2_LNW_VI(float) } else { M2_LNW_VI(__nv_bfloat16) }
 #undef M2_LNW_VI
 #undef M2_LNW
+#undef M2_LNW2
     M2_LAUNCH_CHECK("add_layernorm_warp_kernel");
     return M2_OK;
   }
   M2_REQUIRE(a->out != nullptr && a->out_bf16 == nullptr && a->out_tm_f16 == nullptr, M2_ERR_UNSUPPORTED,
-             "m2_add_layernorm_fwd: the bf16 copy needs bf16 inputs, n a multiple of 256 (<= 2048) and 16-byte aligned rows");
+             "m2_add_layernorm_fwd: the copies need n a multiple of 256 (<= 2048) and 16-byte aligned rows");
+  M2_REQUIRE(a->b != nullptr, M2_ERR_UNSUPPORTED, "m2_add_layernorm_fwd: b = NULL needs n a multiple of 256 (<= 2048) and 16-byte aligned rows");
   const size_t smem = (size_t)a->n * sizeof(float);
   const int threads = a->n >= 1024 ? 256 : 128;
 #define M2_LN(TI, TO) add_layernorm_kernel<TI, TO><<<a->m, threads, smem, st>>>( \

@@ -18,6 +18,7 @@ import torch
 import torch.nn as nn
 
 from .glu_mlp import BertGatedLinearUnitMLP
+from .hyena_filter import _autocast_bf16
 from .sequence_mixer import MonarchMixerSequenceMixing
 
 
@@ -80,7 +81,29 @@ class M2BertEmbeddings(nn.Module):
             if position_ids is None:
                 position_ids = self.position_ids[:, :L]
             e = e + self.position_embeddings(position_ids)
+        if (e.is_cuda and e.dim() == 3 and e.dtype == torch.float32 and not torch.is_grad_enabled()
+                and _autocast_bf16()
+                and not (self.training and self.dropout.p > 0) and e.shape[-1] % 256 == 0 and e.shape[-1] <= 2048):
+            # the first mixer reads bf16 / time-major fp16 copies of this output: have the LayerNorm
+            # kernel write them instead of separate cast, fill and transpose passes
+            return self._layernorm_with_copies(e)
         return self.dropout(self.LayerNorm(e))
+
+    def _layernorm_with_copies(self, e):
+        from . import ops
+        from .sequence_mixer import _PAD
+        B, L, D = e.shape
+        aug = torch.empty((B * L, D + _PAD), dtype=torch.bfloat16, device=e.device)
+        tm = None
+        if ops.longconv_kind_batch(B, L, torch.bfloat16, D) == 3:
+            tm = torch.empty((D, B, L), dtype=torch.float16, device=e.device)
+        y = ops.add_layernorm_fwd(e.reshape(B * L, D), None, self.LayerNorm.weight, self.LayerNorm.bias,
+                                  self.LayerNorm.eps, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=True)
+        y = y.view(B, L, D)
+        y._m2_aug = aug
+        if tm is not None:
+            y._m2_tm = tm
+        return y
 
 
 class M2BertLayer(nn.Module):

@@ -242,24 +242,25 @@ def blockdiag_glu_fwd(x2d, wg, inter):
 
 
 def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm_copy=None, fill_pad=False):
-    """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype.  bf16_copy:
+    """LayerNorm(a + b) over the last dimension; a, b (m, n) of the same dtype (b may be None).  bf16_copy:
     optional (m, >= n) bf16 tensor that receives the result rounded to bf16.  tm_copy: optional
     (n, B, L) fp16 tensor with B * L = m that receives the result time-major (see
     time_major_f16).  out_dtype=None writes only the copies and returns None."""
     _need_cuda(a2d, b2d)
     if a2d.stride(-1) != 1:
         a2d = a2d.contiguous()
-    if b2d.stride(-1) != 1:
+    if b2d is not None and b2d.stride(-1) != 1:
         b2d = b2d.contiguous()
     m, n = a2d.shape
-    assert b2d.shape == a2d.shape and b2d.dtype == a2d.dtype
+    assert b2d is None or (b2d.shape == a2d.shape and b2d.dtype == a2d.dtype)
     out = torch.empty((m, n), dtype=out_dtype, device=a2d.device) if out_dtype is not None else None
     w, bb = _f32c(weight), _f32c(bias)
     a = _lib.AddLayernormArgs()
     a.m, a.n, a.in_dtype = m, n, _dt(a2d)
     a.out_dtype = M2_BF16 if out_dtype == torch.bfloat16 else M2_F32
     a.a, a.lda = a2d.data_ptr(), max(a2d.stride(0), n)
-    a.b, a.ldb = b2d.data_ptr(), max(b2d.stride(0), n)
+    if b2d is not None:
+        a.b, a.ldb = b2d.data_ptr(), max(b2d.stride(0), n)
     a.weight, a.bias, a.eps = w.data_ptr(), bb.data_ptr(), float(eps)
     if out is not None:
         a.out, a.ldo = out.data_ptr(), out.stride(0)

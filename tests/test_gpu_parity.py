@@ -504,3 +504,22 @@ def test_add_layernorm_time_major_copy(B, L, D):
     aug2, tm2 = torch.empty_like(aug), torch.empty_like(tm)
     assert ops.add_layernorm_fwd(a, b, w, bias, 1e-12, None, bf16_copy=aug2, tm_copy=tm2, fill_pad=True) is None
     assert torch.equal(aug2, aug) and torch.equal(tm2, tm)
+
+
+def test_layernorm_float32_input_with_copies():
+    """The embeddings' LayerNorm: float32 input, no second addend, copies for the first mixer."""
+    B, L, D = 4, 32, 768
+    g = torch.Generator().manual_seed(9)
+    e = torch.randn((B * L, D), generator=g).to(DEV)
+    w = torch.randn(D, generator=g).to(DEV)
+    bias = torch.randn(D, generator=g).to(DEV)
+    ref = torch.nn.functional.layer_norm(e, (D,), w, bias, 1e-12)
+    aug = torch.full((B * L, D + 64), float("nan"), dtype=torch.bfloat16, device=DEV)
+    tm = torch.full((D, B, L), float("nan"), dtype=torch.float16, device=DEV)
+    out = ops.add_layernorm_fwd(e, None, w, bias, 1e-12, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=True)
+    assert O.parity_error(npy(out), npy(ref)) < 1e-5
+    assert torch.equal(aug[:, :D], out.bfloat16()) and bool((aug[:, D] == 1).all()) and bool((aug[:, D + 1:] == 0).all())
+    assert torch.equal(tm, ops.time_major_f16(out.view(B, L, D)))
+    e2 = torch.randn((B * L, D), generator=g).to(DEV)
+    both = ops.add_layernorm_fwd(e, e2, w, bias, 1e-12, torch.float32)
+    assert O.parity_error(npy(both), npy(torch.nn.functional.layer_norm(e + e2, (D,), w, bias, 1e-12))) < 1e-5
