@@ -52,6 +52,7 @@ class M2BertConfig:
     hyena_filter_dropout: float = 0.0
     hyena_filter_order: int = 128
     hyena_training_additions: bool = False
+    pool_all: bool = False           # pooler: mean over unmasked positions instead of the first token
 
 
 class M2BertEmbeddings(nn.Module):
@@ -150,14 +151,38 @@ class M2BertEncoder(nn.Module):
         return outs
 
 
-class M2BertModel(nn.Module):
-    """Embeddings + encoder; forward(input_ids, ...) -> (sequence_output, None)."""
+class M2BertPooler(nn.Module):
+    """dense + tanh on the first token, or (config.pool_all) on the mean of the unmasked positions
+    (reference BertPooler, bert/src/bert_layers.py:816-859; its `sequence_token_planting` variant is not
+    carried over).  State-dict keys `dense.weight`, `dense.bias` as in the reference."""
 
-    def __init__(self, config, check_finite=False):
+    def __init__(self, config):
+        super().__init__()
+        self.dense = nn.Linear(config.hidden_size, config.hidden_size)
+        self.activation = nn.Tanh()
+        self.pool_all = config.pool_all
+
+    def forward(self, hidden_states, pool=True, mask=None):
+        if not self.pool_all:
+            first = hidden_states[:, 0] if pool else hidden_states
+            return self.activation(self.dense(first))
+        if mask is None:
+            raise ValueError("pool_all needs the attention mask")
+        mask = mask.to(hidden_states.dtype)
+        mean = (hidden_states * mask.unsqueeze(-1)).sum(dim=1) / mask.sum(dim=1, keepdim=True)
+        return self.activation(self.dense(mean))
+
+
+class M2BertModel(nn.Module):
+    """Embeddings + encoder (+ pooler); forward(input_ids, ...) -> (sequence_output, pooled_output or None),
+    the reference BertModel's pair (bert/src/bert_layers.py:899-919)."""
+
+    def __init__(self, config, check_finite=False, add_pooling_layer=False):
         super().__init__()
         self.config = config
         self.embeddings = M2BertEmbeddings(config)
         self.encoder = M2BertEncoder(config)
+        self.pooler = M2BertPooler(config) if add_pooling_layer else None
         self.check_finite = check_finite
 
     def forward(self, input_ids, token_type_ids=None, attention_mask=None, position_ids=None,
@@ -166,4 +191,7 @@ class M2BertModel(nn.Module):
         outs = self.encoder(h, attention_mask, output_all_encoded_layers)
         if self.check_finite and not torch.isfinite(outs[-1]).all():
             raise ValueError("non-finite values in the encoder output")
-        return (outs if output_all_encoded_layers else outs[-1]), None
+        pooled = None
+        if self.pooler is not None:
+            pooled = self.pooler(outs[-1], mask=attention_mask)
+        return (outs if output_all_encoded_layers else outs[-1]), pooled

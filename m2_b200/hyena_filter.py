@@ -140,7 +140,10 @@ class HyenaFilter(OptimModule):
         for child in self.implicit_filter.children():
             for name in child.state_dict():
                 getattr(child, name)._optim = {"weight_decay": wd, "lr": lr}
+        # the reference's encoder sets these when its FlashFFTConv route is on (bert_layers.py:616-626);
+        # they are accepted and ignored: the kernels of this package are the only route
         self.flashfft = None
+        self.use_flash_fft = False
         self._cache = {}
 
     # ---- cached kernel products -------------------------------------------------------

@@ -156,3 +156,76 @@ def test_two_rank_gloo_shard_and_gather(tmp_path):
     outs = [p.communicate(timeout=120)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), outs
     assert all("ok" in o for o in outs)
+
+
+# ---- checkpoint adapters (longer maximum sequence length) -----------------------------------
+def test_expand_sequence_length_roundtrip_into_longer_model():
+    import torch
+    from m2_b200 import checkpoint
+    from m2_b200.encoder import M2BertConfig, M2BertModel
+    small = dict(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, hyena_filter_order=8,
+                 hyena_emb_dim=5, monarch_mlp_nblocks=4)
+    torch.manual_seed(0)
+    src = M2BertModel(M2BertConfig(max_position_embeddings=16, long_conv_l_max=16, **small))
+    dst = M2BertModel(M2BertConfig(max_position_embeddings=64, long_conv_l_max=64, **small))
+    sd = {"model.bert." + k: v.clone() for k, v in src.state_dict().items()}
+    sd = checkpoint.strip_prefix(sd)
+    assert set(sd) == set(src.state_dict())
+    big = checkpoint.expand_sequence_length(sd, 64)
+    # position embeddings: the old table repeated four times
+    pe = big["embeddings.position_embeddings.weight"]
+    assert pe.shape == (64, 32) and all(torch.equal(pe[16 * i:16 * (i + 1)], sd["embeddings.position_embeddings.weight"]) for i in range(4))
+    z0 = sd["encoder.layer.1.attention.filter_fn2.pos_emb.z"]
+    z = big["encoder.layer.1.attention.filter_fn2.pos_emb.z"]
+    assert z.shape == (1, 64, 5) and bool((z[:, :16] == 0).all())           # slot 0 stays zero
+    assert all(torch.equal(z[:, 16 * s:16 * (s + 1)], z0) for s in (1, 2, 3))
+    assert not any(k.endswith("pos_emb.t") or k.endswith("position_ids") for k in big)
+    before = dst.encoder.layer[0].attention.filter_fn.pos_emb.t.clone()
+    res = checkpoint.load_expanded(dst, big)
+    assert all(k.endswith("pos_emb.t") or k.endswith("position_ids") for k in res.missing_keys)
+    assert torch.equal(dst.encoder.layer[0].attention.filter_fn.pos_emb.t, before)   # the longer model's own time axis
+    assert torch.equal(dst.encoder.layer[0].attention.in_linear.weight, src.encoder.layer[0].attention.in_linear.weight)
+    # a copy that does not fit is dropped, other lengths are rejected, wrong keys are loud
+    z2 = checkpoint.expand_sequence_length(sd, 32)["encoder.layer.0.attention.filter_fn.pos_emb.z"]
+    assert z2.shape == (1, 32, 5) and torch.equal(z2[:, 16:], sd["encoder.layer.0.attention.filter_fn.pos_emb.z"])
+    with pytest.raises(ValueError):
+        checkpoint.expand_sequence_length(sd, 40)
+    big["encoder.layer.0.attention.nonsense"] = torch.zeros(1)
+    with pytest.raises(RuntimeError):
+        checkpoint.load_expanded(dst, big)
+
+
+def test_flash_fft_attribute_protocol_is_accepted():
+    """The reference's encoder pokes `flashfft` / `use_flash_fft` onto the filters
+    (bert/src/bert_layers.py:616-626); the drop-in filters accept and ignore them."""
+    from m2_b200 import HyenaFilter
+    f = HyenaFilter(16, emb_dim=5, order=8, seq_len=32, bidirectional=True)
+    assert f.flashfft is None and f.use_flash_fft is False
+    f.flashfft, f.use_flash_fft = object(), True
+    assert f.use_flash_fft is True
+
+
+def test_pooler_and_embedder_staging():
+    import torch
+    from m2_b200.embed import M2BertEmbedder
+    from m2_b200.encoder import M2BertConfig, M2BertModel, M2BertPooler
+    cfg = M2BertConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=1, hyena_filter_order=8,
+                       max_position_embeddings=16, long_conv_l_max=16, pool_all=True)
+    pooler = M2BertPooler(cfg)
+    h = torch.randn(3, 16, 32)
+    m = torch.zeros(3, 16, dtype=torch.long)
+    m[0, :5] = 1; m[1, :] = 1; m[2, :1] = 1
+    ref = torch.tanh(pooler.dense(torch.stack([h[0, :5].mean(0), h[1].mean(0), h[2, :1].mean(0)])))
+    assert torch.allclose(pooler(h, mask=m), ref, atol=1e-6)
+    cfg.pool_all = False
+    first = M2BertPooler(cfg)
+    assert torch.allclose(first(h), torch.tanh(first.dense(h[:, 0])), atol=1e-6)
+    model = M2BertModel(cfg, add_pooling_layer=True)
+    assert {"pooler.dense.weight", "pooler.dense.bias"} <= set(model.state_dict())
+    emb = M2BertEmbedder(model, max_len=16, batch_size=4)
+    emb._fill([[5, 6, 7], list(range(1, 30))])                 # short text padded, long text cut
+    assert emb._ids[0].tolist() == [5, 6, 7] + [cfg.pad_token_id] * 13 and emb._mask[0].tolist() == [1] * 3 + [0] * 13
+    assert emb._ids[1].tolist() == list(range(1, 17)) and emb._mask[1].sum() == 16
+    assert emb._mask[2].tolist() == [1] + [0] * 15             # empty rows keep a non-zero denominator
+    with pytest.raises(ValueError):
+        M2BertEmbedder(M2BertModel(cfg), max_len=16, batch_size=4)

@@ -523,3 +523,29 @@ def test_layernorm_float32_input_with_copies():
     e2 = torch.randn((B * L, D), generator=g).to(DEV)
     both = ops.add_layernorm_fwd(e, e2, w, bias, 1e-12, torch.float32)
     assert O.parity_error(npy(both), npy(torch.nn.functional.layer_norm(e + e2, (D,), w, bias, 1e-12))) < 1e-5
+
+
+def test_embedder_chunks_match_direct_calls():
+    """The host feeder (pad to one length, chunk, graph replay, pooled output) against direct model calls."""
+    from m2_b200.embed import M2BertEmbedder
+    from m2_b200.encoder import M2BertConfig, M2BertModel
+    torch.manual_seed(3)
+    cfg = M2BertConfig(vocab_size=500, hidden_size=256, intermediate_size=1024, num_hidden_layers=2, hyena_filter_order=16,
+                       max_position_embeddings=128, long_conv_l_max=128, pool_all=True)
+    model = M2BertModel(cfg, add_pooling_layer=True).to(DEV).eval()
+    rng = np.random.default_rng(4)
+    texts = [rng.integers(1, 500, size=int(n)).tolist() for n in rng.integers(3, 200, size=150)]
+    emb = M2BertEmbedder(model, max_len=128, batch_size=64)
+    got = emb.encode(texts)
+    assert got.shape == (150, 256) and np.isfinite(got).all()
+    eager = M2BertEmbedder(model, max_len=128, batch_size=64, use_graph=False).encode(texts)
+    assert np.array_equal(got, eager)
+    # direct call on the first chunk, padded by hand
+    ids = torch.zeros((64, 128), dtype=torch.long)
+    mask = torch.zeros((64, 128), dtype=torch.long)
+    for i, t in enumerate(texts[:64]):
+        n = min(len(t), 128)
+        ids[i, :n] = torch.tensor(t[:n]); mask[i, :n] = 1
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        _, pooled = model(ids.to(DEV), attention_mask=mask.to(DEV))
+    assert np.array_equal(got[:64], pooled.float().cpu().numpy())
