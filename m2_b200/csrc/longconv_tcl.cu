@@ -177,18 +177,21 @@ __device__ void write_header(float* spec, int tid, int nt) {
 // g[n] w^{n/2}, g = the filter with its wrapped half negated; bins gathered in table order.
 template <typename G>
 __global__ void __launch_bounds__(512)
-spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D) {
+spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D, int R) {
   constexpr int N = G::N, N2 = G::N2, N3 = G::N3;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, nt = blockDim.x;
   if (blockIdx.x == (unsigned)D) { write_header<G>(spec, tid, nt); return; }
   float2* s = reinterpret_cast<float2*>(smem_raw);
   const int c = blockIdx.x;
-  const float* row = kfilt + (size_t)c * N;
+  // the filter row has period R <= N ([forward taps | zeros | reversed backward taps]): its first half
+  // stays at the start, its wrapped half moves to the end of the length-N period
+  const float* row = kfilt + (size_t)c * R;
   for (int n = tid; n < N; n += nt) {
     double sn, cs;
     sincospi((double)n / N, &sn, &cs);                         // w^{n/2} = cos(pi n / N) - i sin(pi n / N)
-    const double g = (n < N / 2) ? (double)row[n] : -(double)row[n];
+    const double tap = n < R / 2 ? (double)row[n] : (n >= N - R / 2 ? (double)row[n - N + R] : 0.0);
+    const double g = (n < N / 2) ? tap : -tap;
     s[n] = make_float2((float)(g * cs), (float)(-g * sn));
   }
   __syncthreads();
@@ -224,7 +227,7 @@ spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
 // shared memory).
 template <typename G>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512)
-spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D) {
+spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D, int R) {
   namespace cg = cooperative_groups;
   constexpr int N = G::N, M = N / 2, Mh = M / 2, N2 = G::N2, N3 = G::N3, LGM = G::LG - 1;
   cg::cluster_group cluster = cg::this_cluster();
@@ -239,7 +242,10 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
     cluster.sync();
     return;
   }
-  const float* row = kfilt + (size_t)c * N;
+  const float* row = kfilt + (size_t)c * R;                    // period R <= N, see spectrum_kind2_kernel
+  auto tap = [&](int n) -> double {
+    return n < R / 2 ? (double)row[n] : (n >= N - R / 2 ? (double)row[n - N + R] : 0.0);
+  };
   // packed, pre-twisted input x[m] = z[m] W_M^{m/2}; first stage pairs m and m + Mh
   for (int i = tid; i < Mh; i += nt) {
     float2 x[2];
@@ -247,7 +253,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
     for (int e = 0; e < 2; ++e) {
       const int m = i + e * Mh;
       const double sg = (2 * m < N / 2) ? 1.0 : -1.0;          // wrapped half of the filter negated
-      const double zr = sg * (double)row[2 * m], zi = sg * (double)row[2 * m + 1];
+      const double zr = sg * tap(2 * m), zi = sg * tap(2 * m + 1);
       double sn, cs;
       sincospi((double)m / M, &sn, &cs);                       // W_M^{m/2} = cos(pi m / M) - i sin(pi m / M)
       x[e] = make_float2((float)(zr * cs + zi * sn), (float)(zi * cs - zr * sn));
@@ -750,17 +756,17 @@ using Geo16k = Geo<32, 16, 4, 2>;
 using Geo64k = Geo<64, 32, 1, 4>;
 
 template <typename G>
-static int launch_spectrum(int D, const float* k, float* spec, cudaStream_t st) {
+static int launch_spectrum(int D, int R, const float* k, float* spec, cudaStream_t st) {
   if (G::N <= 16384) {
     auto kern = spectrum_kind2_kernel<G>;
     const size_t smem = (size_t)G::N * sizeof(float2);
     M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<D + 1, 512, smem, st>>>(k, spec, D);
+    kern<<<D + 1, 512, smem, st>>>(k, spec, D, R);
   } else {
     auto kern = spectrum_kind2_cluster_kernel<G>;
     const size_t smem = (size_t)(G::N / 4) * sizeof(float2);
     M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<2 * (D + 1), 512, smem, st>>>(k, spec, D);
+    kern<<<2 * (D + 1), 512, smem, st>>>(k, spec, D, R);
   }
   M2_LAUNCH_CHECK("spectrum_kind2_kernel");
   return M2_OK;
@@ -786,8 +792,7 @@ static int launch_conv(const Params& P, cudaStream_t st) {
 // supply time-contiguous tensors
 int longconv_tcl_supported(int seq_len, m2_dtype act_dtype) {
   if (act_dtype != M2_BF16 || seq_len % 4 != 0) return 0;
-  return (seq_len > 1024 && seq_len <= 2048) || (seq_len > 4096 && seq_len <= 8192) ||
-         (seq_len > 16384 && seq_len <= 32768);
+  return seq_len > 512 && seq_len <= 32768;      // transform length 4096 up to 2048, 16384 up to 8192, else 65536
 }
 
 size_t spectrum_kind2_floats(int D, int L) {
@@ -798,16 +803,17 @@ size_t spectrum_kind2_floats(int D, int L) {
 
 int spectrum_kind2_launch(int D, int L, const float* k, float* spec, cudaStream_t st) {
   M2_REQUIRE(longconv_tcl_supported(L, M2_BF16), M2_ERR_UNSUPPORTED,
-             "m2_filter_spectrum: kind 2 covers seq_len in (1024, 2048], (4096, 8192], (16384, 32768], multiples of 4");
-  if (L <= 2048) return lcl::launch_spectrum<lcl::Geo4k>(D, k, spec, st);
-  if (L <= 8192) return lcl::launch_spectrum<lcl::Geo16k>(D, k, spec, st);
-  return lcl::launch_spectrum<lcl::Geo64k>(D, k, spec, st);
+             "m2_filter_spectrum: kind 2 covers 512 < seq_len <= 32768, multiples of 4");
+  const int R = m2_filter_row_len(L);
+  if (L <= 2048) return lcl::launch_spectrum<lcl::Geo4k>(D, R, k, spec, st);
+  if (L <= 8192) return lcl::launch_spectrum<lcl::Geo16k>(D, R, k, spec, st);
+  return lcl::launch_spectrum<lcl::Geo64k>(D, R, k, spec, st);
 }
 
 int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
   using namespace lcl;
   M2_REQUIRE(longconv_tcl_supported(a->seq_len, a->act_dtype), M2_ERR_UNSUPPORTED,
-             "m2_longconv_fwd: kind 2 needs bf16 activations and seq_len in (1024, 2048], (4096, 8192] or (16384, 32768]");
+             "m2_longconv_fwd: kind 2 needs bf16 activations and 512 < seq_len <= 32768, a multiple of 4");
   M2_REQUIRE(a->xin_st == 1 && a->out_st == 1 && (a->n_filters == 1 || a->u_st == 1), M2_ERR_UNSUPPORTED,
              "m2_longconv_fwd: kind 2 needs time-contiguous tensors ((batch, channel, time) layout)");
   M2_REQUIRE(a->xin_sc % 4 == 0 && a->xin_sb % 4 == 0 && a->out_sc % 4 == 0 && a->out_sb % 4 == 0 &&
