@@ -241,6 +241,28 @@ typedef struct {
 
 int m2_add_layernorm_fwd(const m2_add_layernorm_args* args, void* stream);
 
+/* ---------------------------------------------------------------------------------------
+ * Embeddings: out = LayerNorm((word_table[input_ids] + type_table[token_type_ids]) + pos_table[position_ids])
+ * in float32 -- the gathers, the two adds and the LayerNorm of BertEmbeddings.forward,
+ * bert/src/bert_layers.py:186-252 (dropout is the identity in eval mode) -- in one launch, with the
+ * same optional copies for the first mixer as m2_add_layernorm_fwd.
+ *   tables float32, row-major with n columns; ids int64 (m); token_type_ids NULL = type 0 everywhere;
+ *   pos_table NULL = no position term; position_ids NULL = position r % seq_len for row r.
+ *   n a multiple of 256 up to 2048.  out may be NULL when out_bf16 is given.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int m, n;
+  const float* word_table; const long long* input_ids;
+  const float* type_table; const long long* token_type_ids;
+  const float* pos_table;  const long long* position_ids;
+  const float* weight; const float* bias; float eps;
+  float* out; long long ldo;
+  void* out_bf16; long long ld_bf16; int bf16_pad_cols;
+  void* out_tm_f16; long long tm_sb, tm_sc; int seq_len;
+} m2_embed_layernorm_args;
+
+int m2_embed_layernorm_fwd(const m2_embed_layernorm_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,6 +81,19 @@ class AddLayernormArgs(C.Structure):
     ]
 
 
+class EmbedLayernormArgs(C.Structure):
+    _fields_ = [
+        ("m", C.c_int), ("n", C.c_int),
+        ("word_table", C.c_void_p), ("input_ids", C.c_void_p),
+        ("type_table", C.c_void_p), ("token_type_ids", C.c_void_p),
+        ("pos_table", C.c_void_p), ("position_ids", C.c_void_p),
+        ("weight", C.c_void_p), ("bias", C.c_void_p), ("eps", C.c_float),
+        ("out", C.c_void_p), ("ldo", C.c_longlong),
+        ("out_bf16", C.c_void_p), ("ld_bf16", C.c_longlong), ("bf16_pad_cols", C.c_int),
+        ("out_tm_f16", C.c_void_p), ("tm_sb", C.c_longlong), ("tm_sc", C.c_longlong), ("seq_len", C.c_int),
+    ]
+
+
 # name -> (restype, argtypes); every symbol include/m2_b200.h declares
 SYMBOLS = {
     "m2_version": (C.c_int, []),
@@ -98,6 +111,7 @@ SYMBOLS = {
     "m2_blockdiag_fwd": (C.c_int, [C.POINTER(BlockdiagArgs), C.c_void_p]),
     "m2_blockdiag_glu_fwd": (C.c_int, [C.POINTER(GluArgs), C.c_void_p]),
     "m2_add_layernorm_fwd": (C.c_int, [C.POINTER(AddLayernormArgs), C.c_void_p]),
+    "m2_embed_layernorm_fwd": (C.c_int, [C.POINTER(EmbedLayernormArgs), C.c_void_p]),
 }
 
 _lib = None

@@ -6,6 +6,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <stdarg.h>
+#include <string.h>
 #include "../../include/m2_b200.h"
 
 // ---- host side error plumbing -------------------------------------------------------

@@ -147,9 +147,17 @@ add_layernorm_kernel(const TI* a, long long lda, const TI* b, long long ldb, con
 
 // Vectorised variant: one warp per row, the row held in registers (n a multiple of 256 up to
 // 2048, 16-byte aligned rows); optional second output rounded to bf16.
+// Row selection for the embeddings' LayerNorm: addend a is row ids_a[r] of a table, addend b row
+// ids_b[r] (or r % b_mod) of a second one, and a third float32 addend c (row ids_c[r], or row 0) joins
+// as (a + c) + b -- the reference's word + token-type, then + position order.
+struct LnGather {
+  const long long* ids_a; const long long* ids_b; int b_mod;
+  const float* c; long long ldc; const long long* ids_c;
+};
+
 template <typename TI, typename TO, int VI>
 __global__ void __launch_bounds__(512)
-add_layernorm_warp_kernel(const TI* a, long long lda, const TI* b, long long ldb,
+add_layernorm_warp_kernel(const TI* a, long long lda, const TI* b, long long ldb, const LnGather gt,
                           const float* __restrict__ w, const float* __restrict__ bias, float eps, TO* out,
                           long long ldo, __nv_bfloat16* out2, long long ld2, int m,
                           __half* out_tm, long long tm_sb, long long tm_sc, int seq_len, int rpw, int pad2) {
@@ -179,13 +187,22 @@ add_layernorm_warp_kernel(const TI* a, long long lda, const TI* b, long long ldb
       }
     }
   } else {
-    const float4* pa = reinterpret_cast<const float4*>(a + (long long)warp * lda);
-    const float4* pb = b ? reinterpret_cast<const float4*>(b + (long long)warp * ldb) : nullptr;
+    const long long ra = gt.ids_a ? gt.ids_a[warp] : warp;
+    const long long rb = gt.ids_b ? gt.ids_b[warp] : (gt.b_mod > 0 ? warp % gt.b_mod : warp);
+    const float4* pa = reinterpret_cast<const float4*>(a + ra * lda);
+    const float4* pb = b ? reinterpret_cast<const float4*>(b + rb * ldb) : nullptr;
+    const float4* pc = gt.c ? reinterpret_cast<const float4*>(gt.c + (gt.ids_c ? gt.ids_c[warp] : 0) * gt.ldc) : nullptr;
 #pragma unroll
     for (int i = 0; i < VI; ++i) {
       const int q = (i * 32 + lane) * 2;
       const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 a0 = __ldg(pa + q), a1 = __ldg(pa + q + 1), b0 = pb ? __ldg(pb + q) : z, b1 = pb ? __ldg(pb + q + 1) : z;
+      float4 a0 = __ldg(pa + q), a1 = __ldg(pa + q + 1);
+      if (pc) {
+        const float4 c0 = __ldg(pc + q), c1 = __ldg(pc + q + 1);
+        a0 = make_float4(a0.x + c0.x, a0.y + c0.y, a0.z + c0.z, a0.w + c0.w);
+        a1 = make_float4(a1.x + c1.x, a1.y + c1.y, a1.z + c1.z, a1.w + c1.w);
+      }
+      const float4 b0 = pb ? __ldg(pb + q) : z, b1 = pb ? __ldg(pb + q + 1) : z;
       const float s8[8] = {a0.x + b0.x, a0.y + b0.y, a0.z + b0.z, a0.w + b0.w, a1.x + b1.x, a1.y + b1.y, a1.z + b1.z, a1.w + b1.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) { v[i][j] = s8[j]; sum += s8[j]; }
@@ -342,7 +359,37 @@ extern "C" int m2_blockdiag_glu_fwd(const m2_glu_args* a, void* stream) {
   return M2_OK;
 }
 
+static int add_layernorm_core(const m2_add_layernorm_args* a, const m2::LnGather& gather, void* stream);
+
 extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream) {
+  const m2::LnGather none = {nullptr, nullptr, 0, nullptr, 0, nullptr};
+  return add_layernorm_core(a, none, stream);
+}
+
+extern "C" int m2_embed_layernorm_fwd(const m2_embed_layernorm_args* e, void* stream) {
+  M2_REQUIRE(e != nullptr, M2_ERR_ARG, "m2_embed_layernorm_fwd: args is NULL");
+  M2_REQUIRE(e->m >= 0 && e->n > 0, M2_ERR_ARG, "m2_embed_layernorm_fwd: bad sizes");
+  if (e->m == 0) return M2_OK;
+  M2_REQUIRE(e->word_table && e->input_ids && e->type_table && e->weight && e->bias, M2_ERR_ARG,
+             "m2_embed_layernorm_fwd: NULL pointer");
+  M2_REQUIRE(!e->pos_table || e->position_ids || e->seq_len > 0, M2_ERR_ARG,
+             "m2_embed_layernorm_fwd: position table without position_ids needs seq_len");
+  M2_REQUIRE(e->n % 256 == 0 && e->n <= 2048 && m2_aligned(e->word_table, 16) && m2_aligned(e->type_table, 16) &&
+             m2_aligned(e->pos_table, 16), M2_ERR_UNSUPPORTED,
+             "m2_embed_layernorm_fwd: needs hidden size a multiple of 256 up to 2048 and 16-byte aligned tables");
+  m2_add_layernorm_args a;
+  memset(&a, 0, sizeof(a));
+  a.m = e->m; a.n = e->n; a.in_dtype = M2_F32; a.out_dtype = M2_F32;
+  a.a = e->word_table; a.lda = e->n; a.b = e->pos_table; a.ldb = e->n;
+  a.weight = e->weight; a.bias = e->bias; a.eps = e->eps;
+  a.out = e->out; a.ldo = e->ldo; a.out_bf16 = e->out_bf16; a.ld_bf16 = e->ld_bf16; a.bf16_pad_cols = e->bf16_pad_cols;
+  a.out_tm_f16 = e->out_tm_f16; a.tm_sb = e->tm_sb; a.tm_sc = e->tm_sc; a.seq_len = e->seq_len;
+  const m2::LnGather g = {e->input_ids, e->pos_table ? e->position_ids : nullptr, e->pos_table && !e->position_ids ? e->seq_len : 0,
+                          e->type_table, e->n, e->token_type_ids};
+  return add_layernorm_core(&a, g, stream);
+}
+
+static int add_layernorm_core(const m2_add_layernorm_args* a, const m2::LnGather& gather, void* stream) {
   using namespace m2;
   M2_REQUIRE(a != nullptr, M2_ERR_ARG, "m2_add_layernorm_fwd: args is NULL");
   M2_REQUIRE(a->m >= 0 && a->n > 0, M2_ERR_ARG, "m2_add_layernorm_fwd: bad sizes m=%d n=%d", a->m, a->n);
@@ -384,7 +431,7 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
 #define M2_LNW2(TI, TO, VI) do { \
       if (tile > 48 * 1024) M2_CUDA(cudaFuncSetAttribute(add_layernorm_warp_kernel<TI, TO, VI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile)); \
       add_layernorm_warp_kernel<TI, TO, VI><<<blocks, threads, tile, st>>>( \
-      (const TI*)a->a, a->lda, (const TI*)a->b, a->ldb, a->weight, a->bias, a->eps, \
+      (const TI*)a->a, a->lda, (const TI*)a->b, a->ldb, gather, a->weight, a->bias, a->eps, \
       (TO*)a->out, a->ldo, (__nv_bfloat16*)a->out_bf16, a->ld_bf16, a->m, \
       (__half*)a->out_tm_f16, a->tm_sb, a->tm_sc, a->seq_len, rpw, a->bf16_pad_cols); } while (0)
 #define M2_LNW_VI(TO) switch (a->n / 256) { case 1: M2_LNW(TO, 1); break; case 2: M2_LNW(TO, 2); break; \
@@ -397,6 +444,7 @@ extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream
     M2_LAUNCH_CHECK("add_layernorm_warp_kernel");
     return M2_OK;
   }
+  M2_REQUIRE(!gather.ids_a && !gather.c, M2_ERR_UNSUPPORTED, "m2_embed_layernorm_fwd: shape not covered by the vectorised kernel");
   M2_REQUIRE(a->out != nullptr && a->out_bf16 == nullptr && a->out_tm_f16 == nullptr, M2_ERR_UNSUPPORTED,
              "m2_add_layernorm_fwd: the copies need n a multiple of 256 (<= 2048) and 16-byte aligned rows");
   M2_REQUIRE(a->b != nullptr, M2_ERR_UNSUPPORTED, "m2_add_layernorm_fwd: b = NULL needs n a multiple of 256 (<= 2048) and 16-byte aligned rows");

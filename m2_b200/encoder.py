@@ -73,6 +73,12 @@ class M2BertEmbeddings(nn.Module):
 
     def forward(self, input_ids, token_type_ids=None, position_ids=None):
         L = input_ids.shape[1]
+        D = self.word_embeddings.weight.shape[1]
+        if (input_ids.is_cuda and input_ids.dim() == 2 and not torch.is_grad_enabled() and _autocast_bf16()
+                and not (self.training and self.dropout.p > 0) and D % 256 == 0 and D <= 2048
+                and self.word_embeddings.weight.dtype == torch.float32):
+            # gathers, adds, LayerNorm and the first mixer's copies in one launch
+            return self._fused_embeddings(input_ids, token_type_ids, position_ids)
         e = self.word_embeddings(input_ids)
         if token_type_ids is None:
             e = e + self.token_type_embeddings.weight[0]
@@ -89,6 +95,27 @@ class M2BertEmbeddings(nn.Module):
             # kernel write them instead of separate cast, fill and transpose passes
             return self._layernorm_with_copies(e)
         return self.dropout(self.LayerNorm(e))
+
+    def _fused_embeddings(self, input_ids, token_type_ids, position_ids):
+        from . import ops
+        from .sequence_mixer import _PAD
+        B, L = input_ids.shape
+        D = self.word_embeddings.weight.shape[1]
+        aug = torch.empty((B * L, D + _PAD), dtype=torch.bfloat16, device=input_ids.device)
+        tm = None
+        if ops.longconv_kind_batch(B, L, torch.bfloat16, D) == 3:
+            tm = torch.empty((D, B, L), dtype=torch.float16, device=input_ids.device)
+        pos = self.position_embeddings.weight if self.use_positional_encodings else None
+        if pos is not None and position_ids is None and L > pos.shape[0]:
+            raise RuntimeError(f"sequence length {L} exceeds max_position_embeddings {pos.shape[0]}")
+        y = ops.embed_layernorm_fwd(input_ids, self.word_embeddings.weight, self.token_type_embeddings.weight, pos,
+                                    self.LayerNorm.weight, self.LayerNorm.bias, self.LayerNorm.eps,
+                                    token_type_ids=token_type_ids, position_ids=position_ids,
+                                    bf16_copy=aug, tm_copy=tm, fill_pad=True)
+        y._m2_aug = aug
+        if tm is not None:
+            y._m2_tm = tm
+        return y
 
     def _layernorm_with_copies(self, e):
         from . import ops

@@ -280,6 +280,48 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm
     return out
 
 
+def embed_layernorm_fwd(input_ids, word_table, type_table, pos_table, weight, bias, eps, *, token_type_ids=None,
+                        position_ids=None, bf16_copy=None, tm_copy=None, fill_pad=False):
+    """LayerNorm((word_table[input_ids] + type_table[token_type_ids]) + pos_table[position_ids]) in float32 for
+    input_ids (B, L): the embeddings' gathers, adds and LayerNorm in one launch.  token_type_ids None = type 0,
+    pos_table None = no position term, position_ids None = positions 0..L-1.  Returns (B, L, n) float32;
+    bf16_copy / tm_copy / fill_pad as in add_layernorm_fwd."""
+    _need_cuda(input_ids, word_table)
+    B, L = input_ids.shape
+    n = word_table.shape[1]
+    m = B * L
+
+    def ids64(t):
+        return t.reshape(-1).to(torch.long).contiguous() if t is not None else None
+
+    keep = [ids64(input_ids), ids64(token_type_ids),
+            ids64(position_ids.expand(B, L)) if position_ids is not None else None,
+            _f32c(word_table), _f32c(type_table), _f32c(pos_table) if pos_table is not None else None,
+            _f32c(weight), _f32c(bias)]
+    out = torch.empty((B, L, n), dtype=torch.float32, device=input_ids.device)
+    a = _lib.EmbedLayernormArgs()
+    a.m, a.n, a.eps, a.seq_len = m, n, float(eps), L
+    a.input_ids, a.word_table, a.type_table = keep[0].data_ptr(), keep[3].data_ptr(), keep[4].data_ptr()
+    if keep[1] is not None:
+        a.token_type_ids = keep[1].data_ptr()
+    if keep[5] is not None:
+        a.pos_table = keep[5].data_ptr()
+        if keep[2] is not None:
+            a.position_ids = keep[2].data_ptr()
+    a.weight, a.bias = keep[6].data_ptr(), keep[7].data_ptr()
+    a.out, a.ldo = out.data_ptr(), n
+    if bf16_copy is not None:
+        assert bf16_copy.dtype == torch.bfloat16 and bf16_copy.stride(-1) == 1 and bf16_copy.shape[0] == m
+        a.out_bf16, a.ld_bf16 = bf16_copy.data_ptr(), bf16_copy.stride(0)
+        if fill_pad:
+            a.bf16_pad_cols = bf16_copy.shape[1] - n
+    if tm_copy is not None:
+        assert tm_copy.dtype == torch.float16 and tuple(tm_copy.shape) == (n, B, L) and tm_copy.stride(2) == 1
+        a.out_tm_f16, a.tm_sc, a.tm_sb = tm_copy.data_ptr(), tm_copy.stride(0), tm_copy.stride(1)
+    _launch("m2_embed_layernorm_fwd", input_ids, _lib.lib().m2_embed_layernorm_fwd, C.byref(a))
+    return out
+
+
 def device_status() -> int:
     v = C.c_int(0)
     _lib.check(_lib.lib().m2_device_status(C.byref(v)), "m2_device_status")

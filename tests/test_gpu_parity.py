@@ -551,3 +551,29 @@ def test_embedder_chunks_match_direct_calls():
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
         _, pooled = model(ids.to(DEV), attention_mask=mask.to(DEV))
     assert np.array_equal(got[:64], pooled.float().cpu().numpy())
+
+
+@pytest.mark.parametrize("with_types,with_pos,explicit_pos", [(False, True, False), (True, True, True), (True, False, False)])
+def test_fused_embeddings_layernorm(with_types, with_pos, explicit_pos):
+    """Gathers + (word + type) + position + LayerNorm in one launch against the stock-op composition."""
+    B, L, D, V = 3, 32, 256, 97
+    g = torch.Generator().manual_seed(21)
+    word = torch.randn((V, D), generator=g).to(DEV)
+    types = torch.randn((2, D), generator=g).to(DEV)
+    pos = torch.randn((L + 5, D), generator=g).to(DEV) if with_pos else None
+    w = torch.randn(D, generator=g).to(DEV)
+    bias = torch.randn(D, generator=g).to(DEV)
+    ids = torch.randint(0, V, (B, L), generator=g).to(DEV)
+    tt = torch.randint(0, 2, (B, L), generator=g).to(DEV) if with_types else None
+    pid = torch.randint(0, L + 5, (1, L), generator=g).to(DEV) if explicit_pos else None
+    e = word[ids] + (types[tt] if with_types else types[0])
+    if with_pos:
+        e = e + (pos[pid.expand(B, L)] if explicit_pos else pos[:L])
+    ref = torch.nn.functional.layer_norm(e, (D,), w, bias, 1e-12)
+    aug = torch.full((B * L, D + 64), float("nan"), dtype=torch.bfloat16, device=DEV)
+    tm = torch.full((D, B, L), float("nan"), dtype=torch.float16, device=DEV)
+    out = ops.embed_layernorm_fwd(ids, word, types, pos, w, bias, 1e-12, token_type_ids=tt, position_ids=pid,
+                                  bf16_copy=aug, tm_copy=tm, fill_pad=True)
+    assert O.parity_error(npy(out), npy(ref)) < 1e-5
+    assert torch.equal(aug[:, :D], out.view(B * L, D).bfloat16()) and bool((aug[:, D] == 1).all())
+    assert torch.equal(tm, ops.time_major_f16(out))
