@@ -120,8 +120,9 @@ int    m2_filter_spectrum_bias(int kind, int d_model, int seq_len, const float* 
  * (:131-147).
  *   xin : device, in_linear output; element (b, t, ch), ch in [0, 3*d_model) ordered x1|x2|v,
  *         at xin[b*xin_sb + t*xin_st + ch*xin_sc]; either xin_st == 1 or xin_sc == 1.
- *   u   : device, raw layer input (b, t, c) with its own strides and dtype; used only when
- *         n_filters == 2.
+ *   u   : device, raw layer input (b, t, c) with its own strides and dtype (float32 or bf16; kinds 2
+ *         and 3 also take the fp16 copy written by m2_time_major_f16 / m2_add_layernorm_fwd); used
+ *         only when n_filters == 2.
  *   out : device, (b, t, c) with its own strides, dtype act_dtype: the tensor out_linear
  *         consumes.
  * bf16_rounding != 0 rounds to bf16 where the reference under autocast does (conv output,
@@ -144,9 +145,9 @@ typedef struct {
   const float* short_b;     /* device (3*d_model):    short_filter.bias */
   const float* spec[2];     /* device, from m2_filter_spectrum (filter_fn, filter_fn2) */
   const float* bias[2];     /* device (d_model): filter_fn.bias, filter_fn2.bias (NULL for kind 3) */
-  int yu_bf16;              /* kind 3 only: != 0 rounds the residual convolution to bf16 before the
-                               final add, as the reference does when the layer input is bf16 (the
-                               other kinds infer this from u_dtype) */
+  int yu_bf16;              /* with an fp16 u (kind 3 always, kind 2 optionally): != 0 rounds the residual
+                               convolution to bf16 before the final add, as the reference does when the
+                               layer input is bf16 (with a float32 / bf16 u this follows from u_dtype) */
 } m2_longconv_args;
 
 int m2_longconv_fwd(const m2_longconv_args* args, void* stream);

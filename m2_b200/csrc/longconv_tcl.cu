@@ -308,6 +308,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
 // ---------------------------------------------------------------------------------------
 struct Params {
   int B, L, D, nf, rows;
+  int u_f16, yu_bf16;                               // 2-byte u holds fp16 (not bf16); round the residual conv to bf16
   const __nv_bfloat16* xin; long long xsb, xsc;      // (b, channel) row start = xin + b*xsb + ch*xsc, time stride 1
   const void* u; long long usb, usc;
   __nv_bfloat16* out; long long osb, osc;
@@ -526,7 +527,13 @@ longconv_tcl_kernel(const Params P) {
                   a[e][0] = v.x; a[e][1] = v.y; a[e][2] = v.z; a[e][3] = v.w;
                 } else {
                   const uint2 v = __ldg(reinterpret_cast<const uint2*>(urow + t0));
-                  a[e][0] = bf_lo(v.x); a[e][1] = bf_hi(v.x); a[e][2] = bf_lo(v.y); a[e][3] = bf_hi(v.y);
+                  if (P.u_f16) {
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
+                    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
+                    a[e][0] = lo.x; a[e][1] = lo.y; a[e][2] = hi.x; a[e][3] = hi.y;
+                  } else {
+                    a[e][0] = bf_lo(v.x); a[e][1] = bf_hi(v.x); a[e][2] = bf_lo(v.y); a[e][3] = bf_hi(v.y);
+                  }
                 }
               }
             }
@@ -725,7 +732,7 @@ longconv_tcl_kernel(const Params P) {
             if (t0 < P.L) {
               const float4 y = *reinterpret_cast<const float4*>(Y + t0);
               float yv[4] = {y.x, y.y, y.z, y.w};
-              if (sizeof(TU) == 2) {                           // bf16 layer input: yu is cast to bf16 first
+              if (P.yu_bf16) {                                 // bf16 layer input: yu is cast to bf16 first
 #pragma unroll
                 for (int j = 0; j < 4; ++j) yv[j] = bf16r(yv[j]);
               }
@@ -827,7 +834,10 @@ int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
   P.out = (__nv_bfloat16*)a->out; P.osb = a->out_sb; P.osc = a->out_sc;
   P.sw = a->short_w; P.sb = a->short_b;
   for (int f = 0; f < 2; ++f) { P.spec[f] = a->spec[f]; P.bias[f] = a->bias[f]; }
-  const bool ubf = a->n_filters == 2 && a->u_dtype == M2_BF16;
+  // 2-byte residual input: bf16, or the fp16 time-major copy a LayerNorm / m2_time_major_f16 wrote
+  const bool ubf = a->n_filters == 2 && (a->u_dtype == M2_BF16 || a->u_dtype == M2_F16);
+  P.u_f16 = a->n_filters == 2 && a->u_dtype == M2_F16;
+  P.yu_bf16 = a->n_filters == 2 && (a->u_dtype == M2_BF16 || (a->u_dtype == M2_F16 && a->yu_bf16));
   if (a->n_filters == 2) {
     const size_t ua = ubf ? 8 : 16;
     M2_REQUIRE(m2_aligned(a->u, ua) && a->u_sc % 4 == 0 && a->u_sb % 4 == 0, M2_ERR_ALIGN,

@@ -103,7 +103,7 @@ class M2BertEmbeddings(nn.Module):
         D = self.word_embeddings.weight.shape[1]
         aug = torch.empty((B * L, D + _PAD), dtype=torch.bfloat16, device=input_ids.device)
         tm = None
-        if ops.longconv_kind_batch(B, L, torch.bfloat16, D) == 3:
+        if L % 8 == 0 and ops.longconv_kind_batch(B, L, torch.bfloat16, D) in (2, 3):
             tm = torch.empty((D, B, L), dtype=torch.float16, device=input_ids.device)
         pos = self.position_embeddings.weight if self.use_positional_encodings else None
         if pos is not None and position_ids is None and L > pos.shape[0]:
@@ -123,7 +123,7 @@ class M2BertEmbeddings(nn.Module):
         B, L, D = e.shape
         aug = torch.empty((B * L, D + _PAD), dtype=torch.bfloat16, device=e.device)
         tm = None
-        if ops.longconv_kind_batch(B, L, torch.bfloat16, D) == 3:
+        if L % 8 == 0 and ops.longconv_kind_batch(B, L, torch.bfloat16, D) in (2, 3):
             tm = torch.empty((D, B, L), dtype=torch.float16, device=e.device)
         y = ops.add_layernorm_fwd(e.reshape(B * L, D), None, self.LayerNorm.weight, self.LayerNorm.bias,
                                   self.LayerNorm.eps, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=True)

@@ -61,9 +61,10 @@ class BertGatedLinearUnitMLP(nn.Module):
             from .sequence_mixer import _PAD
             aug = torch.empty((x2.shape[0], x.shape[-1] + _PAD), dtype=torch.bfloat16, device=x.device)
         tm = None
-        if aug is not None and ops.longconv_kind_batch(x.shape[0], x.shape[1], torch.bfloat16, x.shape[2]) == 3:
-            # a following mixer of this shape runs the Toeplitz-GEMM convolution, which reads the
-            # layer input as a time-major fp16 operand: written here too
+        if (aug is not None and x.shape[1] % 8 == 0
+                and ops.longconv_kind_batch(x.shape[0], x.shape[1], torch.bfloat16, x.shape[2]) in (2, 3)):
+            # a following mixer of this shape runs a time-contiguous convolution kernel, which reads the
+            # layer input as a time-major fp16 tensor: written here too
             tm = torch.empty((x.shape[2], x.shape[0], x.shape[1]), dtype=torch.float16, device=x.device)
         skip = copies_only and tm is not None
         y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,

@@ -119,13 +119,23 @@ class MonarchMixerSequenceMixing(nn.Module):
         x_aug = augmented_input(u)
         with torch.autocast("cuda", enabled=False):
             xin_t = torch.matmul(w_in, x_aug.transpose(1, 2))                    # (B, 3D, L)
-            u_t = ures.transpose(1, 2).contiguous() if ures is not None else None
-            y_t = torch.empty((B, D + _PAD, L), dtype=torch.bfloat16, device=u.device)
-            y_t[:, D] = 1.0
-            y_t[:, D + 1:] = 0.0
-            ops.longconv_fwd(xin_t.transpose(1, 2), u_t.transpose(1, 2) if u_t is not None else None,
+            u_view, yu_bf16 = None, False
+            if ures is not None:
+                tm = getattr(ures, "_m2_tm", None)                               # (D, B, L) fp16 from the LayerNorm
+                if tm is not None and tm.shape == (D, B, L) and tm.device == u.device:
+                    u_view = tm.permute(1, 2, 0)                                 # (B, L, D) view, time-contiguous
+                    yu_bf16 = getattr(ures, "_m2_src_dtype", ures.dtype) == torch.bfloat16
+                else:
+                    u_view = ures.transpose(1, 2).contiguous().transpose(1, 2)
+            y_t = getattr(self, "_y_t", None)
+            if y_t is None or y_t.shape != (B, D + _PAD, L) or y_t.device != u.device:
+                y_t = torch.empty((B, D + _PAD, L), dtype=torch.bfloat16, device=u.device)
+                y_t[:, D] = 1.0
+                y_t[:, D + 1:] = 0.0
+                self._y_t = y_t
+            ops.longconv_fwd(xin_t.transpose(1, 2), u_view,
                              self.short_filter.weight, self.short_filter.bias, specs, biases,
-                             kind=2, bf16_rounding=True, out=y_t[:, :D].transpose(1, 2))
+                             kind=2, bf16_rounding=True, out=y_t[:, :D].transpose(1, 2), yu_bf16=yu_bf16)
             return torch.matmul(y_t.transpose(1, 2), w_out.t())                  # (B, L, D)
 
     def _forward_toeplitz(self, u, ures, specs):
@@ -146,7 +156,7 @@ class MonarchMixerSequenceMixing(nn.Module):
                 if u_t is None or u_t.shape != (D, B, L) or u_t.device != u.device:
                     u_t = ops.time_major_f16(ures)
             buf = getattr(self, "_y_t", None)
-            if buf is None or buf.shape[1] != B * L or buf.device != u.device:
+            if buf is None or buf.shape != (D + _PAD, B * L) or buf.device != u.device:
                 buf = torch.empty((D + _PAD, B * L), dtype=torch.bfloat16, device=u.device)
                 buf[D] = 1.0
                 buf[D + 1:] = 0.0

@@ -426,6 +426,13 @@ def test_longconv_long_row_family(L, D, B, residual, u_bf16):
                                      m.short_filter.bias, specs, [f.conv_bias() for f in filters],
                                      kind=kind, bf16_rounding=True, out=out))
     errs = [O.parity_error(npy(outs[1]), npy(outs[0]))]
+    if residual and L % 8 == 0:
+        # the fp16 time-major copy of u (what a preceding LayerNorm writes) gives the same bits as u itself
+        u16 = ops.time_major_f16(u).permute(1, 2, 0)
+        out16 = torch.empty((B, D, L), dtype=torch.bfloat16, device=DEV).transpose(1, 2)
+        ops.longconv_fwd(xin, u16, m.short_filter.weight, m.short_filter.bias, specs,
+                         [f.conv_bias() for f in filters], kind=2, bf16_rounding=True, out=out16, yu_bf16=u_bf16)
+        assert torch.equal(out16, outs[1])
     if B * L * D <= 1 << 18:
         taps = []
         for f in filters:
