@@ -185,7 +185,9 @@ def dump_layout(ref, path):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of HazyResearch/m2>")
+    ref_root = sys.argv[1]
     ref = import_reference(ref_root)
     here = os.path.dirname(os.path.abspath(__file__))
     dump_layout(ref, os.path.join(here, "state_dict_layout.json"))
