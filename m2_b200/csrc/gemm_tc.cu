@@ -50,6 +50,15 @@ int m2_make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint
 
 namespace gemm {
 
+#ifdef M2_GEMM_TIMING   // tuning only: cycles one thread per role spends waiting / working
+__device__ unsigned long long g_gemm_cycles[16];
+#define GT_T0() long long gt_prev_ = clock64()
+#define GT_MARK(cond, i) do { if (cond) { long long n_ = clock64(); atomicAdd(&g_gemm_cycles[i], (unsigned long long)(n_ - gt_prev_)); gt_prev_ = n_; } } while (0)
+#else
+#define GT_T0() do {} while (0)
+#define GT_MARK(cond, i) do {} while (0)
+#endif
+
 constexpr int BM = 128;
 constexpr int BK = 64;                 // one 128-byte swizzle row of bf16
 constexpr int EPI_WARPS = 16;              // four warps per TMEM lane quarter, each a quarter of the columns
@@ -120,10 +129,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      GT_T0();
       for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
         const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
         for (int ks = 0; ks < P.ksteps; ++ks) {
+          GT_MARK(true, 0);
           if (!tc::mbar_wait(empty + stage, phase ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+          GT_MARK(true, 1);
           unsigned char* st = smem + stage * C::STAGE_BYTES;
           tc::mbar_expect_tx(full + stage, C::STAGE_BYTES);
           tc::tma_load_2d(st, &tmA, full + stage, kb * P.p + ks * BK, mt * BM);
@@ -144,12 +156,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int buf = 0; uint32_t bphase = 0;
       bool ok = true;
+      GT_T0();
       for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
+        GT_MARK(true, 2);
         if (!tc::mbar_wait(tempty + buf, bphase ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) break;
+        GT_MARK(true, 3);
         tc::tc_fence_after();
         const uint32_t acc = tmem_base + buf * C::ACC_COLS;
         for (int ks = 0; ks < P.ksteps; ++ks) {
+          GT_MARK(true, 2);
           if (!tc::mbar_wait(full + stage, phase, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
+          GT_MARK(true, 4);
           tc::tc_fence_after();
           const uint32_t sa = tc::smem_u32(smem + stage * C::STAGE_BYTES);
           const uint64_t dA = tc::smem_desc_k_sw128(sa), dB = tc::smem_desc_k_sw128(sa + A_BYTES);
@@ -178,9 +195,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     static_assert(CW % 16 == 0, "column slice must be a multiple of 16");
     int buf = 0; uint32_t bphase = 0;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
+    const bool gt_me = (warp == 2 && lane == 0);
+    GT_T0();
     for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
       const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
+      GT_MARK(gt_me, 5);
       if (!tc::mbar_wait(tfull + buf, bphase, abort_flag, tc::ST_TIMEOUT_EPI)) break;
+      GT_MARK(gt_me, 6);
       tc::tc_fence_after();
       const int row = mt * BM + quarter * 32 + lane;
       const int col0 = kb * P.q + nt * BN;
@@ -269,6 +290,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     tc::tmem_dealloc(tmem_base, C::TCOLS);
   }
 }
+
+
+#ifdef M2_GEMM_TIMING
+}  // namespace gemm
+}  // namespace m2
+extern "C" int m2_debug_gemm_cycles(unsigned long long* out, int reset) {
+  unsigned long long z[16] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out, m2::gemm::g_gemm_cycles, sizeof(z));
+  if (reset) cudaMemcpyToSymbol(m2::gemm::g_gemm_cycles, z, sizeof(z));
+  return 0;
+}
+namespace m2 {
+namespace gemm {
+#endif
 
 static int sm_count() {
   static int cached[64] = {0};
