@@ -62,7 +62,8 @@ __device__ unsigned long long g_gemm_cycles[16];
 constexpr int BM = 128;
 constexpr int BK = 64;                 // one 128-byte swizzle row of bf16
 constexpr int EPI_WARPS = 16;              // four warps per TMEM lane quarter, each a quarter of the columns
-constexpr int THREADS = 64 + 32 * EPI_WARPS;
+constexpr int EPI_WARP0 = 3;               // warp 0: TMA producer, warps 1-2: MMA issuers, then the epilogue warps
+constexpr int THREADS = 32 * (EPI_WARP0 + EPI_WARPS);
 constexpr int A_BYTES = BM * BK * 2;   // 16 KB
 constexpr int SMEM_BUDGET = 200 * 1024;
 
@@ -91,6 +92,46 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// GLU epilogue of one tile for one warp: columns [chalf*CW, (chalf+1)*CW) of the gate accumulator at
+// `tacc` and of the linear accumulator BN columns further, as gelu(gate) (cast to bf16) * linear.
+// Two register sets: the next 16 columns are on their way from tensor memory while the GELU of the
+// current ones runs (the store keeps the arithmetic ahead of the wait).
+template <int BN, int CW>
+__device__ __forceinline__ void glu_epilogue_tile(uint32_t tacc, int chalf, __nv_bfloat16* orow, bool in_range, int wide_out) {
+  constexpr int NCH = CW / 16;
+  uint32_t a[2][16], b[2][16];
+  tc::tmem_ld16(tacc + chalf * CW, a[0]);
+  tc::tmem_ld16(tacc + BN + chalf * CW, b[0]);
+  tc::tmem_ld_wait();
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int cur = ch & 1, c0 = chalf * CW + 16 * ch;
+    if (ch + 1 < NCH) {
+      tc::tmem_ld16(tacc + c0 + 16, a[cur ^ 1]);
+      tc::tmem_ld16(tacc + BN + c0 + 16, b[cur ^ 1]);
+    }
+    uint32_t packed[8];
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      const uint32_t g = pack_bf16(__uint_as_float(a[cur][j]), __uint_as_float(a[cur][j + 1]));
+      const uint32_t n = pack_bf16(__uint_as_float(b[cur][j]), __uint_as_float(b[cur][j + 1]));
+      float a0, a1;
+      gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
+      packed[j >> 1] = bf2_mul(pack_bf16(a0, a1), n);   // GELU output cast to bf16, times the linear half
+    }
+    if (in_range) {
+      if (wide_out) {                   // one full 32-byte sector per thread
+        stg256(orow + c0, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+      } else {
+        uint4* dst = reinterpret_cast<uint4*>(orow + c0);
+        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+      }
+    }
+    if (ch + 1 < NCH) tc::tmem_ld_wait();
+  }
+}
+
 template <int BN, bool GLU>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params P) {
@@ -108,8 +149,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < C::NSTAGES; ++s) { tc::mbar_init(full + s, 1); tc::mbar_init(empty + s, 1); }
-    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull + b, 1); tc::mbar_init(tempty + b, 32 * EPI_WARPS); }
+    for (int s = 0; s < C::NSTAGES; ++s) { tc::mbar_init(full + s, 1); tc::mbar_init(empty + s, C::NACC); }
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull + b, C::NACC); tc::mbar_init(tempty + b, 32 * EPI_WARPS); }
     *abort_flag = 0;
     tc::mbar_fence_init();
     tc::tma_prefetch_desc(&tmA);
@@ -149,35 +190,41 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------- MMA issuer ---------------------------------
+  } else if (warp >= 1 && warp <= C::NACC) {
+    // ------------------------------- MMA issuers --------------------------------
+    // The issuing thread spends 100-270 cycles per K step on the barrier test and the commit besides the
+    // MMAs themselves (measured stand-alone: 4 MMAs of N = 128 per K step take 523 cycles with a satisfied
+    // mbarrier wait in the loop, 256 without; the tensor pipe alone runs them at 64 cycles each).  The
+    // two accumulators of the gated product therefore have one issuing thread each: warp 1 the gate
+    // block, warp 2 the linear block.  Both wait for the same stage and both commit to its `empty`
+    // barrier and to the accumulator buffer's `tfull` (count NACC).
     if (lane == 0) {
       constexpr uint32_t idesc = tc::make_idesc(BM, BN, 1);
+      const int chain = warp - 1;
+      const uint64_t dA0 = tc::smem_desc_k_sw128(tc::smem_u32(smem + chain * (A_BYTES + C::B_BYTES)));
+      const uint64_t dB0 = dA0 + (uint64_t)(A_BYTES >> 4);
       int stage = 0; uint32_t phase = 0;
       int buf = 0; uint32_t bphase = 0;
       bool ok = true;
+      const bool gt_iss = warp == 1;
       GT_T0();
       for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
-        GT_MARK(true, 2);
+        GT_MARK(gt_iss, 2);
         if (!tc::mbar_wait(tempty + buf, bphase ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) break;
-        GT_MARK(true, 3);
+        GT_MARK(gt_iss, 3);
         tc::tc_fence_after();
-        const uint32_t acc = tmem_base + buf * C::ACC_COLS;
+        const uint32_t acc = tmem_base + buf * C::ACC_COLS + chain * BN;
         for (int ks = 0; ks < P.ksteps; ++ks) {
-          GT_MARK(true, 2);
+          GT_MARK(gt_iss, 2);
           if (!tc::mbar_wait(full + stage, phase, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
-          GT_MARK(true, 4);
+          GT_MARK(gt_iss, 4);
           tc::tc_fence_after();
-          const uint32_t sa = tc::smem_u32(smem + stage * C::STAGE_BYTES);
-          const uint64_t dA = tc::smem_desc_k_sw128(sa), dB = tc::smem_desc_k_sw128(sa + A_BYTES);
-          const uint64_t dA2 = tc::smem_desc_k_sw128(sa + A_BYTES + C::B_BYTES);
-          const uint64_t dB2 = tc::smem_desc_k_sw128(sa + 2 * A_BYTES + C::B_BYTES);
+          const uint64_t off = (uint64_t)(stage * (C::STAGE_BYTES >> 4));
+          const uint64_t dA = dA0 + off, dB = dB0 + off;
 #pragma unroll
           for (int kk = 0; kk < BK / 16; ++kk) {
-            const uint32_t accum = (ks | kk) ? 1u : 0u;
             // 16 bf16 along K = 32 bytes = 2 units of the descriptor's 16-byte address field
-            tc::mma_ss(acc, dA + 2 * kk, dB + 2 * kk, idesc, accum);
-            if (GLU) tc::mma_ss(acc + BN, dA2 + 2 * kk, dB2 + 2 * kk, idesc, accum);
+            tc::mma_ss(acc, dA + 2 * kk, dB + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
           }
           tc::mma_commit(empty + stage);        // stage reusable once these MMAs have read it
           if (++stage == C::NSTAGES) { stage = 0; phase ^= 1; }
@@ -187,15 +234,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if ((buf ^= 1) == 0) bphase ^= 1;
       }
     }
-  } else {
+  } else if (warp >= EPI_WARP0) {
     // ------------------------------- epilogue -----------------------------------
     const int quarter = warp & 3;               // TMEM lanes this warp may touch: 32*quarter ..
-    const int chalf = (warp - 2) >> 2;          // which slice of the tile's columns
+    const int chalf = (warp - EPI_WARP0) >> 2;  // which slice of the tile's columns
     constexpr int CW = BN / (EPI_WARPS / 4);    // columns per warp
     static_assert(CW % 16 == 0, "column slice must be a multiple of 16");
     int buf = 0; uint32_t bphase = 0;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
-    const bool gt_me = (warp == 2 && lane == 0);
+    const bool gt_me = (warp == EPI_WARP0 && lane == 0);
     GT_T0();
     for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
       const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
@@ -208,40 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t tacc = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* orow = out + (long long)row * P.ldo + col0;
       if constexpr (GLU) {
-        // two register sets: the next 16 columns are on their way from tensor memory while the
-        // GELU of the current ones runs (the store keeps the arithmetic ahead of the wait)
-        constexpr int NCH = CW / 16;
-        uint32_t a[2][16], b[2][16];
-        tc::tmem_ld16(tacc + chalf * CW, a[0]);
-        tc::tmem_ld16(tacc + BN + chalf * CW, b[0]);
-        tc::tmem_ld_wait();
-#pragma unroll
-        for (int ch = 0; ch < NCH; ++ch) {
-          const int cur = ch & 1, c0 = chalf * CW + 16 * ch;
-          if (ch + 1 < NCH) {
-            tc::tmem_ld16(tacc + c0 + 16, a[cur ^ 1]);
-            tc::tmem_ld16(tacc + BN + c0 + 16, b[cur ^ 1]);
-          }
-          uint32_t packed[8];
-#pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            const uint32_t g = pack_bf16(__uint_as_float(a[cur][j]), __uint_as_float(a[cur][j + 1]));
-            const uint32_t n = pack_bf16(__uint_as_float(b[cur][j]), __uint_as_float(b[cur][j + 1]));
-            float a0, a1;
-            gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
-            packed[j >> 1] = bf2_mul(pack_bf16(a0, a1), n);   // GELU output cast to bf16, times the linear half
-          }
-          if (row < P.M) {
-            if (P.wide_out) {                   // one full 32-byte sector per thread
-              stg256(orow + c0, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
-            } else {
-              uint4* dst = reinterpret_cast<uint4*>(orow + c0);
-              dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-              dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-            }
-          }
-          if (ch + 1 < NCH) tc::tmem_ld_wait();
-        }
+        glu_epilogue_tile<BN, CW>(tacc, chalf, orow, row < P.M, P.wide_out);
       } else {
 #pragma unroll 1
       for (int c0 = chalf * CW; c0 < (chalf + 1) * CW; c0 += 16) {
@@ -291,6 +305,196 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+
+
+
+
+// ---------------------------------------------------------------------------------------
+// GLU GEMM with the x slices resident in shared memory.  The kernel above brings 64 KB through TMA per
+// K step (x and wg tiles of both blocks), and its TMA throughput -- about 38 bytes per clock and SM from
+// L2, whatever the box shape and whether one or two threads issue the loads -- is what paces it.  When
+// K = d_model / nblocks <= 192 the two K-slices of x one row tile needs (96 KB) stay put while the CTA
+// walks over the column tiles of the block pair, and only wg rows (32 KB per K step) stream through the
+// ring: 112 instead of 196 KB per tile.  A CTA
+// owns a contiguous range of units (row tile, block pair, group of column tiles), so consecutive units
+// mostly share their x; when they do not, the first tile of the new unit brings the x tiles in K step
+// by K step, each as soon as the last MMAs reading the old one have completed (`a_empty`).
+// Two issuing warps as above; same epilogue.
+// ---------------------------------------------------------------------------------------
+namespace res {
+constexpr int BN = 128, MAX_KS = 3, NSTB = 4;
+constexpr int B_STAGE = 2 * BN * BK * 2;                   // gate + linear wg rows of one K step: 32 KB
+constexpr int OFF_B = 2 * MAX_KS * A_BYTES;                // after the resident x tiles: 96 KB
+constexpr int OFF_BAR = OFF_B + NSTB * B_STAGE;
+constexpr int NBARS = 2 * NSTB + MAX_KS + 4;
+constexpr int SMEM = OFF_BAR + NBARS * 8 + 16 + 1024;
+static_assert(SMEM <= 227 * 1024, "shared memory budget");
+}  // namespace res
+
+struct ResParams {
+  int M, p, q, nb_half, ksteps, ntn, gs, ngroups, total_units, wide_out;
+  void* out; long long ldo;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+glu_res_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const ResParams P) {
+  using namespace res;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* b_full = bars;                   // [NSTB] wg rows (and, on a unit's first tile, x tiles) landed
+  uint64_t* b_empty = b_full + NSTB;         // [NSTB] both issuers' MMAs have read the stage
+  uint64_t* a_empty = b_empty + NSTB;        // [MAX_KS] both issuers are done with the x tiles of K step ks
+  uint64_t* tfull = a_empty + MAX_KS;        // [2]
+  uint64_t* tempty = tfull + 2;              // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTB; ++s) { tc::mbar_init(b_full + s, 1); tc::mbar_init(b_empty + s, 2); }
+    for (int k = 0; k < MAX_KS; ++k) tc::mbar_init(a_empty + k, 2);
+    for (int b = 0; b < 2; ++b) { tc::mbar_init(tfull + b, 2); tc::mbar_init(tempty + b, 32 * EPI_WARPS); }
+    *abort_flag = 0;
+    tc::mbar_fence_init();
+    tc::tma_prefetch_desc(&tmA);
+    tc::tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tc::tmem_alloc(tmem_slot, 512);
+    tc::tmem_relinquish();
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // this CTA's contiguous range of units; unit = (pair = row tile x block pair, group of column tiles)
+  const int u0 = (int)((long long)blockIdx.x * P.total_units / gridDim.x);
+  const int u1 = (int)((long long)(blockIdx.x + 1) * P.total_units / gridDim.x);
+  auto decode = [&](int unit, int& pair, int& mt, int& kb, int& nt0, int& ntiles) {
+    pair = unit / P.ngroups;
+    const int g = unit % P.ngroups;
+    mt = pair / P.nb_half; kb = pair % P.nb_half;
+    nt0 = g * P.gs;
+    ntiles = P.ntn - nt0 < P.gs ? P.ntn - nt0 : P.gs;
+  };
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int epoch = -1, prev_pair = -1;
+      bool ok = true;
+      for (int unit = u0; unit < u1 && ok; ++unit) {
+        int pair, mt, kb, nt0, ntiles;
+        decode(unit, pair, mt, kb, nt0, ntiles);
+        const bool new_x = pair != prev_pair;
+        if (new_x) { ++epoch; prev_pair = pair; }
+        for (int t = 0; t < ntiles && ok; ++t) {
+          const bool load_x = new_x && t == 0;
+          for (int ks = 0; ks < P.ksteps; ++ks) {
+            if (!tc::mbar_wait(b_empty + stage, phase ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+            if (load_x && epoch > 0 &&
+                !tc::mbar_wait(a_empty + ks, (uint32_t)(epoch - 1) & 1u, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
+            unsigned char* st = smem + OFF_B + stage * B_STAGE;
+            tc::mbar_expect_tx(b_full + stage, B_STAGE + (load_x ? 2 * A_BYTES : 0));
+            if (load_x) {
+              tc::tma_load_2d(smem + ks * A_BYTES, &tmA, b_full + stage, kb * P.p + ks * BK, mt * BM);
+              tc::tma_load_2d(smem + (MAX_KS + ks) * A_BYTES, &tmA, b_full + stage, (kb + P.nb_half) * P.p + ks * BK, mt * BM);
+            }
+            const int row_g = kb * P.q + (nt0 + t) * BN;
+            tc::tma_load_2d(st, &tmB, b_full + stage, ks * BK, row_g);
+            tc::tma_load_2d(st + B_STAGE / 2, &tmB, b_full + stage, ks * BK, row_g + P.nb_half * P.q);
+            if (++stage == NSTB) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------- MMA issuers: warp 1 gate, warp 2 linear ----------------------
+    // Each thread issues every tile's MMAs of its accumulator in order, so its commit to `a_empty` after
+    // the last tile that reads the old x covers all of its earlier MMAs as well.
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc::make_idesc(BM, BN, 1);
+      const int chain = warp - 1;
+      const uint64_t dA0 = tc::smem_desc_k_sw128(tc::smem_u32(smem + chain * MAX_KS * A_BYTES));
+      const uint64_t dB0 = tc::smem_desc_k_sw128(tc::smem_u32(smem + OFF_B + chain * (B_STAGE / 2)));
+      int stage = 0; uint32_t phase = 0;
+      int buf = 0; uint32_t bphase = 0;
+      bool ok = true;
+      const bool gt_iss = warp == 1;
+      GT_T0();
+      for (int unit = u0; unit < u1 && ok; ++unit) {
+        int pair, mt, kb, nt0, ntiles;
+        decode(unit, pair, mt, kb, nt0, ntiles);
+        const bool x_changes = unit + 1 < u1 && (unit + 1) / P.ngroups != pair;
+        for (int t = 0; t < ntiles && ok; ++t) {
+          GT_MARK(gt_iss, 2);
+          if (!tc::mbar_wait(tempty + buf, bphase ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) { ok = false; break; }
+          GT_MARK(gt_iss, 3);
+          tc::tc_fence_after();
+          const uint32_t acc = tmem_base + buf * 2 * BN + chain * BN;
+          const bool release_x = x_changes && t == ntiles - 1;
+          for (int ks = 0; ks < P.ksteps; ++ks) {
+            GT_MARK(gt_iss, 2);
+            if (!tc::mbar_wait(b_full + stage, phase, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
+            GT_MARK(gt_iss, 4);
+            tc::tc_fence_after();
+            const uint64_t dA = dA0 + (uint64_t)(ks * (A_BYTES >> 4)), dB = dB0 + (uint64_t)(stage * (B_STAGE >> 4));
+#pragma unroll
+            for (int kk = 0; kk < BK / 16; ++kk) tc::mma_ss(acc, dA + 2 * kk, dB + 2 * kk, idesc, (ks | kk) ? 1u : 0u);
+            tc::mma_commit(b_empty + stage);
+            if (release_x) tc::mma_commit(a_empty + ks);
+            if (++stage == NSTB) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          tc::mma_commit(tfull + buf);
+          if ((buf ^= 1) == 0) bphase ^= 1;
+        }
+      }
+    }
+  } else if (warp >= EPI_WARP0) {
+    // ------------------------------- epilogue -----------------------------------
+    const int quarter = warp & 3;
+    const int chalf = (warp - EPI_WARP0) >> 2;
+    constexpr int CW = BN / (EPI_WARPS / 4);
+    int buf = 0; uint32_t bphase = 0;
+    bool ok = true;
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
+    const bool gt_me = (warp == EPI_WARP0 && lane == 0);
+    GT_T0();
+    for (int unit = u0; unit < u1 && ok; ++unit) {
+      int pair, mt, kb, nt0, ntiles;
+      decode(unit, pair, mt, kb, nt0, ntiles);
+      const int row = mt * BM + quarter * 32 + lane;
+      for (int t = 0; t < ntiles; ++t) {
+        GT_MARK(gt_me, 5);
+        if (!tc::mbar_wait(tfull + buf, bphase, abort_flag, tc::ST_TIMEOUT_EPI)) { ok = false; break; }
+        GT_MARK(gt_me, 6);
+        tc::tc_fence_after();
+        const uint32_t tacc = tmem_base + buf * 2 * BN + ((uint32_t)(quarter * 32) << 16);
+        __nv_bfloat16* orow = out + (long long)row * P.ldo + kb * P.q + (nt0 + t) * BN;
+        glu_epilogue_tile<BN, CW>(tacc, chalf, orow, row < P.M, P.wide_out);
+        tc::tc_fence_before();
+        tc::mbar_arrive(tempty + buf);
+        if ((buf ^= 1) == 0) bphase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------- teardown -------------------------------------
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    for (int s = 0; s < NSTB; ++s)
+      for (uint32_t i = 0; i < 4096 && !tc::mbar_try_wait(b_full + s, 0) && !tc::mbar_try_wait(b_full + s, 1); ++i) {}
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, 512);
+  }
+}
 
 #ifdef M2_GEMM_TIMING
 }  // namespace gemm
@@ -383,6 +587,22 @@ int glu_tc_launch(const m2_glu_args* a, cudaStream_t st) {
   P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->inter;
   P.out = a->h; P.ldo = a->ldh; P.bias = nullptr;
   P.wide_out = m2_aligned(a->h, 32) && a->ldh % 16 == 0 && q % 16 == 0;
+  if (P.ksteps <= res::MAX_KS && !getenv("M2_GLU_DUAL")) {
+    ResParams R;
+    R.M = a->m; R.p = p; R.q = q; R.nb_half = a->nblocks / 2; R.ksteps = P.ksteps; R.ntn = q / res::BN;
+    // column tiles per unit: about 6 units per SM, so that the contiguous ranges balance
+    const long long pairs = (long long)P.ntm * R.nb_half;
+    int gs = R.ntn;
+    while (gs > 1 && pairs * ((R.ntn + gs - 1) / gs) < 6LL * sm_count()) gs = (gs + 1) / 2;
+    R.gs = gs; R.ngroups = (R.ntn + gs - 1) / gs;
+    R.total_units = (int)(pairs * R.ngroups);
+    R.wide_out = P.wide_out; R.out = a->h; R.ldo = a->ldh;
+    M2_CUDA(cudaFuncSetAttribute(glu_res_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, res::SMEM));
+    const int grid = R.total_units < sm_count() ? R.total_units : sm_count();
+    glu_res_kernel<<<grid, THREADS, res::SMEM, st>>>(tmA, tmB, R);
+    M2_LAUNCH_CHECK("glu_res_kernel");
+    return M2_OK;
+  }
   return launch<128, true>(tmA, tmB, P, st);
 }
 
