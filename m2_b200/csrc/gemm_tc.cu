@@ -94,27 +94,29 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 
 // GLU epilogue of one tile for one warp: columns [chalf*CW, (chalf+1)*CW) of the gate accumulator at
 // `tacc` and of the linear accumulator BN columns further, as gelu(gate) (cast to bf16) * linear.
-// Two register sets: the next 16 columns are on their way from tensor memory while the GELU of the
-// current ones runs (the store keeps the arithmetic ahead of the wait).
+// All of the warp's columns are read into registers first and the accumulator buffer is handed back
+// (`tempty`) before any arithmetic, so the next tile's MMAs never wait for a GELU.
 template <int BN, int CW>
-__device__ __forceinline__ void glu_epilogue_tile(uint32_t tacc, int chalf, __nv_bfloat16* orow, bool in_range, int wide_out) {
+__device__ __forceinline__ void glu_epilogue_tile(uint32_t tacc, int chalf, __nv_bfloat16* orow, bool in_range, int wide_out,
+                                                  uint64_t* tempty) {
   constexpr int NCH = CW / 16;
-  uint32_t a[2][16], b[2][16];
-  tc::tmem_ld16(tacc + chalf * CW, a[0]);
-  tc::tmem_ld16(tacc + BN + chalf * CW, b[0]);
-  tc::tmem_ld_wait();
+  uint32_t a[NCH][16], b[NCH][16];
 #pragma unroll
   for (int ch = 0; ch < NCH; ++ch) {
-    const int cur = ch & 1, c0 = chalf * CW + 16 * ch;
-    if (ch + 1 < NCH) {
-      tc::tmem_ld16(tacc + c0 + 16, a[cur ^ 1]);
-      tc::tmem_ld16(tacc + BN + c0 + 16, b[cur ^ 1]);
-    }
+    tc::tmem_ld16(tacc + chalf * CW + 16 * ch, a[ch]);
+    tc::tmem_ld16(tacc + BN + chalf * CW + 16 * ch, b[ch]);
+  }
+  tc::tmem_ld_wait();
+  tc::tc_fence_before();
+  tc::mbar_arrive(tempty);
+#pragma unroll
+  for (int ch = 0; ch < NCH; ++ch) {
+    const int c0 = chalf * CW + 16 * ch;
     uint32_t packed[8];
 #pragma unroll
     for (int j = 0; j < 16; j += 2) {
-      const uint32_t g = pack_bf16(__uint_as_float(a[cur][j]), __uint_as_float(a[cur][j + 1]));
-      const uint32_t n = pack_bf16(__uint_as_float(b[cur][j]), __uint_as_float(b[cur][j + 1]));
+      const uint32_t g = pack_bf16(__uint_as_float(a[ch][j]), __uint_as_float(a[ch][j + 1]));
+      const uint32_t n = pack_bf16(__uint_as_float(b[ch][j]), __uint_as_float(b[ch][j + 1]));
       float a0, a1;
       gelu_pair(__uint_as_float(g << 16), __uint_as_float(g & 0xFFFF0000u), a0, a1);
       packed[j >> 1] = bf2_mul(pack_bf16(a0, a1), n);   // GELU output cast to bf16, times the linear half
@@ -128,7 +130,6 @@ __device__ __forceinline__ void glu_epilogue_tile(uint32_t tacc, int chalf, __nv
         dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
       }
     }
-    if (ch + 1 < NCH) tc::tmem_ld_wait();
   }
 }
 
@@ -255,13 +256,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const uint32_t tacc = tmem_base + buf * C::ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* orow = out + (long long)row * P.ldo + col0;
       if constexpr (GLU) {
-        glu_epilogue_tile<BN, CW>(tacc, chalf, orow, row < P.M, P.wide_out);
+        glu_epilogue_tile<BN, CW>(tacc, chalf, orow, row < P.M, P.wide_out, tempty + buf);
       } else {
-#pragma unroll 1
-      for (int c0 = chalf * CW; c0 < (chalf + 1) * CW; c0 += 16) {
-        uint32_t a[16];
-        tc::tmem_ld16(tacc + c0, a);
-        tc::tmem_ld_wait();
+      // the warp's columns go to registers in one sweep and the buffer is handed back before the stores
+      constexpr int NCH = CW / 16;
+      uint32_t acc_r[NCH][16];
+#pragma unroll
+      for (int ch = 0; ch < NCH; ++ch) tc::tmem_ld16(tacc + chalf * CW + 16 * ch, acc_r[ch]);
+      tc::tmem_ld_wait();
+      tc::tc_fence_before();
+      tc::mbar_arrive(tempty + buf);
+#pragma unroll
+      for (int ch = 0; ch < NCH; ++ch) {
+        const int c0 = chalf * CW + 16 * ch;
+        const uint32_t (&a)[16] = acc_r[ch];
         uint32_t packed[8];
 #pragma unroll
         for (int j = 0; j < 16; j += 2) {
@@ -285,8 +293,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       }
       }
-      tc::tc_fence_before();
-      tc::mbar_arrive(tempty + buf);
       if ((buf ^= 1) == 0) bphase ^= 1;
     }
   }
@@ -475,9 +481,7 @@ glu_res_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc::tc_fence_after();
         const uint32_t tacc = tmem_base + buf * 2 * BN + ((uint32_t)(quarter * 32) << 16);
         __nv_bfloat16* orow = out + (long long)row * P.ldo + kb * P.q + (nt0 + t) * BN;
-        glu_epilogue_tile<BN, CW>(tacc, chalf, orow, row < P.M, P.wide_out);
-        tc::tc_fence_before();
-        tc::mbar_arrive(tempty + buf);
+        glu_epilogue_tile<BN, CW>(tacc, chalf, orow, row < P.M, P.wide_out, tempty + buf);
         if ((buf ^= 1) == 0) bphase ^= 1;
       }
     }
