@@ -591,6 +591,8 @@ int glu_tc_launch(const m2_glu_args* a, cudaStream_t st) {
   P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->inter;
   P.out = a->h; P.ldo = a->ldh; P.bias = nullptr;
   P.wide_out = m2_aligned(a->h, 32) && a->ldh % 16 == 0 && q % 16 == 0;
+  // K <= 192 per block: x slices resident in shared memory.  M2_GLU_DUAL=1 in the environment selects the
+  // streaming two-accumulator kernel instead (the tests compare the two bit for bit).
   if (P.ksteps <= res::MAX_KS && !getenv("M2_GLU_DUAL")) {
     ResParams R;
     R.M = a->m; R.p = p; R.q = q; R.nb_half = a->nblocks / 2; R.ksteps = P.ksteps; R.ntn = q / res::BN;
