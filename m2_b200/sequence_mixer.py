@@ -22,7 +22,7 @@ class _AugmentedLinear:
     rounded to bf16 exactly once -- like F.linear -- whatever layout the GEMM writes."""
 
     def __init__(self):
-        self.key, self.w = None, None
+        self.key, self.w, self.b = None, None, None
 
     def get(self, lin):
         key = (lin.weight.data_ptr(), lin.weight._version, lin.bias._version, lin.weight.device)
@@ -32,6 +32,7 @@ class _AugmentedLinear:
             w[:, :in_f] = lin.weight.detach()
             w[:, in_f] = lin.bias.detach()
             self.key, self.w = key, w
+            self.b = w[:, in_f].contiguous()          # the bf16-rounded bias on its own, for addmm
         return self.w
 
 
@@ -156,17 +157,17 @@ class MonarchMixerSequenceMixing(nn.Module):
                 if u_t is None or u_t.shape != (D, B, L) or u_t.device != u.device:
                     u_t = ops.time_major_f16(ures)
             buf = getattr(self, "_y_t", None)
-            if buf is None or buf.shape != (D + _PAD, B * L) or buf.device != u.device:
-                buf = torch.empty((D + _PAD, B * L), dtype=torch.bfloat16, device=u.device)
-                buf[D] = 1.0
-                buf[D + 1:] = 0.0
+            if buf is None or buf.shape != (D, B * L) or buf.device != u.device:
+                buf = torch.empty((D, B * L), dtype=torch.bfloat16, device=u.device)
                 self._y_t = buf
             ops.longconv_fwd(xin_t.view(3 * D, B, L).permute(1, 2, 0),
                              u_t.permute(1, 2, 0) if u_t is not None else None,
                              self.short_filter.weight, self.short_filter.bias, specs, None,
-                             kind=3, bf16_rounding=True, out=buf[:D].view(D, B, L).permute(1, 2, 0),
+                             kind=3, bf16_rounding=True, out=buf.view(D, B, L).permute(1, 2, 0),
                              yu_bf16=ures is not None and getattr(ures, "_m2_src_dtype", ures.dtype) == torch.bfloat16)
-            return torch.matmul(buf.t(), w_out.t()).view(B, L, D)
+            # the output is row-major (B*L, D), so the library GEMM's own bias epilogue applies (bias added
+            # in the float32 accumulator, one rounding, as F.linear) and K stays 768 instead of 768 + 64
+            return torch.addmm(self._aug_out.b, buf.t(), w_out[:, :D].t()).view(B, L, D)
 
     def forward(self, u, **kwargs):
         _check_forward_only(self, u)
