@@ -5,8 +5,7 @@
  * Conventions
  *   - plain C: pointers, sizes and strides only; no framework types.
  *   - every pointer marked "device" is caller-owned device memory of the CURRENT device;
- *     the library never allocates or frees device memory in these calls (the one
- *     exception is a per-device cache of constant twiddle tables built on first use).
+ *     the library never allocates or frees device memory in these calls.
  *   - calls are asynchronous on `stream` (a cudaStream_t passed as void*).
  *   - return value: M2_OK or an m2_status error; m2_last_error() gives a thread-local
  *     human-readable message.  Nothing aborts, nothing throws.
@@ -27,7 +26,7 @@
 extern "C" {
 #endif
 
-#define M2_B200_ABI_VERSION 1
+#define M2_B200_ABI_VERSION 2
 
 typedef enum { M2_F32 = 0, M2_BF16 = 1, M2_F16 = 2 /* only where an entry point says so */ } m2_dtype;
 
@@ -40,6 +39,13 @@ typedef enum {
   M2_ERR_DEVICE = 5        /* a kernel gave up on a bounded wait (see m2_device_status) */
 } m2_status;
 
+/* Bits of the device status word read by m2_device_status(). */
+#define M2_DEV_TIMEOUT_TMA   1   /* a wait for a TMA load ran out */
+#define M2_DEV_TIMEOUT_MMA   2   /* a wait for tensor-core work or a free accumulator ran out */
+#define M2_DEV_TIMEOUT_EPI   4   /* an epilogue's wait for an accumulator ran out */
+#define M2_DEV_TIMEOUT_EMPTY 8   /* a producer's wait for a free shared-memory stage ran out */
+#define M2_DEV_BAD_INDEX     16  /* m2_embed_layernorm_fwd met an id outside its table (clamped) */
+
 /* ABI version of the loaded library (== M2_B200_ABI_VERSION it was built with). */
 int m2_version(void);
 
@@ -49,6 +55,12 @@ const char* m2_last_error(void);
 /* Reads and clears the device-side status word of the current device: 0 = no kernel has
  * given up on a bounded wait since the last call.  Synchronises the device. */
 int m2_device_status(int* status_out);
+
+/* Failure-path self-test (no counterpart in the reference): launches one thread that waits, for at most
+ * limit_ns (1 ns .. 1 s) of the GPU's timer, on a barrier nothing arrives at.  The wait gives up exactly as
+ * a stalled wait inside the kernels would: the launch completes, M2_DEV_TIMEOUT_TMA appears in
+ * m2_device_status() and later launches run normally.  Nothing faults or hangs. */
+int m2_selftest_wait_timeout(unsigned long long limit_ns, void* stream);
 
 /* ---------------------------------------------------------------------------------------
  * Implicit long-convolution filter.
@@ -205,6 +217,8 @@ typedef struct {
   const void* x; long long ldx;
   const void* wg;
   void* h; long long ldh;
+  int variant;   /* 0: the library picks the kernel; 1: always the kernel that streams x and wg tiles through
+                    shared memory (the general one; results are bit-identical, kept selectable for cross-checks) */
 } m2_glu_args;
 
 int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);
@@ -250,6 +264,10 @@ int m2_add_layernorm_fwd(const m2_add_layernorm_args* args, void* stream);
  *   tables float32, row-major with n columns; ids int64 (m); token_type_ids NULL = type 0 everywhere;
  *   pos_table NULL = no position term; position_ids NULL = position r % seq_len for row r.
  *   n a multiple of 256 up to 2048.  out may be NULL when out_bf16 is given.
+ *   vocab_rows / type_rows / pos_rows: row counts of the tables.  An id outside [0, rows) is never read
+ *   out of bounds: it is clamped into the table and M2_DEV_BAD_INDEX is set in the device status word
+ *   (torch's embedding would raise a device-side assert there); seq_len > pos_rows without explicit
+ *   position_ids is refused on the host.
  * ------------------------------------------------------------------------------------- */
 typedef struct {
   int m, n;
@@ -260,6 +278,7 @@ typedef struct {
   float* out; long long ldo;
   void* out_bf16; long long ld_bf16; int bf16_pad_cols;
   void* out_tm_f16; long long tm_sb, tm_sc; int seq_len;
+  long long vocab_rows, type_rows, pos_rows;
 } m2_embed_layernorm_args;
 
 int m2_embed_layernorm_fwd(const m2_embed_layernorm_args* args, void* stream);

@@ -10,7 +10,7 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libm2b200.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 M2_F32, M2_BF16, M2_F16 = 0, 1, 2
 
@@ -65,7 +65,7 @@ class GluArgs(C.Structure):
         ("m", C.c_int), ("d_model", C.c_int), ("inter", C.c_int), ("nblocks", C.c_int),
         ("dtype", C.c_int),
         ("x", C.c_void_p), ("ldx", C.c_longlong), ("wg", C.c_void_p),
-        ("h", C.c_void_p), ("ldh", C.c_longlong),
+        ("h", C.c_void_p), ("ldh", C.c_longlong), ("variant", C.c_int),
     ]
 
 
@@ -91,6 +91,7 @@ class EmbedLayernormArgs(C.Structure):
         ("out", C.c_void_p), ("ldo", C.c_longlong),
         ("out_bf16", C.c_void_p), ("ld_bf16", C.c_longlong), ("bf16_pad_cols", C.c_int),
         ("out_tm_f16", C.c_void_p), ("tm_sb", C.c_longlong), ("tm_sc", C.c_longlong), ("seq_len", C.c_int),
+        ("vocab_rows", C.c_longlong), ("type_rows", C.c_longlong), ("pos_rows", C.c_longlong),
     ]
 
 
@@ -99,6 +100,7 @@ SYMBOLS = {
     "m2_version": (C.c_int, []),
     "m2_last_error": (C.c_char_p, []),
     "m2_device_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "m2_selftest_wait_timeout": (C.c_int, [C.c_ulonglong, C.c_void_p]),
     "m2_filter_row_len": (C.c_int, [C.c_int]),
     "m2_hyena_filter": (C.c_int, [C.POINTER(FilterArgs), C.c_void_p]),
     "m2_longconv_kind": (C.c_int, [C.c_int, C.c_int, C.c_int]),

@@ -13,6 +13,7 @@ import torch.nn as nn
 from torch.nn import init
 
 from . import ops
+from ._tags import forward_only
 from .hyena_filter import _autocast_bf16
 
 
@@ -45,7 +46,6 @@ def _compute_dtype(x):
 
 def blockdiag_multiply(x, weight, _cache=None):
     """out[..., k*q:(k+1)*q] = x[..., k*p:(k+1)*p] @ weight[k].T ; weight (nblocks, q, p)."""
-    from .sequence_mixer import _check_forward_only
     nb, q, p = weight.shape
     if x.shape[-1] != nb * p:
         raise AssertionError(f"last dimension {x.shape[-1]} != nblocks*p = {nb * p}")
@@ -148,9 +148,8 @@ class BlockdiagLinear(StructuredLinear):
             return w.contiguous()
         return self._w_cache.get(self.weight) if dt == torch.bfloat16 else w.to(dt)
 
+    @forward_only
     def forward_matmul(self, x):
-        from .sequence_mixer import _check_forward_only
-        _check_forward_only(self, x)
         return self._run(x, None)
 
     def _run(self, x, bias):
@@ -165,11 +164,10 @@ class BlockdiagLinear(StructuredLinear):
         out = ops.blockdiag_fwd(x2, self._weight_as(dt), bias, x2.shape[-1], self.out_features)
         return out.reshape(*x.shape[:-1], self.out_features)
 
+    @forward_only
     def forward(self, x):
         """Padding of the input, the block multiply, the crop and the bias add run as one
         kernel."""
-        from .sequence_mixer import _check_forward_only
-        _check_forward_only(self, x)
         if x.shape[-1] > self.in_features_extended:
             raise RuntimeError(f"input has {x.shape[-1]} features, layer takes {self.in_features}")
         return self._run(x, self.bias)

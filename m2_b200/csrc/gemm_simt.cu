@@ -150,10 +150,21 @@ add_layernorm_kernel(const TI* a, long long lda, const TI* b, long long ldb, con
 // Row selection for the embeddings' LayerNorm: addend a is row ids_a[r] of a table, addend b row
 // ids_b[r] (or r % b_mod) of a second one, and a third float32 addend c (row ids_c[r], or row 0) joins
 // as (a + c) + b -- the reference's word + token-type, then + position order.
+// rows_a / rows_b / rows_c: row counts of the three tables; an id outside [0, rows) is clamped into the table
+// and reported through the device status word (ST_BAD_INDEX) instead of being read out of bounds.
 struct LnGather {
   const long long* ids_a; const long long* ids_b; int b_mod;
   const float* c; long long ldc; const long long* ids_c;
+  long long rows_a, rows_b, rows_c;
 };
+
+constexpr int ST_BAD_INDEX = 16;   // bit of m2_dev_status_word: an embedding id was outside its table
+
+__device__ __forceinline__ long long clamp_row(long long id, long long rows, bool& bad) {
+  if (id < 0) { bad = true; return 0; }
+  if (id >= rows) { bad = true; return rows - 1; }
+  return id;
+}
 
 template <typename TI, typename TO, int VI>
 __global__ void __launch_bounds__(512)
@@ -187,11 +198,14 @@ add_layernorm_warp_kernel(const TI* a, long long lda, const TI* b, long long ldb
       }
     }
   } else {
-    const long long ra = gt.ids_a ? gt.ids_a[warp] : warp;
-    const long long rb = gt.ids_b ? gt.ids_b[warp] : (gt.b_mod > 0 ? warp % gt.b_mod : warp);
+    bool bad = false;
+    const long long ra = gt.ids_a ? clamp_row(gt.ids_a[warp], gt.rows_a, bad) : warp;
+    const long long rb = gt.ids_b ? clamp_row(gt.ids_b[warp], gt.rows_b, bad) : (gt.b_mod > 0 ? warp % gt.b_mod : warp);
+    const long long rc = gt.ids_c ? clamp_row(gt.ids_c[warp], gt.rows_c, bad) : 0;
+    if (bad && lane == 0) atomicOr(&m2_dev_status_word, ST_BAD_INDEX);
     const float4* pa = reinterpret_cast<const float4*>(a + ra * lda);
     const float4* pb = b ? reinterpret_cast<const float4*>(b + rb * ldb) : nullptr;
-    const float4* pc = gt.c ? reinterpret_cast<const float4*>(gt.c + (gt.ids_c ? gt.ids_c[warp] : 0) * gt.ldc) : nullptr;
+    const float4* pc = gt.c ? reinterpret_cast<const float4*>(gt.c + rc * gt.ldc) : nullptr;
 #pragma unroll
     for (int i = 0; i < VI; ++i) {
       const int q = (i * 32 + lane) * 2;
@@ -362,7 +376,7 @@ extern "C" int m2_blockdiag_glu_fwd(const m2_glu_args* a, void* stream) {
 static int add_layernorm_core(const m2_add_layernorm_args* a, const m2::LnGather& gather, void* stream);
 
 extern "C" int m2_add_layernorm_fwd(const m2_add_layernorm_args* a, void* stream) {
-  const m2::LnGather none = {nullptr, nullptr, 0, nullptr, 0, nullptr};
+  const m2::LnGather none = {nullptr, nullptr, 0, nullptr, 0, nullptr, 0, 0, 0};
   return add_layernorm_core(a, none, stream);
 }
 
@@ -374,6 +388,10 @@ extern "C" int m2_embed_layernorm_fwd(const m2_embed_layernorm_args* e, void* st
              "m2_embed_layernorm_fwd: NULL pointer");
   M2_REQUIRE(!e->pos_table || e->position_ids || e->seq_len > 0, M2_ERR_ARG,
              "m2_embed_layernorm_fwd: position table without position_ids needs seq_len");
+  M2_REQUIRE(e->vocab_rows > 0 && e->type_rows > 0 && (!e->pos_table || e->pos_rows > 0), M2_ERR_ARG,
+             "m2_embed_layernorm_fwd: table row counts must be positive");
+  M2_REQUIRE(!e->pos_table || e->position_ids || e->seq_len <= e->pos_rows, M2_ERR_ARG,
+             "m2_embed_layernorm_fwd: seq_len %d exceeds the position table's %lld rows", e->seq_len, e->pos_rows);
   M2_REQUIRE(e->n % 256 == 0 && e->n <= 2048 && m2_aligned(e->word_table, 16) && m2_aligned(e->type_table, 16) &&
              m2_aligned(e->pos_table, 16), M2_ERR_UNSUPPORTED,
              "m2_embed_layernorm_fwd: needs hidden size a multiple of 256 up to 2048 and 16-byte aligned tables");
@@ -385,7 +403,7 @@ extern "C" int m2_embed_layernorm_fwd(const m2_embed_layernorm_args* e, void* st
   a.out = e->out; a.ldo = e->ldo; a.out_bf16 = e->out_bf16; a.ld_bf16 = e->ld_bf16; a.bf16_pad_cols = e->bf16_pad_cols;
   a.out_tm_f16 = e->out_tm_f16; a.tm_sb = e->tm_sb; a.tm_sc = e->tm_sc; a.seq_len = e->seq_len;
   const m2::LnGather g = {e->input_ids, e->pos_table ? e->position_ids : nullptr, e->pos_table && !e->position_ids ? e->seq_len : 0,
-                          e->type_table, e->n, e->token_type_ids};
+                          e->type_table, e->n, e->token_type_ids, e->vocab_rows, e->pos_rows, e->type_rows};
   return add_layernorm_core(&a, g, stream);
 }
 

@@ -50,14 +50,6 @@ int m2_make_tmap_bf16_2d(CUtensorMap* map, const void* base, uint64_t rows, uint
 
 namespace gemm {
 
-#ifdef M2_GEMM_TIMING   // tuning only: cycles one thread per role spends waiting / working
-__device__ unsigned long long g_gemm_cycles[16];
-#define GT_T0() long long gt_prev_ = clock64()
-#define GT_MARK(cond, i) do { if (cond) { long long n_ = clock64(); atomicAdd(&g_gemm_cycles[i], (unsigned long long)(n_ - gt_prev_)); gt_prev_ = n_; } } while (0)
-#else
-#define GT_T0() do {} while (0)
-#define GT_MARK(cond, i) do {} while (0)
-#endif
 
 constexpr int BM = 128;
 constexpr int BK = 64;                 // one 128-byte swizzle row of bf16
@@ -171,13 +163,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      GT_T0();
       for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
         const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
         for (int ks = 0; ks < P.ksteps; ++ks) {
-          GT_MARK(true, 0);
           if (!tc::mbar_wait(empty + stage, phase ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          GT_MARK(true, 1);
           unsigned char* st = smem + stage * C::STAGE_BYTES;
           tc::mbar_expect_tx(full + stage, C::STAGE_BYTES);
           tc::tma_load_2d(st, &tmA, full + stage, kb * P.p + ks * BK, mt * BM);
@@ -207,18 +196,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int buf = 0; uint32_t bphase = 0;
       bool ok = true;
-      const bool gt_iss = warp == 1;
-      GT_T0();
       for (int tile = blockIdx.x; tile < P.total_tiles && ok; tile += gridDim.x) {
-        GT_MARK(gt_iss, 2);
         if (!tc::mbar_wait(tempty + buf, bphase ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) break;
-        GT_MARK(gt_iss, 3);
         tc::tc_fence_after();
         const uint32_t acc = tmem_base + buf * C::ACC_COLS + chain * BN;
         for (int ks = 0; ks < P.ksteps; ++ks) {
-          GT_MARK(gt_iss, 2);
           if (!tc::mbar_wait(full + stage, phase, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
-          GT_MARK(gt_iss, 4);
           tc::tc_fence_after();
           const uint64_t off = (uint64_t)(stage * (C::STAGE_BYTES >> 4));
           const uint64_t dA = dA0 + off, dB = dB0 + off;
@@ -243,13 +226,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     static_assert(CW % 16 == 0, "column slice must be a multiple of 16");
     int buf = 0; uint32_t bphase = 0;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
-    const bool gt_me = (warp == EPI_WARP0 && lane == 0);
-    GT_T0();
     for (int tile = blockIdx.x; tile < P.total_tiles; tile += gridDim.x) {
       const int nt = tile % P.ntn, kb = (tile / P.ntn) % P.nb_out, mt = tile / (P.ntn * P.nb_out);
-      GT_MARK(gt_me, 5);
       if (!tc::mbar_wait(tfull + buf, bphase, abort_flag, tc::ST_TIMEOUT_EPI)) break;
-      GT_MARK(gt_me, 6);
       tc::tc_fence_after();
       const int row = mt * BM + quarter * 32 + lane;
       const int col0 = kb * P.q + nt * BN;
@@ -429,23 +408,17 @@ glu_res_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int buf = 0; uint32_t bphase = 0;
       bool ok = true;
-      const bool gt_iss = warp == 1;
-      GT_T0();
       for (int unit = u0; unit < u1 && ok; ++unit) {
         int pair, mt, kb, nt0, ntiles;
         decode(unit, pair, mt, kb, nt0, ntiles);
         const bool x_changes = unit + 1 < u1 && (unit + 1) / P.ngroups != pair;
         for (int t = 0; t < ntiles && ok; ++t) {
-          GT_MARK(gt_iss, 2);
           if (!tc::mbar_wait(tempty + buf, bphase ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) { ok = false; break; }
-          GT_MARK(gt_iss, 3);
           tc::tc_fence_after();
           const uint32_t acc = tmem_base + buf * 2 * BN + chain * BN;
           const bool release_x = x_changes && t == ntiles - 1;
           for (int ks = 0; ks < P.ksteps; ++ks) {
-            GT_MARK(gt_iss, 2);
             if (!tc::mbar_wait(b_full + stage, phase, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
-            GT_MARK(gt_iss, 4);
             tc::tc_fence_after();
             const uint64_t dA = dA0 + (uint64_t)(ks * (A_BYTES >> 4)), dB = dB0 + (uint64_t)(stage * (B_STAGE >> 4));
 #pragma unroll
@@ -468,16 +441,12 @@ glu_res_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int buf = 0; uint32_t bphase = 0;
     bool ok = true;
     __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(P.out);
-    const bool gt_me = (warp == EPI_WARP0 && lane == 0);
-    GT_T0();
     for (int unit = u0; unit < u1 && ok; ++unit) {
       int pair, mt, kb, nt0, ntiles;
       decode(unit, pair, mt, kb, nt0, ntiles);
       const int row = mt * BM + quarter * 32 + lane;
       for (int t = 0; t < ntiles; ++t) {
-        GT_MARK(gt_me, 5);
         if (!tc::mbar_wait(tfull + buf, bphase, abort_flag, tc::ST_TIMEOUT_EPI)) { ok = false; break; }
-        GT_MARK(gt_me, 6);
         tc::tc_fence_after();
         const uint32_t tacc = tmem_base + buf * 2 * BN + ((uint32_t)(quarter * 32) << 16);
         __nv_bfloat16* orow = out + (long long)row * P.ldo + kb * P.q + (nt0 + t) * BN;
@@ -500,19 +469,6 @@ glu_res_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
-#ifdef M2_GEMM_TIMING
-}  // namespace gemm
-}  // namespace m2
-extern "C" int m2_debug_gemm_cycles(unsigned long long* out, int reset) {
-  unsigned long long z[16] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, m2::gemm::g_gemm_cycles, sizeof(z));
-  if (reset) cudaMemcpyToSymbol(m2::gemm::g_gemm_cycles, z, sizeof(z));
-  return 0;
-}
-namespace m2 {
-namespace gemm {
-#endif
 
 static int sm_count() {
   static int cached[64] = {0};
@@ -591,9 +547,9 @@ int glu_tc_launch(const m2_glu_args* a, cudaStream_t st) {
   P.total_tiles = P.ntm * P.nb_out * P.ntn; P.out_cols = a->inter;
   P.out = a->h; P.ldo = a->ldh; P.bias = nullptr;
   P.wide_out = m2_aligned(a->h, 32) && a->ldh % 16 == 0 && q % 16 == 0;
-  // K <= 192 per block: x slices resident in shared memory.  M2_GLU_DUAL=1 in the environment selects the
-  // streaming two-accumulator kernel instead (the tests compare the two bit for bit).
-  if (P.ksteps <= res::MAX_KS && !getenv("M2_GLU_DUAL")) {
+  // K <= 192 per block: x slices resident in shared memory, unless the caller asks for the streaming
+  // two-accumulator kernel (variant 1; the tests compare the two bit for bit).
+  if (P.ksteps <= res::MAX_KS && a->variant != 1) {
     ResParams R;
     R.M = a->m; R.p = p; R.q = q; R.nb_half = a->nblocks / 2; R.ksteps = P.ksteps; R.ntn = q / res::BN;
     // column tiles per unit: about 6 units per SM, so that the contiguous ranges balance

@@ -29,17 +29,6 @@
 namespace m2 {
 namespace lc {
 
-// Phase timing for kernel tuning: built only with -DM2_LC_TIMING; worker thread 0 of every
-// CTA adds the clock cycles it spent in each phase to a device array.
-#ifdef M2_LC_TIMING
-__device__ unsigned long long g_phase_cycles[16];
-#define LC_T0() long long t_prev_ = clock64()
-#define LC_MARK(i) do { if (tid == 0) { long long n_ = clock64(); atomicAdd(&g_phase_cycles[i], (unsigned long long)(n_ - t_prev_)); t_prev_ = n_; } } while (0)
-#else
-#define LC_T0() do {} while (0)
-#define LC_MARK(i) do {} while (0)
-#endif
-
 constexpr int NFFT = 256;
 constexpr int CT = 128;                    // channels per unit
 constexpr int THREADS = 256;
@@ -295,7 +284,6 @@ longconv_tc128_kernel(const Params P) {
       }
     }
 
-    LC_T0();
     for (int f = 0; f < P.nf && ok; ++f) {
       // ---------------- operand tiles of stage F1: a[t] as fp16, tile n2 = t % 8, k = t / 8 ----------------
       {
@@ -366,9 +354,7 @@ longconv_tc128_kernel(const Params P) {
           sts64(Hs + j * TILE + prow0 + 16 + pkoff, hv[1][j][0], hv[1][j][1]);
         }
       }
-      LC_MARK(0);
       LC_STAGE(0)
-      LC_MARK(1);
 
       // ---------------- hop 1: F1 result -> operand tiles of F2 ----------------
 #pragma unroll 1
@@ -402,9 +388,7 @@ longconv_tc128_kernel(const Params P) {
       for (int kl = 0; kl < 4; ++kl) { gq[kl][0] = __ldg(G + 2 * kl); gq[kl][1] = __ldg(G + 2 * kl + 1); }
       const float bk = __ldg(P.bias[f] + c0 + r) * KAPPA;
       tc::tc_fence_before();
-      LC_MARK(2);
       LC_STAGE(1)
-      LC_MARK(3);
 
       // ---------------- hop 2: spectrum x filter -> operand tiles of I2 ----------------
 #pragma unroll
@@ -437,9 +421,7 @@ longconv_tc128_kernel(const Params P) {
         }
       }
       tc::tc_fence_before();
-      LC_MARK(4);
       LC_STAGE(2)
-      LC_MARK(5);
 
       // ---------------- hop 3: I2 result -> operand tiles of I1 (tile 2 n2 + ri, k = k1) ----------------
 #pragma unroll 1
@@ -464,9 +446,7 @@ longconv_tc128_kernel(const Params P) {
           sts128(Hs + (2 * n2 + ri) * TILE + rowoff + half * 128, pk[n2][0], pk[n2][1], pk[n2][2], pk[n2][3]);
       }
       tc::tc_fence_before();
-      LC_MARK(6);
       LC_STAGE(3)
-      LC_MARK(7);
 
       // ---------------- hop 4: y (float32) -> shared [t][channel] ----------------
       {
@@ -503,9 +483,7 @@ longconv_tc128_kernel(const Params P) {
         }
       }
       tc::tc_fence_before();
-      LC_MARK(8);
       LC_WORKER_BARRIER()
-      LC_MARK(9);
 
       // ---------------- epilogue: gate / residual add, coalesced bf16 stores ----------------
       {
@@ -537,9 +515,7 @@ longconv_tc128_kernel(const Params P) {
           }
         }
       }
-      LC_MARK(10 + (f == 0 ? 0 : 1));
       LC_WORKER_BARRIER()                                    // the y tile is free again
-      LC_MARK(12);
     }
   }
 #undef LC_STAGE
@@ -556,15 +532,6 @@ constexpr size_t SMEM_BYTES = H_BYTES + MAT_BYTES + 64 + 128;
 
 }  // namespace lc
 
-#ifdef M2_LC_TIMING
-extern "C" int m2_debug_phase_cycles(unsigned long long* out, int reset) {
-  unsigned long long z[16] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, lc::g_phase_cycles, sizeof(z));
-  if (reset) cudaMemcpyToSymbol(lc::g_phase_cycles, z, sizeof(z));
-  return 0;
-}
-#endif
 
 int longconv_tc_supported(int seq_len, m2_dtype act_dtype, int d_model) {
   return act_dtype == M2_BF16 && seq_len > 64 && seq_len <= 128 && d_model % lc::CT == 0;

@@ -167,17 +167,6 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// Role timing for kernel tuning: built only with -DM2_TZ_TIMING; one thread per role adds the
-// clock cycles it spent in each phase to a device array.
-#ifdef M2_TZ_TIMING
-__device__ unsigned long long g_tz_cycles[16];
-#define TZ_T0() long long tz_prev_ = clock64()
-#define TZ_MARK(cond, i) do { if (cond) { long long n_ = clock64(); atomicAdd(&g_tz_cycles[i], (unsigned long long)(n_ - tz_prev_)); tz_prev_ = n_; } } while (0)
-#else
-#define TZ_T0() do {} while (0)
-#define TZ_MARK(cond, i) do {} while (0)
-#endif
-
 // warp-uniform bounded wait: every lane polls, the warp leaves together
 #define TZ_WAIT(bar, parity, why) \
   if (!__all_sync(0xffffffffu, tc::mbar_wait((bar), (parity), abort_flag, (why)))) break
@@ -235,7 +224,6 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     if (lane == 0) {
       int it = 0, epoch = -1, prev_c = -1;
       bool ok = true;
-      TZ_T0();
       for (int unit = u_first; unit < u_last && ok; ++unit) {
         const int c = unit / P.nbt, b0 = (unit % P.nbt) * TB;
         if (c != prev_c) {
@@ -249,9 +237,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         }
         for (int j = 0; j < P.nsub; ++j, ++it) {
           const int s = it % NST;
-          TZ_MARK(true, 11);
           if (!tc::mbar_wait(empty_main + s, ((it / NST) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
-          TZ_MARK(true, 12);
           unsigned char* st = smem + s * STAGE_BYTES;
           tc::mbar_expect_tx(full_main + s, 2 * RAW_BYTES);
           tc::tma_load_3d(st, &tmX, full_main + s, TW * j - HALO, b0, c);
@@ -292,17 +278,14 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       constexpr uint32_t idesc = tc::make_idesc(TB, 128, 0);
       int it = 0, ut = 0, epoch = -1, prev_c = -1, ui = 0;
       bool ok = true;
-      TZ_T0();
       for (int unit = u_first; unit < u_last && ok; ++unit, ++ui) {
         const int c = unit / P.nbt;
         if (c != prev_c) {
           prev_c = c; ++epoch;
           if (!tc::mbar_wait(strip_full + (epoch & 1), (epoch >> 1) & 1, abort_flag, tc::ST_TIMEOUT_TMA)) break;
         }
-        TZ_MARK(true, 0);
         const int p = epoch & 1, acc = ui & 1;
         if (!tc::mbar_wait(tmem_empty + acc, ((ui >> 1) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_MMA)) break;
-        TZ_MARK(true, 1);
         tc::tc_fence_after();
         const uint32_t tacc = tmem_base + acc * 256;
         const uint32_t strip0 = tc::smem_u32(smem + OFF_STRIP + (2 * p) * STRIP_BYTES);
@@ -310,9 +293,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           const int s = it % NST, a = it % NA1;
           if (P.nf == 2 && (j & 1) == 0 &&
               !tc::mbar_wait(u_full + ut % NU, (ut / NU) & 1, abort_flag, tc::ST_TIMEOUT_TMA)) { ok = false; break; }
-          TZ_MARK(true, 2);
           if (!tc::mbar_wait(a1_full + a, (it / NA1) & 1, abort_flag, tc::ST_TIMEOUT_MMA)) { ok = false; break; }
-          TZ_MARK(true, 3);
           tc::tc_fence_after();
           const uint32_t a1 = tc::smem_u32(smem + OFF_A1 + a * OP_BYTES);
           // 64-step tile of the residual operand: K step q of it starts 32 q bytes into the swizzled rows
@@ -329,7 +310,6 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           }
           if (P.nf == 2 && ((j & 1) || j == P.nsub - 1)) { tc::mma_commit(u_empty + ut % NU); ++ut; }
           tc::mma_commit(a1_empty + a);
-          TZ_MARK(true, 4);
         }
         if (!ok) break;
         tc::mma_commit(tmem_full + acc);
@@ -342,8 +322,6 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int hh = (warp - CTRL_WARPS) >> 2;             // which half of the time axis
     const int r = quarter * 32 + lane;
     int ui = 0;
-    const bool tz_me = (warp == CTRL_WARPS && lane == 0);
-    TZ_T0();
     for (int unit = u_first; unit < u_last; ++unit, ++ui) {
       const int c = unit / P.nbt, b = (unit % P.nbt) * TB + r;
       const int acc = ui & 1;
@@ -352,9 +330,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const int ch = P.D + c;
       const float w0 = bf16r(__ldg(P.sw + 3 * ch)), w1 = bf16r(__ldg(P.sw + 3 * ch + 1)),
                   w2 = bf16r(__ldg(P.sw + 3 * ch + 2)), wb = bf16r(__ldg(P.sb + ch));
-      TZ_MARK(tz_me, 5);
       TZ_WAIT(tmem_full + acc, (ui >> 1) & 1, tc::ST_TIMEOUT_EPI);
-      TZ_MARK(tz_me, 6);
       tc::tc_fence_after();
       const uint32_t tacc = tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16);
       __nv_bfloat16* orow = P.out + (long long)c * P.osc + (long long)b * P.osb;
@@ -365,9 +341,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         if (t0 >= P.L) break;
         const int j = 4 * (ui % XSETS) + t0 / TW, toff = t0 % TW;   // x2 slot
         if ((k & 1) == 0) {
-          TZ_MARK(tz_me, 5);
           if (!__all_sync(0xffffffffu, tc::mbar_wait(x2_full + j, (ui / XSETS) & 1, abort_flag, tc::ST_TIMEOUT_TMA))) { ok = false; break; }
-          TZ_MARK(tz_me, 7);
         }
         uint32_t d1[16], d2[16];
         tc::tmem_ld16(tacc + t0, d1);
@@ -429,8 +403,6 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
     const int r = (pw & 3) * 32 + lane, h = pw >> 2;      // batch row, which 16 of the stage's 32 steps
     int it = 0;
     bool ok = true;
-    const bool tz_me = (pw == 0 && lane == 0);
-    TZ_T0();
     for (int unit = u_first; unit < u_last && ok; ++unit) {
       const int c = unit / P.nbt;
       const int cv = 2 * P.D + c;
@@ -441,9 +413,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const f32x2 wb = f2_pack(bf16r(__ldg(P.sb + c)), bf16r(__ldg(P.sb + cv)));
       for (int j = 0; j < P.nsub; ++j, ++it) {
         const int s = it % NST, a = it % NA1;
-        TZ_MARK(tz_me, 8);
         if (!__all_sync(0xffffffffu, tc::mbar_wait(full_main + s, (it / NST) & 1, abort_flag, tc::ST_TIMEOUT_TMA))) { ok = false; break; }
-        TZ_MARK(tz_me, 9);
         const uint32_t xrow = tc::smem_u32(smem + s * STAGE_BYTES) + r * RAW_ROW + h * 32;
         const uint32_t hx = lds32(xrow + 12), hv = lds32(xrow + RAW_BYTES + 12);
         const uint4 x0 = lds128(xrow + 16), x1 = lds128(xrow + 32);
@@ -472,9 +442,7 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
             else if (tbase + 2 * i + 1 >= P.L) aw[i] &= 0x0000ffffu;
           }
         }
-        TZ_MARK(tz_me, 8);
         if (!__all_sync(0xffffffffu, tc::mbar_wait(a1_empty + a, ((it / NA1) & 1) ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY))) { ok = false; break; }
-        TZ_MARK(tz_me, 10);
         const uint32_t dst = tc::smem_u32(smem + OFF_A1 + a * OP_BYTES) + (2 * h) * OP_LBO + r * 16;
         sts128(dst, aw[0], aw[1], aw[2], aw[3]);
         sts128(dst + OP_LBO, aw[4], aw[5], aw[6], aw[7]);
@@ -509,15 +477,6 @@ longconv_tz_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 
 }  // namespace tz
 
-#ifdef M2_TZ_TIMING
-extern "C" int m2_debug_tz_cycles(unsigned long long* out, int reset) {
-  unsigned long long z[16] = {0};
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out, tz::g_tz_cycles, sizeof(z));
-  if (reset) cudaMemcpyToSymbol(tz::g_tz_cycles, z, sizeof(z));
-  return 0;
-}
-#endif
 
 int longconv_tz_supported(int batch, int seq_len, m2_dtype act_dtype) {
   return act_dtype == M2_BF16 && seq_len >= 16 && seq_len <= 128 && seq_len % 8 == 0 && batch >= 64;

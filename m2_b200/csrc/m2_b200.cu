@@ -9,3 +9,4 @@
 #include "longconv.cu"
 #include "gemm_tc.cu"
 #include "gemm_simt.cu"
+#include "selftest.cu"

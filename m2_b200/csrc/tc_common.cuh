@@ -10,7 +10,15 @@ namespace tc {
 // Status bits a kernel ORs into m2_dev_status_word when a bounded wait gives up.
 constexpr int ST_TIMEOUT_TMA = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_EPI = 4, ST_TIMEOUT_EMPTY = 8;
 
-constexpr uint32_t WAIT_SPINS = 1u << 22;   // each spin is a try_wait with a hardware time slice
+// Every wait on an mbarrier gives up after this long on the GPU's nanosecond timer (a wait covers one TMA
+// load, one group of MMAs or one tile hand-off, never a whole launch).
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -41,16 +49,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false (and records `why`) if the phase never completes or another
-// role already gave up; the caller then leaves its loop so the CTA can exit cleanly.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int why) {
-  for (uint32_t i = 0; i < WAIT_SPINS; ++i) {
+// Bounded wait: returns false (and records `why` in the device status word) if the phase does not
+// complete within limit_ns, or if another role of the CTA already gave up; the caller then leaves its
+// loop so the CTA can drain, free its tensor memory and exit.  The clock is read every 64 polls.
+__device__ __forceinline__ bool mbar_wait_ns(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int why,
+                                             unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > limit_ns) break;
+    }
   }
   *abort_flag = 1;
   atomicOr(&m2_dev_status_word, why);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int why) {
+  return mbar_wait_ns(bar, parity, abort_flag, why, WAIT_LIMIT_NS);
 }
 
 __device__ __forceinline__ void fence_proxy_async_smem() {

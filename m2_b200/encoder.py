@@ -17,6 +17,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn as nn
 
+from ._tags import attach
 from .glu_mlp import BertGatedLinearUnitMLP
 from .hyena_filter import _autocast_bf16
 from .sequence_mixer import MonarchMixerSequenceMixing
@@ -53,6 +54,8 @@ class M2BertConfig:
     hyena_filter_order: int = 128
     hyena_training_additions: bool = False
     pool_all: bool = False           # pooler: mean over unmasked positions instead of the first token
+    use_cls_token: bool = True
+    sequence_token_planting: bool = False
 
 
 class M2BertEmbeddings(nn.Module):
@@ -112,10 +115,7 @@ class M2BertEmbeddings(nn.Module):
                                     self.LayerNorm.weight, self.LayerNorm.bias, self.LayerNorm.eps,
                                     token_type_ids=token_type_ids, position_ids=position_ids,
                                     bf16_copy=aug, tm_copy=tm, fill_pad=True)
-        y._m2_aug = aug
-        if tm is not None:
-            y._m2_tm = tm
-        return y
+        return attach(y, bf16=aug, tm=tm)
 
     def _layernorm_with_copies(self, e):
         from . import ops
@@ -128,10 +128,7 @@ class M2BertEmbeddings(nn.Module):
         y = ops.add_layernorm_fwd(e.reshape(B * L, D), None, self.LayerNorm.weight, self.LayerNorm.bias,
                                   self.LayerNorm.eps, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=True)
         y = y.view(B, L, D)
-        y._m2_aug = aug
-        if tm is not None:
-            y._m2_tm = tm
-        return y
+        return attach(y, bf16=aug, tm=tm)
 
 
 class M2BertLayer(nn.Module):
@@ -179,24 +176,45 @@ class M2BertEncoder(nn.Module):
 
 
 class M2BertPooler(nn.Module):
-    """dense + tanh on the first token, or (config.pool_all) on the mean of the unmasked positions
-    (reference BertPooler, bert/src/bert_layers.py:816-859; its `sequence_token_planting` variant is not
-    carried over).  State-dict keys `dense.weight`, `dense.bias` as in the reference."""
+    """dense + tanh on the first token, on the mean of the unmasked positions (config.pool_all), or on
+    the "planted" token average (config.sequence_token_planting) -- every branch of the reference's
+    BertPooler (bert/src/bert_layers.py:816-859).  State-dict keys `dense.weight`, `dense.bias`.
+
+    The planting branch follows the reference to the letter: ONE vector -- the sum, over every example
+    and every position 128, 256, ... whose mask is 1, of that position's hidden state -- is added to the
+    first-token row of every example, in place in `hidden_states` as the reference does, and the result is
+    divided by the number of positions summed (over all examples) before the dense layer."""
 
     def __init__(self, config):
         super().__init__()
         self.dense = nn.Linear(config.hidden_size, config.hidden_size)
         self.activation = nn.Tanh()
-        self.pool_all = config.pool_all
+        self.pool_all = getattr(config, "pool_all", False)
+        self.use_cls_token = getattr(config, "use_cls_token", True)
+        self.sequence_token_planting = getattr(config, "sequence_token_planting", False)
 
     def forward(self, hidden_states, pool=True, mask=None):
         if not self.pool_all:
-            first = hidden_states[:, 0] if pool else hidden_states
+            if self.sequence_token_planting:
+                if mask is None:
+                    raise ValueError("sequence_token_planting needs the attention mask")
+                first = hidden_states[:, 0]
+                n_slots = int(hidden_states.shape[1] / 128)
+                if n_slots > 1:
+                    planted = hidden_states[:, 128:128 * n_slots:128]                # positions 128, 256, ...
+                    keep = (mask[:, 128:128 * n_slots:128] == 1)
+                    count = keep.sum()
+                    first += (planted * keep.unsqueeze(-1).to(planted.dtype)).sum(dim=(0, 1))
+                else:
+                    count = torch.zeros((), dtype=torch.long, device=hidden_states.device)
+                first = first / count
+            else:
+                first = hidden_states[:, 0] if pool else hidden_states
             return self.activation(self.dense(first))
         if mask is None:
             raise ValueError("pool_all needs the attention mask")
-        mask = mask.to(hidden_states.dtype)
-        mean = (hidden_states * mask.unsqueeze(-1)).sum(dim=1) / mask.sum(dim=1, keepdim=True)
+        denom = torch.sum(mask, dim=1, keepdim=True)
+        mean = torch.sum(hidden_states * mask.unsqueeze(-1), dim=1) / denom
         return self.activation(self.dense(mean))
 
 

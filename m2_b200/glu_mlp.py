@@ -8,6 +8,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
+from ._tags import attach, forward_only
 from .blockdiag_linear import BlockdiagLinear, _compute_dtype
 
 
@@ -34,13 +35,12 @@ class BertGatedLinearUnitMLP(nn.Module):
         self.dropout = nn.Dropout(config.hidden_dropout_prob)
         self.layernorm = nn.LayerNorm(config.hidden_size, eps=config.layer_norm_eps)
 
+    @forward_only
     def forward(self, hidden_states: torch.Tensor, copies_only: bool = False) -> torch.Tensor:
         """copies_only (used by M2BertEncoder between layers): when the next mixer of this shape
         reads nothing but the bf16 and time-major fp16 copies of the output, skip the float32
         tensor and return the bf16 copy as the hidden state (tagged with the dtype the
         reference's tensor would have, which decides one rounding point in the mixer)."""
-        from .sequence_mixer import _check_forward_only
-        _check_forward_only(self, hidden_states)
         if self.training and self.dropout.p > 0:
             raise RuntimeError("m2_b200: dropout inside the fused MLP is not implemented; use eval()")
         cfg = self.config
@@ -72,11 +72,8 @@ class BertGatedLinearUnitMLP(nn.Module):
                                   fill_pad=aug is not None)
         if skip:
             y = aug[:, :x.shape[-1]].view(x.shape[0], x.shape[1], x.shape[2])
-            y._m2_src_dtype = out_dtype
         else:
             y = y.reshape(x.shape)
-        if aug is not None:
-            y._m2_aug = aug
-        if tm is not None:
-            y._m2_tm = tm
+        if aug is not None or tm is not None:
+            attach(y, bf16=aug, tm=tm, src_dtype=out_dtype)
         return y

@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 
 from . import ops
+from ._tags import forward_only
 
 
 class OptimModule(nn.Module):
@@ -205,14 +206,24 @@ class HyenaFilter(OptimModule):
         k = self.time_filter(L, _autocast_bf16())
         return k[:, -L:].flip(-1).t().unsqueeze(0)
 
+    @forward_only
     def forward(self, x, L, k_fwd=None, k_rev=None, bias=None, *args, **kwargs):
-        """y = long_conv(x) + bias * x for x (B, d_model, L).  The filters are the module's
-        own (k_fwd / k_rev are accepted for signature compatibility and ignored: they are
-        what ``filter`` / ``filter_rev`` return)."""
-        from .sequence_mixer import _check_forward_only
-        _check_forward_only(self, x)
-        raise_if = x.dim() != 3 or x.shape[1] != self.d_model
-        if raise_if:
+        """y = long_conv(x) + bias * x for x (B, d_model, L).  Without k_fwd the filters are the
+        module's own (cached).  Caller-supplied filters are used as the reference uses them
+        (hyena_utils.py:219-234): k_fwd (d_model, L) and, for a bidirectional module, k_rev
+        (d_model, L), merged as pad(k_fwd) + pad(flip(k_rev)); a tuple stands for its first entry."""
+        if x.dim() != 3 or x.shape[1] != self.d_model:
             raise RuntimeError(f"HyenaFilter.forward expects (B, {self.d_model}, L), got {tuple(x.shape)}")
         rounding = x.dtype == torch.bfloat16 or _autocast_bf16()
-        return ops.plain_longconv(x, self, L, rounding, bias)
+        if k_fwd is None:
+            return ops.plain_longconv(x, self, L, rounding, bias)
+        k_fwd = k_fwd[0] if type(k_fwd) is tuple else k_fwd
+        R = ops.filter_row_len(L)
+        k = torch.zeros((self.d_model, R), dtype=torch.float32, device=x.device)
+        k[:, :L] = k_fwd.detach().reshape(self.d_model, -1)[:, :L]
+        if self.bidirectional:
+            if k_rev is None:
+                raise RuntimeError("HyenaFilter.forward: a bidirectional filter given k_fwd needs k_rev too")
+            k_rev = k_rev[0] if type(k_rev) is tuple else k_rev
+            k[:, R - L:] += k_rev.detach().reshape(self.d_model, -1)[:, :L].flip(-1)
+        return ops.plain_longconv(x, self, L, rounding, bias, spec=ops.filter_spectrum(k, L, 0))

@@ -224,8 +224,9 @@ def blockdiag_fwd(x2d, w, bias, in_features, out_features):
     return out
 
 
-def blockdiag_glu_fwd(x2d, wg, inter):
-    """h = gelu(G[:, :inter]) * G[:, inter:], G = x2d @ blockdiag(wg)^T, without writing G."""
+def blockdiag_glu_fwd(x2d, wg, inter, variant=0):
+    """h = gelu(G[:, :inter]) * G[:, inter:], G = x2d @ blockdiag(wg)^T, without writing G.  variant=1 forces
+    the general streaming kernel (bit-identical results; for cross-checks)."""
     _need_cuda(x2d, wg)
     nb, q, p = wg.shape
     if x2d.stride(-1) != 1:
@@ -236,7 +237,7 @@ def blockdiag_glu_fwd(x2d, wg, inter):
     a = _lib.GluArgs()
     a.m, a.d_model, a.inter, a.nblocks, a.dtype = m, d_model, int(inter), nb, _dt(x2d)
     a.x, a.ldx, a.wg = x2d.data_ptr(), max(x2d.stride(0), d_model), wg.data_ptr()
-    a.h, a.ldh = h.data_ptr(), h.stride(0)
+    a.h, a.ldh, a.variant = h.data_ptr(), h.stride(0), int(variant)
     _launch("m2_blockdiag_glu_fwd", x2d, _lib.lib().m2_blockdiag_glu_fwd, C.byref(a))
     return h
 
@@ -301,6 +302,8 @@ def embed_layernorm_fwd(input_ids, word_table, type_table, pos_table, weight, bi
     out = torch.empty((B, L, n), dtype=torch.float32, device=input_ids.device)
     a = _lib.EmbedLayernormArgs()
     a.m, a.n, a.eps, a.seq_len = m, n, float(eps), L
+    a.vocab_rows, a.type_rows = word_table.shape[0], type_table.shape[0]
+    a.pos_rows = pos_table.shape[0] if pos_table is not None else 0
     a.input_ids, a.word_table, a.type_table = keep[0].data_ptr(), keep[3].data_ptr(), keep[4].data_ptr()
     if keep[1] is not None:
         a.token_type_ids = keep[1].data_ptr()
@@ -322,18 +325,24 @@ def embed_layernorm_fwd(input_ids, word_table, type_table, pos_table, weight, bi
     return out
 
 
+DEV_TIMEOUT_TMA, DEV_TIMEOUT_MMA, DEV_TIMEOUT_EPI, DEV_TIMEOUT_EMPTY, DEV_BAD_INDEX = 1, 2, 4, 8, 16
+
+
 def device_status() -> int:
+    """Reads and clears the device status word (synchronises): 0, or an OR of the DEV_* bits."""
     v = C.c_int(0)
     _lib.check(_lib.lib().m2_device_status(C.byref(v)), "m2_device_status")
     return v.value
 
 
-def plain_longconv(x, filt, L, bf16_rounding, bias=None):
-    """HyenaFilter.forward alone: y = conv(x, k) + bias * x for x (B, d_model, L)."""
+def plain_longconv(x, filt, L, bf16_rounding, bias=None, spec=None):
+    """HyenaFilter.forward alone: y = conv(x, k) + bias * x for x (B, d_model, L); `spec` (a kind-0
+    table from filter_spectrum) replaces the module's own filter."""
     _need_cuda(x)
     B, D, Lx = x.shape
     assert Lx == L
-    spec = filt.spectrum(L, bf16_rounding, 0)
+    if spec is None:
+        spec = filt.spectrum(L, bf16_rounding, 0)
     bvec = _f32c(filt.conv_bias(bias))
     out = torch.empty_like(x)
     a = _lib.LongconvArgs()

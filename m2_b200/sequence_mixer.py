@@ -9,6 +9,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from . import ops
+from ._tags import copies_of, forward_only, src_dtype_of
 from .hyena_filter import HyenaFilter, _autocast_bf16
 
 
@@ -47,22 +48,15 @@ def make_augmented(m_rows, d, device):
 
 def augmented_input(u):
     """bf16 copy of u with the bias column appended: reuses the copy a preceding m2_b200
-    LayerNorm left on the tensor (attribute `_m2_aug`), else casts u."""
+    LayerNorm wrote (if u has not been edited since), else casts u."""
     B, L, D = u.shape
-    aug = getattr(u, "_m2_aug", None)
+    rec = copies_of(u)
+    aug = rec.bf16 if rec is not None else None
     if aug is not None and aug.shape == (B * L, D + _PAD) and aug.device == u.device:
         return aug.view(B, L, D + _PAD)
     aug = make_augmented(B * L, D, u.device).view(B, L, D + _PAD)
     aug[..., :D] = u
     return aug
-
-
-def _check_forward_only(module, x):
-    """The kernels implement the forward pass only; refuse to build an autograd graph
-    silently."""
-    if torch.is_grad_enabled() and (x.requires_grad or any(p.requires_grad for p in module.parameters())):
-        raise RuntimeError("m2_b200 modules are forward-only: call them under torch.no_grad() "
-                           "or torch.inference_mode()")
 
 
 class MonarchMixerSequenceMixing(nn.Module):
@@ -122,18 +116,17 @@ class MonarchMixerSequenceMixing(nn.Module):
             xin_t = torch.matmul(w_in, x_aug.transpose(1, 2))                    # (B, 3D, L)
             u_view, yu_bf16 = None, False
             if ures is not None:
-                tm = getattr(ures, "_m2_tm", None)                               # (D, B, L) fp16 from the LayerNorm
+                rec = copies_of(ures)
+                tm = rec.tm if rec is not None else None                         # (D, B, L) fp16 from the LayerNorm
                 if tm is not None and tm.shape == (D, B, L) and tm.device == u.device:
                     u_view = tm.permute(1, 2, 0)                                 # (B, L, D) view, time-contiguous
-                    yu_bf16 = getattr(ures, "_m2_src_dtype", ures.dtype) == torch.bfloat16
+                    yu_bf16 = src_dtype_of(ures) == torch.bfloat16
                 else:
                     u_view = ures.transpose(1, 2).contiguous().transpose(1, 2)
-            y_t = getattr(self, "_y_t", None)
-            if y_t is None or y_t.shape != (B, D + _PAD, L) or y_t.device != u.device:
-                y_t = torch.empty((B, D + _PAD, L), dtype=torch.bfloat16, device=u.device)
-                y_t[:, D] = 1.0
-                y_t[:, D + 1:] = 0.0
-                self._y_t = y_t
+            # allocated per call: inside a CUDA-graph capture the buffer then belongs to the graph's own pool
+            y_t = torch.empty((B, D + _PAD, L), dtype=torch.bfloat16, device=u.device)
+            y_t[:, D] = 1.0
+            y_t[:, D + 1:] = 0.0
             ops.longconv_fwd(xin_t.transpose(1, 2), u_view,
                              self.short_filter.weight, self.short_filter.bias, specs, biases,
                              kind=2, bf16_rounding=True, out=y_t[:, :D].transpose(1, 2), yu_bf16=yu_bf16)
@@ -153,24 +146,23 @@ class MonarchMixerSequenceMixing(nn.Module):
             xin_t = torch.matmul(w_in, x_aug.t())                                # (3D, B*L)
             u_t = None
             if ures is not None:
-                u_t = getattr(ures, "_m2_tm", None)
+                rec = copies_of(ures)
+                u_t = rec.tm if rec is not None else None
                 if u_t is None or u_t.shape != (D, B, L) or u_t.device != u.device:
                     u_t = ops.time_major_f16(ures)
-            buf = getattr(self, "_y_t", None)
-            if buf is None or buf.shape != (D, B * L) or buf.device != u.device:
-                buf = torch.empty((D, B * L), dtype=torch.bfloat16, device=u.device)
-                self._y_t = buf
+            # allocated per call: inside a CUDA-graph capture the buffer then belongs to the graph's own pool
+            buf = torch.empty((D, B * L), dtype=torch.bfloat16, device=u.device)
             ops.longconv_fwd(xin_t.view(3 * D, B, L).permute(1, 2, 0),
                              u_t.permute(1, 2, 0) if u_t is not None else None,
                              self.short_filter.weight, self.short_filter.bias, specs, None,
                              kind=3, bf16_rounding=True, out=buf.view(D, B, L).permute(1, 2, 0),
-                             yu_bf16=ures is not None and getattr(ures, "_m2_src_dtype", ures.dtype) == torch.bfloat16)
+                             yu_bf16=ures is not None and src_dtype_of(ures) == torch.bfloat16)
             # the output is row-major (B*L, D), so the library GEMM's own bias epilogue applies (bias added
             # in the float32 accumulator, one rounding, as F.linear) and K stays 768 instead of 768 + 64
             return torch.addmm(self._aug_out.b, buf.t(), w_out[:, :D].t()).view(B, L, D)
 
+    @forward_only
     def forward(self, u, **kwargs):
-        _check_forward_only(self, u)
         if not u.is_cuda:
             raise RuntimeError("m2_b200.MonarchMixerSequenceMixing needs CUDA tensors; there is no CPU fallback")
         if self.hyena_training_additions:

@@ -141,3 +141,20 @@ CASES = {
     "encoder_small": dict(kind="encoder", seed=41, B=2, L=32, D=64, I=256, layers=2, vocab=512,
                           order=32),
 }
+
+
+# Pooler branches of the reference's BertPooler (first token / masked mean / token planting): stored whole,
+# they are a few hundred numbers.  Generated by make_golden.py into pooler.npz.
+POOLER = dict(seed=51, B=3, L=384, D=32, valid=[384, 130, 300])
+
+
+def pooler_inputs():
+    """hidden states (B, L, D), mask (B, L) with `valid[b]` leading ones, dense weight and bias."""
+    c = POOLER
+    h = randn(c["seed"], "h", (c["B"], c["L"], c["D"]))
+    mask = np.zeros((c["B"], c["L"]), dtype=np.float32)
+    for b, n in enumerate(c["valid"]):
+        mask[b, :n] = 1.0
+    w = randn(c["seed"], "w", (c["D"], c["D"])) * 0.2
+    bias = randn(c["seed"], "b", (c["D"],)) * 0.1
+    return h, mask, w.astype(np.float32), bias.astype(np.float32)

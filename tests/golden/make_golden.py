@@ -184,6 +184,26 @@ def dump_layout(ref, path):
         json.dump(layout, f, indent=1, sort_keys=True)
 
 
+def run_pooler(ref):
+    """The three branches of the reference's BertPooler on the inputs of cases.pooler_inputs()."""
+    _, _, bert_layers, _ = ref
+    h, mask, w, b = C.pooler_inputs()
+    store = {}
+    for name, kw in (("first", dict(pool_all=False, sequence_token_planting=False)),
+                     ("mean", dict(pool_all=True, sequence_token_planting=False)),
+                     ("planting", dict(pool_all=False, sequence_token_planting=True))):
+        conf = types.SimpleNamespace(hidden_size=h.shape[-1], use_cls_token=True, **kw)
+        m = bert_layers.BertPooler(conf).eval()
+        with torch.no_grad():
+            m.dense.weight.copy_(torch.from_numpy(w))
+            m.dense.bias.copy_(torch.from_numpy(b))
+            hs = torch.from_numpy(h).float().clone()
+            out = m(hs, mask=torch.from_numpy(mask))
+        store[name] = out.numpy()
+        store[name + "_row0_after"] = hs[:, 0].numpy()      # the planting branch edits the hidden states in place
+    return store
+
+
 def main():
     if len(sys.argv) < 2:
         sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of HazyResearch/m2>")
@@ -196,6 +216,9 @@ def main():
         store = run_case(name, cfg, ref)
         np.savez_compressed(os.path.join(here, name + ".npz"), **store)
         print(name, {k: v.shape for k, v in store.items()})
+    store = run_pooler(ref)
+    np.savez_compressed(os.path.join(here, "pooler.npz"), **store)
+    print("pooler", {k: v.shape for k, v in store.items()})
 
 
 if __name__ == "__main__":

@@ -247,3 +247,64 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
     assert "workload" in line["config"]
+
+
+def test_pooler_matches_reference_branches():
+    """First token, masked mean and token planting against outputs of the reference's BertPooler
+    (tests/golden/pooler.npz, written by make_golden.py), including the planting branch's in-place
+    edit of the hidden states' first row."""
+    from m2_b200.encoder import M2BertPooler
+    gold = np.load(os.path.join(ROOT, "tests", "golden", "pooler.npz"))
+    h, mask, w, b = CS.pooler_inputs()
+    for name, kw in (("first", dict(pool_all=False, sequence_token_planting=False)),
+                     ("mean", dict(pool_all=True, sequence_token_planting=False)),
+                     ("planting", dict(pool_all=False, sequence_token_planting=True))):
+        cfg = M2BertConfig(hidden_size=h.shape[-1], **kw)
+        p = M2BertPooler(cfg).eval()
+        with torch.no_grad():
+            p.dense.weight.copy_(torch.from_numpy(w))
+            p.dense.bias.copy_(torch.from_numpy(b))
+            hs = torch.from_numpy(h).float().clone()
+            out = p(hs, mask=torch.from_numpy(mask))
+        assert np.allclose(out.numpy(), gold[name], atol=2e-6), name
+        assert np.allclose(hs[:, 0].numpy(), gold[name + "_row0_after"], atol=2e-6), name
+
+
+def test_forward_only_guard_runs_without_grad_and_warns_once():
+    """With autograd on and parameters that require grad -- how the reference's own benchmark calls the
+    modules -- the forward runs under no_grad instead of raising."""
+    import warnings
+    from m2_b200 import _tags
+
+    class Probe(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.ones(2))
+
+        @_tags.forward_only
+        def forward(self, x):
+            assert not torch.is_grad_enabled()
+            return x * self.w
+
+    _tags._warned = False
+    m = Probe()
+    with warnings.catch_warnings(record=True) as rec:
+        warnings.simplefilter("always")
+        y = m(torch.ones(2, requires_grad=True))
+        m(torch.ones(2))
+    assert not y.requires_grad
+    assert len([r for r in rec if "forward-only" in str(r.message)]) == 1
+    # the real modules reach the device check, not a forward-only error, when called with grad enabled
+    mixer = m2_b200.MonarchMixerSequenceMixing(16, l_max=8, bidirectional=True, hyena_emb_dim=3, hyena_filter_order=16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        mixer(torch.zeros(1, 8, 16))
+
+
+def test_copies_record_is_dropped_after_an_in_place_edit():
+    from m2_b200 import _tags
+    t = torch.zeros(2, 3)
+    _tags.attach(t, bf16=torch.ones(2, 3, dtype=torch.bfloat16), src_dtype=torch.float32)
+    assert _tags.copies_of(t) is not None
+    t.add_(1.0)
+    assert _tags.copies_of(t) is None and _tags.src_dtype_of(t) == torch.float32
+    assert _tags.copies_of(torch.zeros(1)) is None

@@ -368,15 +368,10 @@ def test_glu_mlp_tile_edges_bf16(M, D, I):
 #      bit-identical to the two-accumulator kernel it replaces for K <= 192 per block -------------------------
 @pytest.mark.parametrize("M,D,I", [(20000, 768, 3072), (20000, 512, 2048), (33000, 256, 1024), (300, 256, 512)])
 def test_glu_resident_slices_match_streaming_kernel(M, D, I):
-    import os
     x = torch.from_numpy(C.randn(70 + D, "x", (M, D))).to(DEV).bfloat16()
     wg = (torch.from_numpy(C.randn(71 + D, "w", (4, 2 * I // 4, D // 4))).to(DEV) / (D // 4) ** 0.5).bfloat16()
     h = ops.blockdiag_glu_fwd(x, wg, I)
-    os.environ["M2_GLU_DUAL"] = "1"
-    try:
-        h2 = ops.blockdiag_glu_fwd(x, wg, I)
-    finally:
-        del os.environ["M2_GLU_DUAL"]
+    h2 = ops.blockdiag_glu_fwd(x, wg, I, variant=1)
     torch.cuda.synchronize()
     assert torch.equal(h, h2)
     rows = torch.tensor([0, 127, 128, M // 2, M - 1], device=DEV)
