@@ -208,8 +208,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch per GPU")
     args = ap.parse_args()
-    name, w = args.workload, WORKLOADS[args.workload]
+    name, w = args.workload, dict(WORKLOADS[args.workload])
+    if args.batch > 0:
+        w["B"] = args.batch
     if args.impl == "reference":
         run_reference(args, name, w)
         return
