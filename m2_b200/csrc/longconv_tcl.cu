@@ -100,7 +100,7 @@ __host__ __device__ constexpr int mat_off(int row, int k) {
 
 // ---------------------------------------------------------------------------------------
 // Spectrum table (kind 2): [HDR_FLOATS floats: matrices + twiddles] then per channel
-// G[(k1 N2 + k2)][k3] as half2, multiplied by KAPPA.
+// G[(k1 N2 + k2)][k3] as half2, multiplied by KAPPA * 2^e, then one float 2^-e per channel.
 // ---------------------------------------------------------------------------------------
 template <typename G>
 __device__ void write_header(float* spec, int tid, int nt) {
@@ -173,6 +173,29 @@ __device__ void write_header(float* spec, int tid, int nt) {
   }
 }
 
+// The spectrum of a long filter has a large dynamic range (its DC gain grows with the length) and fp16
+// tops out at 65504, so every channel's bins are stored multiplied by a power of two 2^e that brings the
+// largest component just below 1; the convolution kernel multiplies its float32 result by 2^-e (stored
+// per channel after the bins).  Power-of-two factors change no mantissa bit.
+__device__ __forceinline__ float gain_scale(float gmax) {
+  if (!(gmax > 0.f) || !isfinite(gmax)) return 1.f;
+  int e;
+  frexpf(gmax, &e);                      // gmax = m * 2^e, m in [0.5, 1)
+  return ldexpf(1.f, -e);
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? red[threadIdx.x] : 0.f;
+  if (threadIdx.x < 32) {
+    for (int o = 16; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
+    if (threadIdx.x == 0) red[0] = t;
+  }
+  __syncthreads();
+  return red[0];
+}
+
 // One CTA per channel: N-point complex FFT (decimation in frequency) in shared memory of
 // g[n] w^{n/2}, g = the filter with its wrapped half negated; bins gathered in table order.
 template <typename G>
@@ -208,12 +231,23 @@ spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
     }
     __syncthreads();
   }
+  // largest |Re|, |Im| over the stored half of the spectrum decides the channel's scale 2^e (see gain_scale)
+  float gmax = 0.f;
+  for (int idx = tid; idx < N / 2; idx += nt) {
+    const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
+    const int p = (int)(__brev((unsigned)(k1 + 32 * k2 + 32 * N2 * k3)) >> (32 - G::LG));
+    gmax = fmaxf(gmax, fmaxf(fabsf(s[p].x), fabsf(s[p].y)));
+  }
+  __shared__ float red[32];
+  gmax = block_max(gmax, red);
+  const float sc = gain_scale(gmax * G::KAPPA);
+  if (tid == 0) spec[G::HDR_FLOATS + (size_t)D * (N / 2) + c] = 1.0f / sc;
   __half2* Gt = reinterpret_cast<__half2*>(spec + G::HDR_FLOATS) + (size_t)c * (N / 2);
   for (int idx = tid; idx < N / 2; idx += nt) {
     const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
     const int k = k1 + 32 * k2 + 32 * N2 * k3;
     const int p = (int)(__brev((unsigned)k) >> (32 - G::LG));
-    Gt[idx] = __floats2half2_rn(s[p].x * G::KAPPA, s[p].y * G::KAPPA);
+    Gt[idx] = __floats2half2_rn(s[p].x * (G::KAPPA * sc), s[p].y * (G::KAPPA * sc));
   }
 }
 
@@ -238,6 +272,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
   const int c = blockIdx.x >> 1;
   if (c == D) {
     if (q == 0) write_header<G>(spec, tid, nt);
+    cluster.sync();
     cluster.sync();
     cluster.sync();
     return;
@@ -285,22 +320,40 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
   // bin kappa of the M-point transform sits at global position rev_M(kappa): CTA = kappa & 1
   const float2* other = cluster.map_shared_rank(s, q ^ 1);
   __half2* Gt = reinterpret_cast<__half2*>(spec + G::HDR_FLOATS) + (size_t)c * (N / 2);
-  for (int idx = tid; idx < N / 2; idx += nt) {
-    const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
-    const int k = k1 + 32 * k2 + 32 * N2 * k3;
-    const int kap = k & (M - 1);
-    if ((kap & 1) != q) continue;
-    const int pk = (int)(__brev((unsigned)kap) >> (32 - LGM)) - q * Mh;
-    const int pm = (int)(__brev((unsigned)(M - 1 - kap)) >> (32 - LGM)) - (q ^ 1) * Mh;
-    const float2 Zk = s[pk], Zp = other[pm];
-    const float2 E = make_float2(0.5f * (Zk.x + Zp.x), 0.5f * (Zk.y - Zp.y));
-    const float2 O = make_float2(0.5f * (Zk.y + Zp.y), -0.5f * (Zk.x - Zp.x));     // (Zk - conj Zp) / 2i
-    double snd, csd;
-    sincospi(2.0 * (kap + 0.5) / N, &snd, &csd);               // w^{kap + 1/2} = cos - i sin
-    const float cs = (float)csd, sn = (float)snd;
-    const float2 wO = make_float2(O.x * cs + O.y * sn, O.y * cs - O.x * sn);
-    const float sg = (k >= M) ? -1.f : 1.f;
-    Gt[idx] = __floats2half2_rn((E.x + sg * wO.x) * G::KAPPA, (E.y + sg * wO.y) * G::KAPPA);
+  __shared__ float red[32];
+  __shared__ float cta_max;
+  // two passes over this CTA's bins: the first finds the channel's largest component (combined with the
+  // other CTA's through distributed shared memory), the second stores the scaled bins
+  float sc = 1.f;
+  for (int pass = 0; pass < 2; ++pass) {
+    float gmax = 0.f;
+    for (int idx = tid; idx < N / 2; idx += nt) {
+      const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
+      const int k = k1 + 32 * k2 + 32 * N2 * k3;
+      const int kap = k & (M - 1);
+      if ((kap & 1) != q) continue;
+      const int pk = (int)(__brev((unsigned)kap) >> (32 - LGM)) - q * Mh;
+      const int pm = (int)(__brev((unsigned)(M - 1 - kap)) >> (32 - LGM)) - (q ^ 1) * Mh;
+      const float2 Zk = s[pk], Zp = other[pm];
+      const float2 E = make_float2(0.5f * (Zk.x + Zp.x), 0.5f * (Zk.y - Zp.y));
+      const float2 O = make_float2(0.5f * (Zk.y + Zp.y), -0.5f * (Zk.x - Zp.x));     // (Zk - conj Zp) / 2i
+      double snd, csd;
+      sincospi(2.0 * (kap + 0.5) / N, &snd, &csd);               // w^{kap + 1/2} = cos - i sin
+      const float cs = (float)csd, sn = (float)snd;
+      const float2 wO = make_float2(O.x * cs + O.y * sn, O.y * cs - O.x * sn);
+      const float sg = (k >= M) ? -1.f : 1.f;
+      const float gr = E.x + sg * wO.x, gi = E.y + sg * wO.y;
+      if (pass == 0) gmax = fmaxf(gmax, fmaxf(fabsf(gr), fabsf(gi)));
+      else Gt[idx] = __floats2half2_rn(gr * (G::KAPPA * sc), gi * (G::KAPPA * sc));
+    }
+    if (pass == 0) {
+      gmax = block_max(gmax, red);
+      if (tid == 0) cta_max = gmax;
+      cluster.sync();
+      const float om = *cluster.map_shared_rank(&cta_max, q ^ 1);
+      sc = gain_scale(fmaxf(gmax, om) * G::KAPPA);
+      if (tid == 0 && q == 0) spec[G::HDR_FLOATS + (size_t)D * (N / 2) + c] = 1.0f / sc;
+    }
   }
   cluster.sync();
 }
@@ -609,7 +662,8 @@ longconv_tcl_kernel(const Params P) {
       // ---------------- hop 3: conj(Z (G + bias)); rows (k1, k2) keep their place, k = (k3, ri) ----------------
       {
         const uint32_t* Gt = reinterpret_cast<const uint32_t*>(P.spec[f] + G::HDR_FLOATS) + (size_t)ch * (G::N / 2);
-        const float bk = __ldg(P.bias[f] + ch) * G::KAPPA;
+        const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);   // 2^-e of this channel
+        const float bk = __ldg(P.bias[f] + ch) * G::KAPPA / inv_gain;
 #pragma unroll 1
         for (int t = ts; t < G::T3T; t += TS) {
           const int rho = 128 * t + l;
@@ -704,6 +758,7 @@ longconv_tcl_kernel(const Params P) {
       LCL_BARRIER()
 
       // ---------------- epilogue: gate / residual add; 8-byte stores along time ----------------
+      const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);     // undo the table's 2^e
 #pragma unroll 1
       for (int cc = 0; cc < CPT; ++cc) {
         const int pc = (sl % CH) + cc * TPS, pg = (CH >= TPS) ? 0 : sl / CH;
@@ -718,7 +773,7 @@ longconv_tcl_kernel(const Params P) {
               load6(x2row, t0, P.L, x6);
               conv4(T2, x6, c2);
               const float4 y = *reinterpret_cast<const float4*>(Y + t0);
-              const float yv[4] = {y.x, y.y, y.z, y.w};
+              const float yv[4] = {y.x * inv_gain, y.y * inv_gain, y.z * inv_gain, y.w * inv_gain};
               float o[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) o[j] = bf16r(yv[j]) * c2[j];      // (conv + bias term) cast, then the gate
@@ -731,7 +786,7 @@ longconv_tcl_kernel(const Params P) {
             const int t0 = R * (n1_0 + i) + r0;
             if (t0 < P.L) {
               const float4 y = *reinterpret_cast<const float4*>(Y + t0);
-              float yv[4] = {y.x, y.y, y.z, y.w};
+              float yv[4] = {y.x * inv_gain, y.y * inv_gain, y.z * inv_gain, y.w * inv_gain};
               if (P.yu_bf16) {                                 // bf16 layer input: yu is cast to bf16 first
 #pragma unroll
                 for (int j = 0; j < 4; ++j) yv[j] = bf16r(yv[j]);
@@ -802,10 +857,11 @@ int longconv_tcl_supported(int seq_len, m2_dtype act_dtype) {
   return seq_len > 512 && seq_len <= 32768;      // transform length 4096 up to 2048, 16384 up to 8192, else 65536
 }
 
+// header + per channel N/2 half2 bins + per channel one float (2^-e, see gain_scale)
 size_t spectrum_kind2_floats(int D, int L) {
-  if (L <= 2048) return (size_t)lcl::Geo4k::HDR_FLOATS + (size_t)(lcl::Geo4k::N / 2) * D;
-  if (L <= 8192) return (size_t)lcl::Geo16k::HDR_FLOATS + (size_t)(lcl::Geo16k::N / 2) * D;
-  return (size_t)lcl::Geo64k::HDR_FLOATS + (size_t)(lcl::Geo64k::N / 2) * D;
+  if (L <= 2048) return (size_t)lcl::Geo4k::HDR_FLOATS + (size_t)(lcl::Geo4k::N / 2 + 1) * D;
+  if (L <= 8192) return (size_t)lcl::Geo16k::HDR_FLOATS + (size_t)(lcl::Geo16k::N / 2 + 1) * D;
+  return (size_t)lcl::Geo64k::HDR_FLOATS + (size_t)(lcl::Geo64k::N / 2 + 1) * D;
 }
 
 int spectrum_kind2_launch(int D, int L, const float* k, float* spec, cudaStream_t st) {
