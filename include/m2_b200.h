@@ -124,6 +124,33 @@ int    m2_filter_spectrum_bias(int kind, int d_model, int seq_len, const float* 
                                float* spec_out, void* stream);
 
 /* ---------------------------------------------------------------------------------------
+ * Dense linear layer  y[b, t, n] = sum_k x[b, t, k] * w[n, k] + bias[n]  with strided activations.
+ * Replaces nn.Linear `in_linear` / `out_linear` of the sequence mixer together with the layout changes
+ * around them: bert/src/mm/monarch_mixer_sequence_mixer.py:81-82 (definitions), :108-109 (in_linear and the
+ * transpose to (B, 3D, L)), :150-152 (the transpose back and out_linear).
+ *   x   : element (b, t, k) at x[b*x_sb + t*x_st + k*x_sc]; either x_sc == 1 (rows of features) or x_st == 1
+ *         (time-contiguous, e.g. a (B, D, L) or channel-major (D, B*L) tensor).
+ *   out : element (b, t, n) at out[b*out_sb + t*out_st + n*out_sc]; either out_sc == 1 or out_st == 1
+ *         (time-contiguous: (B, N, L), or channel-major (N, B*L) with out_sb == seq_len).
+ *   w   : (out_features, in_features) row-major, dtype of x; bias float32 (out_features) or NULL.
+ * M2_BF16: float32 accumulation, the bias (rounded to bf16, as autocast casts it) added in float32, one
+ * rounding to bf16 -- the arithmetic of F.linear under torch.autocast.  Runs on tcgen05 tensor cores when
+ * bases are 16-byte aligned and strides are multiples of 8 elements (not both x and out time-contiguous);
+ * otherwise, and for M2_F32 (float32 accumulation, no rounding), on CUDA cores.
+ * ------------------------------------------------------------------------------------- */
+typedef struct {
+  int batch, seq_len, in_features, out_features;
+  m2_dtype dtype;
+  const void* x; long long x_sb, x_st, x_sc;
+  const void* w;
+  const float* bias;
+  void* out; long long out_sb, out_st, out_sc;
+  int force_simt;      /* != 0: always the CUDA-core kernel (cross-checks) */
+} m2_linear_args;
+
+int m2_linear_fwd(const m2_linear_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------
  * Fused gated long convolution: everything between in_linear and out_linear.
  * Replaces bert/src/mm/monarch_mixer_sequence_mixer.py:109-149 -- the layout change,
  * the depthwise 3-tap short_filter (:112), x1/x2/v split (:114), v*x1 (:116), the FFT

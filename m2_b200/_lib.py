@@ -69,6 +69,17 @@ class GluArgs(C.Structure):
     ]
 
 
+class LinearArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int), ("seq_len", C.c_int), ("in_features", C.c_int), ("out_features", C.c_int),
+        ("dtype", C.c_int),
+        ("x", C.c_void_p), ("x_sb", C.c_longlong), ("x_st", C.c_longlong), ("x_sc", C.c_longlong),
+        ("w", C.c_void_p), ("bias", C.c_void_p),
+        ("out", C.c_void_p), ("out_sb", C.c_longlong), ("out_st", C.c_longlong), ("out_sc", C.c_longlong),
+        ("force_simt", C.c_int),
+    ]
+
+
 class AddLayernormArgs(C.Structure):
     _fields_ = [
         ("m", C.c_int), ("n", C.c_int), ("in_dtype", C.c_int), ("out_dtype", C.c_int),
@@ -108,6 +119,7 @@ SYMBOLS = {
     "m2_filter_spectrum": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]),
     "m2_longconv_kind_batch": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int]),
     "m2_filter_spectrum_bias": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "m2_linear_fwd": (C.c_int, [C.POINTER(LinearArgs), C.c_void_p]),
     "m2_longconv_fwd": (C.c_int, [C.POINTER(LongconvArgs), C.c_void_p]),
     "m2_time_major_f16": (C.c_int, [C.POINTER(TimeMajorArgs), C.c_void_p]),
     "m2_blockdiag_fwd": (C.c_int, [C.POINTER(BlockdiagArgs), C.c_void_p]),

@@ -8,5 +8,6 @@
 #include "longconv_tz.cu"
 #include "longconv.cu"
 #include "gemm_tc.cu"
+#include "linear_tc.cu"
 #include "gemm_simt.cu"
 #include "selftest.cu"

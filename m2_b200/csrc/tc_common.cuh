@@ -138,6 +138,66 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- CTA pairs (cta_group::2): cluster helpers, loads that signal the leader's barrier, pair-wide MMA ----------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync() {       // every thread of every CTA of the cluster
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tile loads into THIS CTA's shared memory whose bytes are counted on a barrier given by its shared::cluster
+// address (the pair leader's).  No multicast: each CTA fetches its own tiles.
+__device__ __forceinline__ void tma_load_2d_2sm(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_2sm(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+// tensor memory of both CTAs of a pair: the same warp of each CTA executes these
+__device__ __forceinline__ void tmem_alloc2(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B over the pair: M up to 256 (128 rows per CTA), each CTA's shared memory
+// holds its rows of A and its half of B's rows at the offsets the descriptors name.  ONE thread of the leader.
+__device__ __forceinline__ void mma_ss2(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// the barrier at this shared-memory offset in every CTA of `cta_mask` gets one arrival once all MMAs issued so
+// far by this thread have completed
+__device__ __forceinline__ void mma_commit2_mc(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask) : "memory");
+}
+
 // ---- descriptors -----------------------------------------------------------------------
 // Shared-memory matrix descriptor, K-major operand stored as rows of 128 bytes with the
 // 128-byte swizzle (what a TMA tile load with a 64 x bf16 inner box writes): 8-row groups
@@ -149,6 +209,18 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
   d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset between 8-row groups
   d |= (uint64_t)1 << 46;                 // descriptor version
   d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+// 128-byte-swizzled operand with explicit offsets.  MN-major use (the contiguous direction of shared memory is
+// M or N, K runs across 128-byte rows -- what a TMA box of 64 contiguous elements x K rows writes): `lbo` = byte
+// distance between consecutive 64-element chunks along M/N, `sbo` = byte distance between groups of 8 K rows.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
   return d;
 }
 // Un-swizzled K-major operand built from 8x8 core matrices (8 rows of 16 bytes, 128 bytes
@@ -167,6 +239,11 @@ __device__ __forceinline__ uint64_t smem_desc_k_nosw(uint32_t saddr, uint32_t lb
 __host__ __device__ constexpr uint32_t make_idesc(int M, int N, int ab_format) {
   return (1u << 4) | ((uint32_t)ab_format << 7) | ((uint32_t)ab_format << 10) |
          ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// The same with each operand's major-ness: 0 = K-major, 1 = MN-major (bits 15 and 16).
+__host__ __device__ constexpr uint32_t make_idesc_major(int M, int N, int ab_format, int a_mn_major, int b_mn_major) {
+  return make_idesc(M, N, ab_format) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16);
 }
 
 }  // namespace tc

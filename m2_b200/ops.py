@@ -204,6 +204,32 @@ def longconv_fwd(xin, u, short_w, short_b, specs, biases, *, kind, bf16_rounding
     return out
 
 
+def linear_fwd(x, w, bias, out=None, *, force_simt=False):
+    """nn.Linear on strided activations: y[b, t, n] = sum_k x[b, t, k] w[n, k] + bias[n].
+
+    x (B, L, K) and out (B, L, N) are torch VIEWS with any strides that keep either the feature axis or the
+    time axis contiguous (a permuted (B, K, L) or channel-major (K, B, L) buffer is passed as its (B, L, K)
+    view); w (N, K) contiguous, dtype of x; bias float32-convertible (N) or None.  Returns `out` (allocated
+    row-major when not given)."""
+    _need_cuda(x, w)
+    B, L, K = x.shape
+    N = w.shape[0]
+    assert w.shape == (N, K) and w.is_contiguous() and w.dtype == x.dtype
+    if out is None:
+        out = torch.empty((B, L, N), dtype=x.dtype, device=x.device)
+    assert out.shape == (B, L, N) and out.dtype == x.dtype
+    b = _f32c(bias) if bias is not None else None
+    a = _lib.LinearArgs()
+    a.batch, a.seq_len, a.in_features, a.out_features, a.dtype = B, L, K, N, _dt(x)
+    a.x, (a.x_sb, a.x_st, a.x_sc) = x.data_ptr(), x.stride()
+    a.w = w.data_ptr()
+    a.bias = b.data_ptr() if b is not None else None
+    a.out, (a.out_sb, a.out_st, a.out_sc) = out.data_ptr(), out.stride()
+    a.force_simt = int(bool(force_simt))
+    _launch("m2_linear_fwd", x, _lib.lib().m2_linear_fwd, C.byref(a))
+    return out
+
+
 def blockdiag_fwd(x2d, w, bias, in_features, out_features):
     """x2d (m, in_features) @ blockdiag(w)^T (+ bias) -> (m, out_features), dtype of x2d."""
     _need_cuda(x2d, w)
