@@ -39,7 +39,10 @@ constexpr int EPI_WARPS = 16, EPI_WARP0 = 4, THREADS = 32 * (EPI_WARP0 + EPI_WAR
 constexpr int CW = ACC_COLS / (EPI_WARPS / 4);   // accumulator columns per epilogue warp: 64
 constexpr int OFF_BAR = NST * STAGE;
 constexpr int NBARS = 2 * NST + 4;
-constexpr int SMEM = OFF_BAR + NBARS * 8 + 16 + 1024;
+constexpr int OFF_BIAS = OFF_BAR + 256;    // float32 copy of the (bf16-rounded) column bias, read by every epilogue thread
+constexpr int BIAS_MAX = 6144;
+constexpr int SMEM = OFF_BIAS + BIAS_MAX * 4 + 1024;
+static_assert(NBARS * 8 + 16 <= 256, "barrier block");
 static_assert(SMEM <= 227 * 1024, "shared memory budget");
 
 enum Mode { ROWS = 0, CHANNELS = 1, TIMEIN = 2 };
@@ -88,6 +91,10 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     tc::tmem_alloc2(tmem_slot, 512);
     tc::tmem_relinquish2();
   }
+  float* sbias = reinterpret_cast<float*>(smem + OFF_BIAS);
+  const bool bias_smem = MODE != CHANNELS && P.bias != nullptr && P.n_rows <= BIAS_MAX;
+  if (bias_smem)
+    for (int i = threadIdx.x; i < ((P.n_rows + 15) & ~15); i += THREADS) sbias[i] = i < P.n_rows ? bf16r(__ldg(P.bias + i)) : 0.f;
   tc::tc_fence_before();
   __syncthreads();
   tc::cluster_sync();                       // the peer's barriers and tensor memory exist before anything touches them
@@ -230,14 +237,25 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (!live || n0 >= P.n_rows) continue;
           const bool fullc = n0 + 16 <= P.n_rows;
           uint32_t packed[8];
+          if (bias_smem) {
+            // the staged bias is padded with zeros to a multiple of 16 entries: whole-chunk vector reads
+            const float4* bp = reinterpret_cast<const float4*>(sbias + n0);
 #pragma unroll
-          for (int j = 0; j < 16; j += 2) {
-            float v0 = __uint_as_float(acc_r[ch][j]), v1 = __uint_as_float(acc_r[ch][j + 1]);
-            if (P.bias) {
-              if (fullc || n0 + j < P.n_rows) v0 += bf16r(__ldg(P.bias + n0 + j));
-              if (fullc || n0 + j + 1 < P.n_rows) v1 += bf16r(__ldg(P.bias + n0 + j + 1));
+            for (int q = 0; q < 4; ++q) {
+              const float4 bq = bp[q];
+              packed[2 * q] = pack_bf16(__uint_as_float(acc_r[ch][4 * q]) + bq.x, __uint_as_float(acc_r[ch][4 * q + 1]) + bq.y);
+              packed[2 * q + 1] = pack_bf16(__uint_as_float(acc_r[ch][4 * q + 2]) + bq.z, __uint_as_float(acc_r[ch][4 * q + 3]) + bq.w);
             }
-            packed[j >> 1] = pack_bf16(v0, v1);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; j += 2) {
+              float v0 = __uint_as_float(acc_r[ch][j]), v1 = __uint_as_float(acc_r[ch][j + 1]);
+              if (P.bias) {
+                if (fullc || n0 + j < P.n_rows) v0 += bf16r(__ldg(P.bias + n0 + j));
+                if (fullc || n0 + j + 1 < P.n_rows) v1 += bf16r(__ldg(P.bias + n0 + j + 1));
+              }
+              packed[j >> 1] = pack_bf16(v0, v1);
+            }
           }
           if (P.vec && fullc) {
             stg256(orow + n0, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);

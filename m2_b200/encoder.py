@@ -101,10 +101,9 @@ class M2BertEmbeddings(nn.Module):
 
     def _fused_embeddings(self, input_ids, token_type_ids, position_ids):
         from . import ops
-        from .sequence_mixer import _PAD
         B, L = input_ids.shape
         D = self.word_embeddings.weight.shape[1]
-        aug = torch.empty((B * L, D + _PAD), dtype=torch.bfloat16, device=input_ids.device)
+        aug = torch.empty((B * L, D), dtype=torch.bfloat16, device=input_ids.device)
         tm = None
         if L % 8 == 0 and ops.longconv_kind_batch(B, L, torch.bfloat16, D) in (2, 3):
             tm = torch.empty((D, B, L), dtype=torch.float16, device=input_ids.device)
@@ -114,19 +113,18 @@ class M2BertEmbeddings(nn.Module):
         y = ops.embed_layernorm_fwd(input_ids, self.word_embeddings.weight, self.token_type_embeddings.weight, pos,
                                     self.LayerNorm.weight, self.LayerNorm.bias, self.LayerNorm.eps,
                                     token_type_ids=token_type_ids, position_ids=position_ids,
-                                    bf16_copy=aug, tm_copy=tm, fill_pad=True)
+                                    bf16_copy=aug, tm_copy=tm, fill_pad=False)
         return attach(y, bf16=aug, tm=tm)
 
     def _layernorm_with_copies(self, e):
         from . import ops
-        from .sequence_mixer import _PAD
         B, L, D = e.shape
-        aug = torch.empty((B * L, D + _PAD), dtype=torch.bfloat16, device=e.device)
+        aug = torch.empty((B * L, D), dtype=torch.bfloat16, device=e.device)
         tm = None
         if L % 8 == 0 and ops.longconv_kind_batch(B, L, torch.bfloat16, D) in (2, 3):
             tm = torch.empty((D, B, L), dtype=torch.float16, device=e.device)
         y = ops.add_layernorm_fwd(e.reshape(B * L, D), None, self.LayerNorm.weight, self.LayerNorm.bias,
-                                  self.LayerNorm.eps, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=True)
+                                  self.LayerNorm.eps, torch.float32, bf16_copy=aug, tm_copy=tm, fill_pad=False)
         y = y.view(B, L, D)
         return attach(y, bf16=aug, tm=tm)
 

@@ -57,9 +57,8 @@ class BertGatedLinearUnitMLP(nn.Module):
         aug = None
         if dt == torch.bfloat16 and x.dim() == 3 and x.shape[-1] % 256 == 0 and x.shape[-1] <= 2048:
             # the next layer's in_linear reads this output cast to bf16: write that copy here
-            # (with the bias column its GEMM uses) instead of leaving it to a separate cast pass
-            from .sequence_mixer import _PAD
-            aug = torch.empty((x2.shape[0], x.shape[-1] + _PAD), dtype=torch.bfloat16, device=x.device)
+            # instead of leaving it to a separate cast pass
+            aug = torch.empty((x2.shape[0], x.shape[-1]), dtype=torch.bfloat16, device=x.device)
         tm = None
         if (aug is not None and x.shape[1] % 8 == 0
                 and ops.longconv_kind_batch(x.shape[0], x.shape[1], torch.bfloat16, x.shape[2]) in (2, 3)):
@@ -69,7 +68,7 @@ class BertGatedLinearUnitMLP(nn.Module):
         skip = copies_only and tm is not None
         y = ops.add_layernorm_fwd(o, x2, self.layernorm.weight, self.layernorm.bias,
                                   self.layernorm.eps, None if skip else out_dtype, bf16_copy=aug, tm_copy=tm,
-                                  fill_pad=aug is not None)
+                                  fill_pad=False)
         if skip:
             y = aug[:, :x.shape[-1]].view(x.shape[0], x.shape[1], x.shape[2])
         else:

@@ -297,7 +297,7 @@ def add_layernorm_fwd(a2d, b2d, weight, bias, eps, out_dtype, bf16_copy=None, tm
     if bf16_copy is not None:
         assert bf16_copy.dtype == torch.bfloat16 and bf16_copy.stride(-1) == 1 and bf16_copy.shape[0] == m
         a.out_bf16, a.ld_bf16 = bf16_copy.data_ptr(), bf16_copy.stride(0)
-        if fill_pad:     # columns n.. of the copy become [1, 0, 0, ...] (see sequence_mixer.make_augmented)
+        if fill_pad:     # columns n.. of the copy become [1, 0, 0, ...] (a constant-one input column for a following GEMM)
             a.bf16_pad_cols = bf16_copy.shape[1] - n
     if tm_copy is not None:
         assert tm_copy.dtype == torch.float16 and tm_copy.dim() == 3 and tm_copy.stride(2) == 1

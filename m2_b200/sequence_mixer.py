@@ -6,57 +6,41 @@ from __future__ import annotations
 
 import torch
 import torch.nn as nn
-import torch.nn.functional as F
 
 from . import ops
 from ._tags import copies_of, forward_only, src_dtype_of
 from .hyena_filter import HyenaFilter, _autocast_bf16
 
 
-_PAD = 64   # extra contraction columns that carry the bias through the GEMM
-
-
-class _AugmentedLinear:
-    """bf16 copy of a Linear's weight with the bias as one more input column, refreshed when
-    the parameters change.  Feeding an input whose extra column is 1 makes the GEMM add the
-    (bf16-rounded, as under autocast) bias inside its float32 accumulator, so the result is
-    rounded to bf16 exactly once -- like F.linear -- whatever layout the GEMM writes."""
+class _Bf16Linear:
+    """bf16 copy of a Linear's weight (what autocast would cast per call), refreshed when the parameter changes;
+    the bias stays float32 -- the GEMM kernel rounds it to bf16 itself, as autocast's cast does."""
 
     def __init__(self):
-        self.key, self.w, self.b = None, None, None
+        self.key, self.w = None, None
 
     def get(self, lin):
-        key = (lin.weight.data_ptr(), lin.weight._version, lin.bias._version, lin.weight.device)
+        key = (lin.weight.data_ptr(), lin.weight._version, lin.weight.device)
         if key != self.key:
-            out_f, in_f = lin.weight.shape
-            w = torch.zeros((out_f, in_f + _PAD), dtype=torch.bfloat16, device=lin.weight.device)
-            w[:, :in_f] = lin.weight.detach()
-            w[:, in_f] = lin.bias.detach()
-            self.key, self.w = key, w
-            self.b = w[:, in_f].contiguous()          # the bf16-rounded bias on its own, for addmm
+            self.key, self.w = key, lin.weight.detach().to(torch.bfloat16).contiguous()
         return self.w
 
 
-def make_augmented(m_rows, d, device):
-    """(m_rows, d + _PAD) bf16 buffer whose extra columns are [1, 0, 0, ...]; the first d
-    columns are left for the caller to fill."""
-    buf = torch.empty((m_rows, d + _PAD), dtype=torch.bfloat16, device=device)
-    buf[:, d] = 1.0
-    buf[:, d + 1:] = 0.0
-    return buf
-
-
-def augmented_input(u):
-    """bf16 copy of u with the bias column appended: reuses the copy a preceding m2_b200
-    LayerNorm wrote (if u has not been edited since), else casts u."""
+def bf16_input(u):
+    """(B, L, D) bf16 tensor in_linear reads: the copy a preceding m2_b200 LayerNorm wrote (if u has not
+    been edited since), else u cast to bf16."""
     B, L, D = u.shape
     rec = copies_of(u)
-    aug = rec.bf16 if rec is not None else None
-    if aug is not None and aug.shape == (B * L, D + _PAD) and aug.device == u.device:
-        return aug.view(B, L, D + _PAD)
-    aug = make_augmented(B * L, D, u.device).view(B, L, D + _PAD)
-    aug[..., :D] = u
-    return aug
+    c = rec.bf16 if rec is not None else None
+    if c is not None and c.shape == (B * L, D) and c.device == u.device:
+        return c.view(B, L, D)
+    if u.dtype == torch.bfloat16 and u.stride(-1) == 1:
+        return u
+    return u.to(torch.bfloat16)
+
+
+def _round_up(n, m):
+    return (n + m - 1) // m * m
 
 
 class MonarchMixerSequenceMixing(nn.Module):
@@ -103,63 +87,56 @@ class MonarchMixerSequenceMixing(nn.Module):
         width = d_model * self.NUM_PROJECTIONS
         self.short_filter = nn.Conv1d(width, width, kernel_size=3, groups=width, padding=2)
 
+    def _weights(self):
+        if not hasattr(self, "_w_in"):
+            self._w_in, self._w_out = _Bf16Linear(), _Bf16Linear()
+        return self._w_in.get(self.in_linear), self._w_out.get(self.out_linear)
+
     def _forward_long_rows(self, u, ures, specs, biases):
-        """bf16 path for long sequences: the convolution kernel works on time-contiguous
-        rows, so in_linear writes (B, 3D, L) and out_linear reads (B, D, L) -- both as
-        library GEMMs on transposed operands, no transposed copy of an activation."""
+        """bf16 path for long sequences: the convolution kernel works on time-contiguous rows, so in_linear
+        writes (B, 3D, L) and out_linear reads (B, D, L) -- both through the operand arrangements of
+        m2_linear_fwd, no transposed copy of an activation.  Rows are padded to a multiple of 16 steps so
+        that every row start is 32-byte aligned."""
         B, L, D = u.shape
-        if not hasattr(self, "_aug_in"):
-            self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
-        w_in, w_out = self._aug_in.get(self.in_linear), self._aug_out.get(self.out_linear)
-        x_aug = augmented_input(u)
-        with torch.autocast("cuda", enabled=False):
-            xin_t = torch.matmul(w_in, x_aug.transpose(1, 2))                    # (B, 3D, L)
-            u_view, yu_bf16 = None, False
-            if ures is not None:
-                rec = copies_of(ures)
-                tm = rec.tm if rec is not None else None                         # (D, B, L) fp16 from the LayerNorm
-                if tm is not None and tm.shape == (D, B, L) and tm.device == u.device:
-                    u_view = tm.permute(1, 2, 0)                                 # (B, L, D) view, time-contiguous
-                    yu_bf16 = src_dtype_of(ures) == torch.bfloat16
-                else:
-                    u_view = ures.transpose(1, 2).contiguous().transpose(1, 2)
-            # allocated per call: inside a CUDA-graph capture the buffer then belongs to the graph's own pool
-            y_t = torch.empty((B, D + _PAD, L), dtype=torch.bfloat16, device=u.device)
-            y_t[:, D] = 1.0
-            y_t[:, D + 1:] = 0.0
-            ops.longconv_fwd(xin_t.transpose(1, 2), u_view,
-                             self.short_filter.weight, self.short_filter.bias, specs, biases,
-                             kind=2, bf16_rounding=True, out=y_t[:, :D].transpose(1, 2), yu_bf16=yu_bf16)
-            return torch.matmul(y_t.transpose(1, 2), w_out.t())                  # (B, L, D)
+        w_in, w_out = self._weights()
+        Lp = _round_up(L, 16)
+        # allocated per call: inside a CUDA-graph capture the buffers then belong to the graph's own pool
+        xin_t = torch.empty((B, 3 * D, Lp), dtype=torch.bfloat16, device=u.device)[:, :, :L]
+        ops.linear_fwd(bf16_input(u), w_in, self.in_linear.bias, out=xin_t.permute(0, 2, 1))
+        u_view, yu_bf16 = None, False
+        if ures is not None:
+            rec = copies_of(ures)
+            tm = rec.tm if rec is not None else None                         # (D, B, L) fp16 from the LayerNorm
+            if tm is not None and tm.shape == (D, B, L) and tm.device == u.device:
+                u_view = tm.permute(1, 2, 0)                                 # (B, L, D) view, time-contiguous
+                yu_bf16 = src_dtype_of(ures) == torch.bfloat16
+            else:
+                u_view = ures.transpose(1, 2).contiguous().transpose(1, 2)
+        y_t = torch.empty((B, D, Lp), dtype=torch.bfloat16, device=u.device)[:, :, :L]
+        ops.longconv_fwd(xin_t.permute(0, 2, 1), u_view, self.short_filter.weight, self.short_filter.bias, specs,
+                         biases, kind=2, bf16_rounding=True, out=y_t.permute(0, 2, 1), yu_bf16=yu_bf16)
+        return ops.linear_fwd(y_t.permute(0, 2, 1), w_out, self.out_linear.bias)                      # (B, L, D)
 
     def _forward_toeplitz(self, u, ures, specs):
-        """bf16 path for short sequences and large batches: the convolution kernel runs one
-        Toeplitz GEMM per channel with the batch as its M dimension, on channel-major
-        time-contiguous tensors -- in_linear writes (3D, B*L) and out_linear reads (D, B*L),
-        both single library GEMMs on transposed operands."""
+        """bf16 path for short sequences and large batches: the convolution kernel runs one Toeplitz GEMM
+        per channel with the batch as its M dimension, on channel-major time-contiguous tensors -- in_linear
+        writes (3D, B*L) and out_linear reads (D, B*L), each one launch of m2_linear_fwd."""
         B, L, D = u.shape
-        if not hasattr(self, "_aug_in"):
-            self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
-        w_in, w_out = self._aug_in.get(self.in_linear), self._aug_out.get(self.out_linear)
-        x_aug = augmented_input(u).reshape(B * L, D + _PAD)
-        with torch.autocast("cuda", enabled=False):
-            xin_t = torch.matmul(w_in, x_aug.t())                                # (3D, B*L)
-            u_t = None
-            if ures is not None:
-                rec = copies_of(ures)
-                u_t = rec.tm if rec is not None else None
-                if u_t is None or u_t.shape != (D, B, L) or u_t.device != u.device:
-                    u_t = ops.time_major_f16(ures)
-            # allocated per call: inside a CUDA-graph capture the buffer then belongs to the graph's own pool
-            buf = torch.empty((D, B * L), dtype=torch.bfloat16, device=u.device)
-            ops.longconv_fwd(xin_t.view(3 * D, B, L).permute(1, 2, 0),
-                             u_t.permute(1, 2, 0) if u_t is not None else None,
-                             self.short_filter.weight, self.short_filter.bias, specs, None,
-                             kind=3, bf16_rounding=True, out=buf.view(D, B, L).permute(1, 2, 0),
-                             yu_bf16=ures is not None and src_dtype_of(ures) == torch.bfloat16)
-            # the output is row-major (B*L, D), so the library GEMM's own bias epilogue applies (bias added
-            # in the float32 accumulator, one rounding, as F.linear) and K stays 768 instead of 768 + 64
-            return torch.addmm(self._aug_out.b, buf.t(), w_out[:, :D].t()).view(B, L, D)
+        w_in, w_out = self._weights()
+        xin_t = torch.empty((3 * D, B, L), dtype=torch.bfloat16, device=u.device)
+        ops.linear_fwd(bf16_input(u), w_in, self.in_linear.bias, out=xin_t.permute(1, 2, 0))
+        u_t = None
+        if ures is not None:
+            rec = copies_of(ures)
+            u_t = rec.tm if rec is not None else None
+            if u_t is None or u_t.shape != (D, B, L) or u_t.device != u.device:
+                u_t = ops.time_major_f16(ures)
+        buf = torch.empty((D, B, L), dtype=torch.bfloat16, device=u.device)
+        ops.longconv_fwd(xin_t.permute(1, 2, 0), u_t.permute(1, 2, 0) if u_t is not None else None,
+                         self.short_filter.weight, self.short_filter.bias, specs, None,
+                         kind=3, bf16_rounding=True, out=buf.permute(1, 2, 0),
+                         yu_bf16=ures is not None and src_dtype_of(ures) == torch.bfloat16)
+        return ops.linear_fwd(buf.permute(1, 2, 0), w_out, self.out_linear.bias)                     # (B, L, D)
 
     @forward_only
     def forward(self, u, **kwargs):
@@ -189,15 +166,11 @@ class MonarchMixerSequenceMixing(nn.Module):
         if kind == 2:
             return self._forward_long_rows(u, ures, specs, biases), None
         if bf16:
-            # in_linear on the bf16 input with the bias carried as one more input column: the
-            # same single rounding as F.linear under autocast, without per-call weight casts
-            if not hasattr(self, "_aug_in"):
-                self._aug_in, self._aug_out = _AugmentedLinear(), _AugmentedLinear()
-            with torch.autocast("cuda", enabled=False):
-                xin = torch.matmul(augmented_input(u), self._aug_in.get(self.in_linear).t())
+            w_in, w_out = self._weights()
+            xin = ops.linear_fwd(bf16_input(u), w_in, self.in_linear.bias)
         else:
-            xin = self.in_linear(u)
+            w_in, w_out = self.in_linear.weight.detach(), self.out_linear.weight.detach()
+            xin = ops.linear_fwd(u, w_in, self.in_linear.bias)
         y = ops.longconv_fwd(xin, ures, self.short_filter.weight, self.short_filter.bias, specs, biases,
                              kind=kind, bf16_rounding=bf16)
-        y = self.out_linear(y)
-        return y, None
+        return ops.linear_fwd(y, w_out, self.out_linear.bias), None
