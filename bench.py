@@ -2,18 +2,27 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-A step is one forward of the 12-layer M2-BERT-80M-shaped encoder (embeddings + 12 x
-[sequence mixer, GLU MLP]) under torch.autocast(bfloat16) on one synthetic batch; each rank
-owns its own batch (weak scaling by batch, no collective on the data path).  Prints one
-JSON line (rank 0).  Keys:
+A step is one forward of the M2-BERT-shaped encoder (embeddings + layers x [sequence mixer, GLU MLP]) under
+torch.autocast(bfloat16) on one synthetic batch.  Rank 0 prints ONE JSON line.
+
+The headline (top-level keys) is the 12-layer 80M encoder at L = 128 with 256 sequences per GPU (weak scaling by
+batch, no collective on the data path).  Without --workload the same run also measures, under `workloads`, the
+other configurations at their stated GLOBAL batch sizes split over the ranks (strong scaling): 80M at L = 8192
+(global batch 32) and L = 32768 (8), the large shape at L = 128 (512) and L = 2048 (64), and -- under
+`channel_shard` -- the 32K mixer's un-mixed middle sharded by d_model channel (each rank computes its channels
+of the full batch of 8; an NCCL all-gather outside the timed region checks the reassembled tensor).
+
+Keys per measurement:
   value        sequences/s over all ranks, inputs resident in HBM
-  e2e          the same through the public API with pinned host token ids copied to the
-               device and the [CLS] rows copied back inside the timed region
-  roofline     fused long-convolution kernel: algorithmic bytes / mean launch time (CUDA
-               events on the launching stream, during the timed steps) / measured HBM peak
-  cpu_baseline the stock-PyTorch-op restatement of the same forward (what the reference
-               runs on a CPU) timed on this box's host cores on a bounded sample
-`--impl reference` times that CPU path alone, on the same config and metric.
+  e2e          the same through the public API with pinned host token ids copied to the device and the [CLS]
+               rows (what a pooled-embedding caller reads) copied back inside the timed region
+  roofline     fused long-convolution kernel: algorithmic bytes / mean launch time (CUDA events on the launching
+               stream, in a separate eager pass) / measured HBM peak
+  kernel_ms_per_step   device time of every launch of this library per step, by entry point
+  cold_first_forward_ms  first forward after construction: filter MLPs and spectrum tables are generated
+  cpu_baseline the stock-PyTorch-op restatement of the same forward (what the reference runs on a CPU) timed on
+               this box's host cores on a bounded sample (N = 1, rank 0, headline only)
+`--impl reference` times that CPU path alone, on the headline's config and metric.
 """
 from __future__ import annotations
 
@@ -34,12 +43,19 @@ import numpy as np
 import torch
 
 WORKLOADS = {
-    # name: (layers, d_model, inter, L, batch per GPU)
-    "m2bert80m-L128": dict(layers=12, D=768, I=3072, L=128, B=256),
-    "m2bert80m-L8192": dict(layers=12, D=768, I=3072, L=8192, B=4),
-    "m2bert80m-L32768": dict(layers=12, D=768, I=3072, L=32768, B=1),
-    "m2bert-large-L128": dict(layers=24, D=1536, I=6144, L=128, B=64),
-    "m2bert-large-L2048": dict(layers=24, D=1536, I=6144, L=2048, B=8),
+    # name: layers, d_model, intermediate, L and either a batch per GPU (weak scaling) or a global batch split
+    # over the ranks (strong scaling) -- the batch sizes of the benchmark configurations
+    "m2bert80m-L128": dict(layers=12, D=768, I=3072, L=128, per_gpu=256),
+    "m2bert80m-L8192": dict(layers=12, D=768, I=3072, L=8192, global_batch=32),
+    "m2bert80m-L32768": dict(layers=12, D=768, I=3072, L=32768, global_batch=8),
+    "m2bert-large-L128": dict(layers=24, D=1536, I=6144, L=128, global_batch=512),
+    "m2bert-large-L2048": dict(layers=24, D=1536, I=6144, L=2048, global_batch=64),
+}
+HEADLINE = "m2bert80m-L128"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the long-convolution kernel, from the ncu captures
+# summarised under profiles/ (file named beside each value); None where no capture of the current kernel exists
+TRAFFIC = {
+    "m2bert80m-L128": (247.2e6, "profiles/longconv_tz_m2bert80m-L128.md"),
 }
 VOCAB = 30528
 METRIC = "M2-BERT-80M fwd sequences/sec"
@@ -163,22 +179,33 @@ def time_cpu(w, sample_b, reps):
     return sample_b / dt, dt
 
 
-def config_of(name, w, n, graph=True):
+def batch_per_gpu(w, world):
+    if "per_gpu" in w:
+        return w["per_gpu"], "weak"
+    g = w["global_batch"]
+    if g % world:
+        raise SystemExit(f"global batch {g} does not split over {world} ranks")
+    return g // world, "strong"
+
+
+def config_of(name, w, B, n, scaling, graph=True):
     return {"workload": f"{name}: {w['layers']}-layer M2-BERT encoder fwd (embeddings + mixer + BlockdiagLinear GLU MLP), "
-                        f"d_model {w['D']}, L={w['L']}, batch {w['B']} per GPU, token ids uniform in [0,{VOCAB}), "
+                        f"d_model {w['D']}, L={w['L']}, batch {B} per GPU, token ids uniform in [0,{VOCAB}), "
                         "random-init weights, bf16 autocast",
-            "batch_per_gpu": w["B"], "global_batch": w["B"] * n, "seq_len": w["L"],
+            "batch_per_gpu": B, "global_batch": B * n, "seq_len": w["L"], "scaling": scaling,
             "parallelism": f"batch-sharded x{n}, no data-path collective",
             "launch": "one CUDA-graph replay per forward" if graph else "eager, one Python call per kernel",
-            "l2": "explicit L2 flush (256 MiB write) between timed iterations"}
+            "l2": "explicit L2 flush (256 MiB write) between timed iterations",
+            "e2e_result": "[CLS] row of every sequence (the pooled-embedding caller's read), float32"}
 
 
 def run_reference(args, name, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    B, scaling = batch_per_gpu(w, max(args.gpus, 1))
     # bounded sample: a batch small enough that steps+warmup end within minutes
-    sample_b = max(1, min(w["B"], 32 if w["L"] <= 128 else 1))
+    sample_b = max(1, min(B, 32 if w["L"] <= 128 else 1))
     torch.set_num_threads(os.cpu_count() or 1)
     run = cpu_forward_fn(w, w["layers"], sample_b)
     for _ in range(args.warmup):
@@ -191,57 +218,79 @@ def run_reference(args, name, w):
     sample = f"{sample_b} sequences per step of the same workload, float32, stock PyTorch ops on CPU"
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_of(name, w, args.gpus, graph=not args.no_graph),
+            "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_of(name, w, B, args.gpus, scaling, graph=not args.no_graph),
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                              "sample": sample},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="m2bert80m-L128", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
-    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch per GPU")
-    args = ap.parse_args()
-    name, w = args.workload, dict(WORKLOADS[args.workload])
-    if args.batch > 0:
-        w["B"] = args.batch
-    if args.impl == "reference":
-        run_reference(args, name, w)
-        return
+class Ctx:
+    """Process-wide state of one benchmark run."""
 
-    import torch.distributed as dist
+    def __init__(self, args):
+        import torch.distributed as dist
+        self.args, self.dist = args, dist
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        assert self.world == args.gpus or self.world == 1 and args.gpus == 1, "launch with torchrun for --gpus > 1"
+        torch.cuda.set_device(self.local)
+        self.dev = torch.device("cuda", self.local)
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
+        self.stream = torch.cuda.current_stream(self.dev)
+
+    def barrier(self):
+        torch.cuda.synchronize(self.dev)
+        if self.world > 1:
+            self.dist.barrier()
+        torch.cuda.synchronize(self.dev)
+
+    def timed(self, step, steps):
+        """Per-step CUDA events on the launching stream, L2 flushed between steps; ms over exactly `steps`."""
+        evs = []
+        for _ in range(steps):
+            self.flush.fill_(1)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(self.stream); step(); e.record(self.stream)
+            evs.append((s, e))
+        torch.cuda.synchronize(self.dev)
+        return sum(s.elapsed_time(e) for s, e in evs)
+
+    def max_over_ranks(self, values):
+        t = torch.tensor(values, dtype=torch.float64, device=self.dev)
+        if self.world > 1:
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return t.tolist()
+
+
+def measure(ctx, name, w, steps, warmup, clocks=False):
+    """One workload on every rank: resident and end-to-end throughput, per-kernel device times, roofline of the
+    long-convolution kernel.  Returns the measurement dict on rank 0 (None elsewhere)."""
     from m2_b200 import ops
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    assert world == args.gpus or world == 1 and args.gpus == 1, "launch with torchrun for --gpus > 1"
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
+    args, dev, world, rank = ctx.args, ctx.dev, ctx.world, ctx.rank
+    B, scaling = batch_per_gpu(w, world)
+    L, D = w["L"], w["D"]
     model = build_model(w, seed=0).to(dev)
-    B, L = w["B"], w["L"]
     g = torch.Generator().manual_seed(1234 + rank)
     ids_host = torch.randint(0, VOCAB, (B, L), generator=g).pin_memory()
     ids_dev = ids_host.to(dev)
-    cls_host = torch.empty((B, w["D"]), dtype=torch.float32).pin_memory()
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-    stream = torch.cuda.current_stream(dev)
+    cls_host = torch.empty((B, D), dtype=torch.float32).pin_memory()
 
     def step_eager():
         with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
             out, _ = model(ids_dev)
         return out
+
+    # cold: the first forward generates every layer's filters (MLP on CUDA cores) and spectrum tables
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    step_eager()
+    torch.cuda.synchronize(dev)
+    cold_ms = 1e3 * (time.perf_counter() - t0)
 
     if args.no_graph:
         step_resident = step_eager
@@ -255,7 +304,7 @@ def main():
     else:
         # the public fixed-shape entry point: one captured forward, replayed per batch
         from m2_b200.graph import GraphedForward
-        graphed = GraphedForward(model, ids_dev, warmup=max(args.warmup, 3))
+        graphed = GraphedForward(model, ids_dev, warmup=max(warmup, 3))
 
         def step_resident():
             return graphed(graphed.static_in[0])[0]
@@ -265,88 +314,161 @@ def main():
             cls_host.copy_(out[:, 0], non_blocking=True)
             return out
 
-    def barrier():
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize(dev)
-
-    def timed(step, steps):
-        """Per-step CUDA events on the launching stream, L2 flushed between steps."""
-        evs = []
-        for _ in range(steps):
-            flush.fill_(1)
-            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            s.record(stream); step(); e.record(stream)
-            evs.append((s, e))
-        torch.cuda.synchronize(dev)
-        return sum(s.elapsed_time(e) for s, e in evs)      # ms over exactly `steps` steps
-
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step_resident()
     step_e2e()
-    barrier()
-
-    sampler = ClockSampler(local)
-    if rank == 0:
+    ctx.barrier()
+    sampler = ClockSampler(ctx.local) if (clocks and rank == 0) else None
+    if sampler:
         sampler.start()
     ops.LAUNCHES = 0
-    total_ms = timed(step_resident, args.steps)
+    total_ms = ctx.timed(step_resident, steps)
     launches = ops.LAUNCHES
-    barrier()
-    e2e_ms = timed(step_e2e, args.steps)
-    barrier()
-    clocks = sampler.stop() if rank == 0 else None
-    # per-kernel device times: a separate eager pass with an event pair around every launch of
-    # this library (the events would perturb the timed steps)
+    ctx.barrier()
+    e2e_ms = ctx.timed(step_e2e, steps)
+    ctx.barrier()
+    clock_rec = sampler.stop() if sampler else None
+    # per-kernel device times: a separate eager pass with an event pair around every launch of this library
+    # (the events would perturb the timed steps)
     ops.PROFILE = ops.LaunchProfile()
     prof_steps = 3
     for _ in range(prof_steps):
-        flush.fill_(1)
+        ctx.flush.fill_(1)
         step_eager()
     torch.cuda.synchronize(dev)
     prof, ops.PROFILE = ops.PROFILE, None
-
-    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = t.tolist()
-
+    total_ms, e2e_ms = ctx.max_over_ranks([total_ms, e2e_ms])
+    res = None
     if rank == 0:
-        ms_per_step = total_ms / args.steps
-        value = world * B / (ms_per_step / 1e3)
-        e2e_value = world * B / (e2e_ms / args.steps / 1e3)
-        # roofline of the fused long-convolution kernel (one launch per layer per step)
+        ms_per_step = total_ms / steps
         conv_ms = prof.mean_ms("m2_longconv_fwd")
-        D = w["D"]
         alg_bytes = 10.0 * B * D * L + 16.0 * D * L          # bf16 activations, two filters
         peak, peak_src = measured_peaks()
         achieved = alg_bytes / (conv_ms * 1e-3) / 1e9 if conv_ms else None
-        # DRAM bytes per launch of that kernel from the ncu captures summarised under profiles/
-        # (dram__bytes_read.sum + dram__bytes_write.sum); None where no capture of the shape exists
-        traffic = {"m2bert80m-L128": 247.2e6, "m2bert80m-L8192": 564e6}.get(name)
-        roof = {"bound": "hbm", "kernel": "m2_longconv_fwd", "achieved": achieved, "peak": peak,
-                "peak_source": peak_src, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
-                "traffic": traffic, "launch_ms": conv_ms, "algorithmic_bytes_per_launch": alg_bytes,
-                "kernel_ms_per_step": {k: prof.mean_ms(k) * prof.count(k) / prof_steps for k in prof.names()}}
+        traffic, traffic_src = TRAFFIC.get(name, (None, None)) if B == WORKLOADS[name].get("per_gpu", WORKLOADS[name].get("global_batch")) else (None, None)
+        res = {"value": world * B / (ms_per_step / 1e3), "unit": UNIT, "ms_per_step": ms_per_step, "steps": steps,
+               "scaling": scaling, "config": config_of(name, w, B, world, scaling, graph=not args.no_graph),
+               "e2e": {"value": world * B / (e2e_ms / steps / 1e3), "unit": UNIT,
+                       "h2d_bytes_per_step": ids_host.numel() * 8, "d2h_bytes_per_step": cls_host.numel() * 4},
+               "tokens_per_ms": world * B * L / ms_per_step,
+               "gpu_launches": launches, "cold_first_forward_ms": cold_ms, "clocks": clock_rec,
+               "roofline": {"bound": "hbm", "kernel": "m2_longconv_fwd", "achieved": achieved, "peak": peak,
+                            "peak_source": peak_src, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
+                            "traffic": traffic, "traffic_source": traffic_src, "launch_ms": conv_ms,
+                            "algorithmic_bytes_per_launch": alg_bytes},
+               "kernel_ms_per_step": {k: prof.mean_ms(k) * prof.count(k) / prof_steps for k in prof.names()}}
+    return res
+
+
+def measure_channel_shard(ctx, steps, warmup):
+    """The 32K mixer sharded by d_model channel: every rank holds the full batch of 8 and computes channels
+    [r D/N, (r+1) D/N) of the tensor out_linear consumes (in_linear rows, short conv, gates, both long
+    convolutions).  Timed region: that computation only (max over ranks); afterwards an NCCL all-gather
+    reassembles the shards and rank 0 compares them with the tensor computed whole on its own GPU."""
+    from m2_b200 import sharding
+    w = dict(WORKLOADS["m2bert80m-L32768"], layers=1)
+    B, L, D = w["global_batch"], w["L"], w["D"]
+    dev, world, rank = ctx.dev, ctx.world, ctx.rank
+    mixer = build_model(w, seed=0).to(dev).encoder.layer[0].attention
+    u = torch.randn((B, L, D), generator=torch.Generator().manual_seed(4321)).to(dev)     # the same on every rank
+    lo, hi = sharding.shard_range(D, rank, world)
+
+    def step():
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            return mixer.forward_channels(u, lo, hi)
+
+    for _ in range(max(warmup, 3)):
+        step()
+    ctx.barrier()
+    ms = ctx.timed(step, steps)
+    ctx.barrier()
+    (ms,) = ctx.max_over_ranks([ms])
+    mine = step().contiguous()
+    equal = None
+    if world > 1:
+        gathered = sharding.gather_channels(mine)
+        if rank == 0:
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                equal = bool(torch.equal(gathered, mixer.forward_channels(u, 0, D)))
+        del gathered
+    res = None
+    if rank == 0:
+        res = {"workload": f"sequence mixer without out_linear, d_model {D}, L={L}, batch {B} on every rank, "
+                           f"{D // world} channels per rank, u ~ N(0,1), bf16 autocast",
+               "value": B / (ms / steps / 1e3), "unit": UNIT, "ms_per_step": ms / steps, "steps": steps,
+               "scaling": "strong", "channels_per_gpu": hi - lo,
+               "gathered_equals_single_gpu": equal, "collective": "NCCL all_gather after the timed region (verification only)"}
+    del mixer, u, mine
+    torch.cuda.empty_cache()
+    return res
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+                    help="measure only this workload (default: the L=128 headline plus all others under `workloads`)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel from Python instead of replaying a CUDA graph")
+    ap.add_argument("--batch", type=int, default=0, help="override the headline workload's batch per GPU")
+    args = ap.parse_args()
+    name = args.workload or HEADLINE
+    w = dict(WORKLOADS[name])
+    if args.batch > 0:
+        w.pop("global_batch", None)
+        w["per_gpu"] = args.batch
+    if args.impl == "reference":
+        run_reference(args, name, w)
+        return
+
+    import gc
+    ctx = Ctx(args)
+    head = measure(ctx, name, w, args.steps, max(args.warmup, 3), clocks=True)
+    gc.collect(); torch.cuda.empty_cache()
+    others, shard = {}, None
+    if args.workload is None:
+        sub_steps = max(3, min(args.steps, 5))
+        for other, ow in WORKLOADS.items():
+            if other == name:
+                continue
+            try:
+                r = measure(ctx, other, dict(ow), sub_steps, 3)
+            except SystemExit as e:                      # a global batch that does not split over this many ranks
+                r = {"skipped": str(e)} if ctx.rank == 0 else None
+            if ctx.rank == 0:
+                others[other] = r
+            gc.collect(); torch.cuda.empty_cache()
+        if WORKLOADS["m2bert80m-L32768"]["D"] % ctx.world == 0:
+            shard = measure_channel_shard(ctx, sub_steps, 3)
+            gc.collect(); torch.cuda.empty_cache()
+
+    if ctx.rank == 0:
         cpu = None
-        if not args.no_cpu_baseline:
-            sample_b = 32 if L <= 128 else 1
+        if not args.no_cpu_baseline and ctx.world == 1:
+            sample_b = 32 if w["L"] <= 128 else 1
             reps = 3
             v, dt = time_cpu(w, sample_b, reps)
             cpu = {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
                    "sample": f"{reps} forwards of {sample_b} sequences of the same workload "
                              f"({dt:.2f} s each), float32, stock PyTorch ops on the host CPU"}
-        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-                "config": config_of(name, w, world, graph=not args.no_graph),
-                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": ids_host.numel() * 8,
-                        "d2h_bytes_per_step": cls_host.numel() * 4},
-                "gpu_launches": launches, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+        line = {"metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": ctx.world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+                "scaling": head["scaling"], "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": head["config"], "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
+                "clocks": head["clocks"], "tokens_per_ms": head["tokens_per_ms"],
+                "cold_first_forward_ms": head["cold_first_forward_ms"],
+                "roofline": dict(head["roofline"], kernel_ms_per_step=head["kernel_ms_per_step"]),
+                "cpu_baseline": cpu}
+        if others:
+            line["workloads"] = others
+        if shard is not None:
+            line["channel_shard"] = shard
         print(json.dumps(line))
-    if world > 1:
-        dist.destroy_process_group()
+    if ctx.world > 1:
+        ctx.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -139,6 +139,61 @@ class MonarchMixerSequenceMixing(nn.Module):
         return ops.linear_fwd(buf.permute(1, 2, 0), w_out, self.out_linear.bias)                     # (B, L, D)
 
     @forward_only
+    def forward_channels(self, u, lo, hi):
+        """Channels [lo, hi) of the tensor out_linear consumes, (B, L, hi - lo) bf16, computed from the full
+        input u (B, L, d_model) under bf16 autocast -- the unit of work when the mixer is sharded by d_model
+        channel over several GPUs: short convolution, gates and long convolutions are independent per
+        channel, in_linear contributes its rows c, D + c, 2D + c, and only out_linear mixes channels (it is
+        not part of a shard).  Shards computed on different GPUs and concatenated along the last axis equal
+        forward_channels(u, 0, d_model) bit for bit.  The reference has no counterpart (its parallelism is
+        data parallel only); this follows bert/src/mm/monarch_mixer_sequence_mixer.py:108-149 per channel."""
+        if not (u.is_cuda and _autocast_bf16()):
+            raise RuntimeError("forward_channels runs on CUDA tensors under torch.autocast('cuda', dtype=torch.bfloat16)")
+        B, L, D = u.shape
+        if not (0 <= lo < hi <= D):
+            raise ValueError(f"channel range [{lo}, {hi}) outside d_model {D}")
+        C = hi - lo
+        filters = [self.filter_fn] + ([self.filter_fn2] if self.residual_long_conv else [])
+        kind = ops.longconv_kind(L, torch.bfloat16, C)
+        if kind == 1:
+            kind = 0                         # the small-batch FFT family wants 128-channel tiles; a shard need not have them
+        key = (lo, hi, L, kind, tuple(f._version_key() for f in filters),
+               self.in_linear.weight._version, self.in_linear.bias._version,
+               self.short_filter.weight._version, self.short_filter.bias._version,
+               tuple(f.bias._version for f in filters))
+        cache = getattr(self, "_shard_cache", None)
+        if cache is None or cache[0] != key:
+            rows = torch.cat([torch.arange(g * D + lo, g * D + hi, device=u.device) for g in range(3)])
+            w_in, _ = self._weights()
+            shard = dict(
+                w=w_in[rows].contiguous(), b=self.in_linear.bias.detach()[rows].contiguous(),
+                sw=self.short_filter.weight.detach()[rows].contiguous(), sb=self.short_filter.bias.detach()[rows].contiguous(),
+                specs=[ops.filter_spectrum(f.time_filter(L, True)[lo:hi].contiguous(), L, kind) for f in filters],
+                biases=[f.conv_bias().detach()[lo:hi].contiguous() for f in filters])
+            self._shard_cache = cache = (key, shard)
+        sh = cache[1]
+        ures = u if self.residual_long_conv else None
+        if kind == 2:
+            Lp = _round_up(L, 16)
+            xin_t = torch.empty((B, 3 * C, Lp), dtype=torch.bfloat16, device=u.device)[:, :, :L]
+            ops.linear_fwd(bf16_input(u), sh["w"], sh["b"], out=xin_t.permute(0, 2, 1))
+            u_view, yu_bf16 = None, False
+            if ures is not None:
+                rec = copies_of(ures)
+                tm = rec.tm if rec is not None else None
+                if tm is not None and tm.shape == (D, B, L):
+                    u_view, yu_bf16 = tm[lo:hi].permute(1, 2, 0), src_dtype_of(ures) == torch.bfloat16
+                else:
+                    u_view = ures[..., lo:hi].transpose(1, 2).contiguous().transpose(1, 2)
+            y_t = torch.empty((B, C, Lp), dtype=torch.bfloat16, device=u.device)[:, :, :L]
+            ops.longconv_fwd(xin_t.permute(0, 2, 1), u_view, sh["sw"], sh["sb"], sh["specs"], sh["biases"],
+                             kind=2, bf16_rounding=True, out=y_t.permute(0, 2, 1), yu_bf16=yu_bf16)
+            return y_t.permute(0, 2, 1)
+        xin = ops.linear_fwd(bf16_input(u), sh["w"], sh["b"])
+        return ops.longconv_fwd(xin, ures[..., lo:hi] if ures is not None else None, sh["sw"], sh["sb"], sh["specs"],
+                                sh["biases"], kind=kind, bf16_rounding=True)
+
+    @forward_only
     def forward(self, u, **kwargs):
         if not u.is_cuda:
             raise RuntimeError("m2_b200.MonarchMixerSequenceMixing needs CUDA tensors; there is no CPU fallback")

@@ -128,3 +128,69 @@ def test_mixer_only_32k_batch8_rows_are_independent():
         ref = T.mixer_forward(sdt, u[:1], bidirectional=True, residual_long_conv=True,
                               prefix="encoder.layer.0.attention.")
     assert err(y[:1], ref) < TOL_BF16
+
+
+def test_channel_shards_reassemble_the_mixer():
+    """The d_model-channel sharding of config 4, on one GPU: shards of the un-mixed middle of the mixer,
+    concatenated, equal the un-sharded tensor bit for bit; out_linear of it equals the mixer's forward."""
+    from m2_b200 import sharding
+    L, D = 8192, 768
+    model, sdt = build(1, D, 3072, L, seed=65)
+    mixer = model.encoder.layer[0].attention
+    u = torch.randn((2, L, D), generator=torch.Generator(device="cpu").manual_seed(10)).to(DEV)
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        whole = mixer.forward_channels(u, 0, D).clone()
+        parts = []
+        for r in range(8):
+            lo, hi = sharding.shard_range(D, r, 8)
+            parts.append(mixer.forward_channels(u, lo, hi).clone())
+        assert torch.equal(torch.cat(parts, dim=-1), whole)
+        y, _ = mixer(u)
+        w_out = mixer.out_linear.weight.detach().bfloat16().contiguous()
+        assert torch.equal(ops.linear_fwd(whole.contiguous(), w_out, mixer.out_linear.bias), y)
+
+
+_SHARD_WORKER = r"""
+import os, sys, torch, torch.distributed as dist
+root, port, rank, world = sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4])
+sys.path.insert(0, root)
+os.environ["NCCL_NVLS_ENABLE"] = "0"
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                        device_id=torch.device("cuda", rank))
+from m2_b200 import sharding
+from tests.test_gpu_configs import build
+import tests.test_gpu_configs as T
+T.DEV = f"cuda:{rank}"
+L, D = 4096, 768
+model, _ = build(1, D, 3072, L, seed=66)
+mixer = model.encoder.layer[0].attention
+u = torch.randn((2, L, D), generator=torch.Generator(device="cpu").manual_seed(11)).to(T.DEV)
+lo, hi = sharding.shard_range(D, rank, world)
+with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+    mine = mixer.forward_channels(u, lo, hi).contiguous()
+    gathered = sharding.gather_channels(mine)
+    whole = mixer.forward_channels(u, 0, D)
+assert torch.equal(gathered, whole), "gathered channel shards differ from the single-GPU tensor"
+torch.cuda.synchronize()
+dist.barrier(); dist.destroy_process_group()
+print("ok", rank)
+"""
+
+
+def test_channel_shards_over_two_gpus_gathered_with_nccl(tmp_path):
+    """Rank r computes channels [r D/2, (r+1) D/2) of the full batch on its own GPU; an NCCL all-gather (the
+    only collective, for verification) reassembles them; equal to the single-GPU tensor."""
+    import os
+    import subprocess
+    import sys
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "shard_worker.py"
+    script.write_text(_SHARD_WORKER)
+    port = str(29700 + os.getpid() % 2000)
+    procs = [subprocess.Popen([sys.executable, str(script), root, port, str(r), "2"],
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), outs
