@@ -1,31 +1,33 @@
 // Fused gated long convolution on tcgen05 tensor cores for long rows (kernel family 2):
 // bf16 activations stored time-contiguous ((B, channels, L) layout), transform length
-// N = 32 * N2 * N3 = 4096 (1024 < L <= 2048), 16384 (4096 < L <= 8192) or 65536
-// (16384 < L <= 32768).
+// N = 32 * N2 * N3 = 4096 (L <= 2048), 16384 (L <= 8192) or 65536 (L <= 32768).
 //
-// One (batch row, channel) sequence is processed at a time by a "slot" of four warps (sixteen
-// for N = 65536, where one sequence fills the SM); a CTA holds several slots that run independently (own barriers, own TMEM columns, own shared-
-// memory region) so that one slot's loads and stage hand-offs overlap the others' work.
+// One (batch row, channel) sequence is processed at a time by a "slot" of 128 * TS threads; a CTA holds several
+// slots that run independently (own barriers, own TMEM columns, own shared-memory region) so that one slot's loads
+// and stage hand-offs overlap the others' work.
 //
-// The real FFT of length N is evaluated at the odd frequencies k + 1/2 (negacyclic form,
-// no DC/Nyquist specials, Hermitian half = k1 < 16) and factored Monarch style with
-// n = R n1 + N3 n2 + n3 (R = N2 N3), k = k1 + 32 k2 + 32 N2 k3:
+// The real FFT of length N is evaluated at the odd frequencies k + 1/2 (negacyclic form, no DC/Nyquist specials,
+// Hermitian half = k1 < 16) and factored Monarch style with n = R n1 + N3 n2 + n3 (R = N2 N3),
+// k = k1 + 32 k2 + 32 N2 k3:
 //
-//   F1  rows r = (n2, n3):  B1[r, k1]   = sum_{n1 < 16} W32^{n1 (k1 + 1/2)} a[R n1 + r]
-//   x T1[r, k1] = w^{r (k1 + 1/2)}, rows -> (k1, n3)
-//   F2  rows (k1, n3):      B2[., k2]   = sum_{n2} W_N2^{n2 k2} B1
-//   x T2[n3, k2] = w^{32 n3 k2}, rows -> (k1, k2)
-//   F3  rows (k1, k2):      Z[., k3]    = sum_{n3} W_N3^{n3 k3} B2
-//   x (G + bias), then the three inverse stages in mirror order; I1 yields only the L kept
-//   outputs y[R n1 + r], n1 < 16.  The inverse DFT stages reuse the forward matrices on
-//   conjugated data (IDFT(x) = conj DFT(conj x)), so each radix needs one matrix only.
+//   F1  B1[r, k1]       = sum_{n1 < 16} W32^{n1 (k1 + 1/2)} a[R n1 + r],   r = (n2, n3)
+//   x   w^{r (k1 + 1/2)}                      (as the product of an n2 part and an n3 part)
+//   F2  B2[k1, n3, k2]  = sum_{n2} W_N2^{n2 k2} B1
+//   x   w^{32 n3 k2}
+//   F3  Z[k1, k2, k3]   = sum_{n3} W_N3^{n3 k3} B2
+//   x   (G + bias), then the three inverse stages in mirror order on conjugated data (IDFT(x) = conj DFT(conj x),
+//   so every radix needs one matrix only); the last stage yields only the L kept outputs y[R n1 + r], n1 < 16.
 //
-// Every stage is a batched real GEMM with M = 128 rows per tile taken from inside the
-// sequence itself, fp16 operands in un-swizzled core-matrix shared memory, constant DFT
-// matrices as B operands and float32 accumulators in tensor memory.  Between stages the
-// thread that owns a TMEM lane applies the twiddle and scatters its row into the next
-// stage's operand layout (the row <-> column exchange of the four-step FFT happens in
-// these stores).
+// Every stage is a batched real GEMM with M = 128 rows per tile, fp16 operands in un-swizzled core-matrix shared
+// memory, constant DFT matrices as B operands and float32 accumulators in tensor memory.  Complex data is PLANAR:
+// a TMEM row holds [Re of all columns | Im of all columns], so the thread that owns the row has both parts of
+// every element, applies the twiddle with packed half2 arithmetic and writes its row as 16-byte chunks of 8
+// consecutive columns.  What makes this possible is the operand view: a stage that contracts over the index held
+// in the PREVIOUS stage's rows reads those chunks as an "MN-major" A operand (the 8 columns of a chunk become 8
+// consecutive M rows, the row index becomes K), so the row <-> column exchange of the four-step FFT happens inside
+// the MMA's operand fetch -- never as scattered stores.  Only the spectrum stage (Z -> inverse F3), which
+// contracts over its own columns, uses the ordinary K-major view.  All chunk stores are bank-conflict free
+// (row groups are padded by 16 bytes where consecutive lanes write to consecutive groups).
 //
 // Computation replaced: bert/src/mm/monarch_mixer_sequence_mixer.py:109-149 and
 // bert/src/mm/hyena_utils.py:16-42, :219-248 of the reference.
@@ -41,9 +43,8 @@ __host__ __device__ constexpr float stage_scale(int n) {   // 2^-ceil(log2(n)/2)
 }
 __host__ __device__ constexpr int cmax(int a, int b) { return a > b ? a : b; }
 
-// N2, N3: radices of the second and third stage (the first is 32); SLOTS: independent
-// sequences in flight per CTA; TS: warps per TMEM lane quarter inside a slot (they split
-// the row tiles of every stage among themselves).
+// N2, N3: radices of the second and third stage (the first is 32); SLOTS: independent sequences in flight per
+// CTA; TS: groups of 128 threads inside a slot (they split the row tiles of every stage among themselves).
 template <int N2_, int N3_, int SLOTS_, int TS_>
 struct Geo {
   static constexpr int N2 = N2_, N3 = N3_, SLOTS = SLOTS_, TS = TS_;
@@ -51,82 +52,90 @@ struct Geo {
   static constexpr int N = 32 * R;
   static constexpr int LG = (N == 4096) ? 12 : (N == 16384) ? 14 : 16;
   static constexpr int K2 = 2 * N2, K3 = 2 * N3;
-  static constexpr int TR = R / 128;            // row tiles of the first / last stage
-  static constexpr int T2T = 16 * N3 / 128;     // row tiles of the DFT_N2 stages
-  static constexpr int T3T = 16 * N2 / 128;     // row tiles of the DFT_N3 stages
-  static constexpr int G2 = N2 / 8, G3 = N3 / 8;             // 8-row groups per k1
+  static constexpr int T1T = R / 128;           // row tiles of the first / last stage (rows r)
+  static constexpr int T2T = N3 / 8;            // row tiles of the DFT_N2 stages (rows (k1, n3), 16 N3 of them)
+  static constexpr int T3T = N2 / 8;            // row tiles of the DFT_N3 stages (rows (k1, k2), 16 N2 of them)
   static constexpr int TPS = 128 * TS;          // threads per slot
   static constexpr int THREADS = SLOTS * TPS;
-  static constexpr bool SPLIT_T1 = R > 512;     // twiddle table of stage 1 as a product of two small ones
-  // operand layouts: core matrices of 8 rows x 16 bytes; LBO = stride between K chunks,
-  // SBO = stride between 8-row groups, TILE = 128 rows.  The padded strides spread the
-  // scattered 4-byte stores of the re-layout steps over the shared-memory banks.
-  static constexpr int A1_LBO = 128, A1_SBO = 2 * 128 + 16, A1_TILE = 16 * A1_SBO;            // K = 16
-  static constexpr int A2_LBO = 144, A2_SBO = (K2 / 8) * 144, A2_TILE = 16 * A2_SBO;          // K = K2
-  static constexpr int A3_LBO = 144, A3_SBO = (K3 / 8) * 144 + 16, A3_TILE = 16 * A3_SBO;     // K = K3
-  static constexpr int A6_LBO = 128, A6_SBO = 4 * 128, A6_TILE = 16 * A6_SBO;                 // K = 32
+  // operand regions (byte strides): a row GROUP is 8 rows of the MMA's M; its K extent is contiguous in 128-byte
+  // core matrices (LBO = 128); groups follow each other at the SBO below (+16 where lanes hit consecutive groups)
+  static constexpr int SBO1 = 256;                          // F1 operand: K = 16 (n1)
+  static constexpr int SBO2 = K2 * 16 + 16;                 // DFT_N2 forward operand: K = (ri, n2)
+  static constexpr int SBO3 = K3 * 16 + 16;                 // DFT_N3 forward operand: K = (ri, n3)
+  static constexpr int SBO3K = K3 * 16, TILE3 = 16 * SBO3K; // DFT_N3 inverse operand (K-major rows): K = (ri, k3)
+  static constexpr int SBO4 = K2 * 16;                      // DFT_N2 inverse operand: K = (ri, k2)
+  static constexpr int SBO5 = 32 * 16 + 16;                 // last stage operand: K = (ri, k1)
+  static constexpr int YF = 16 * R + 4 * (16 * R / 32);     // floats of the padded output buffer (4 after every 32)
   static constexpr int DATA_BYTES =
-      ((cmax(cmax(TR * A1_TILE, T2T * A2_TILE), cmax(cmax(T3T * A3_TILE, TR * A6_TILE), 64 * R)) + 127) / 128) * 128;
-  static constexpr int COLS = cmax(TR * 32, cmax(T2T * K2, T3T * K3));
+      ((cmax(cmax(cmax(R * 32, 2 * N3 * SBO2), cmax(2 * N2 * SBO3, T3T * TILE3)),
+             cmax(cmax(2 * N3 * SBO4, (R / 8) * SBO5), 4 * YF)) + 127) / 128) * 128;
+  static constexpr int COLS = cmax(T1T * 32, cmax(T2T * K2, T3T * K3));
   static constexpr int TCOLS = (SLOTS * COLS <= 32) ? 32 : (SLOTS * COLS <= 64) ? 64 : (SLOTS * COLS <= 128) ? 128
                                : (SLOTS * COLS <= 256) ? 256 : 512;
   static constexpr float S2 = stage_scale(N2), S3 = stage_scale(N3);
   static constexpr float KAPPA = (2.0f / N) / ((S1 * S2 * S3) * (S1 * S2 * S3));
-  // header of the spectrum table (bytes): constant matrices (un-padded core-matrix layout)
-  // and twiddle tables
-  static constexpr int F1_OFF = 0;                       // [32 x 16]
-  static constexpr int I1_OFF = F1_OFF + 1024;           // [16 x 32]
-  static constexpr int F2_OFF = I1_OFF + 1024;           // [K2 x K2]
-  static constexpr int F3_OFF = F2_OFF + K2 * K2 * 2;    // [K3 x K3]
-  static constexpr int T1_OFF = F3_OFF + K3 * K3 * 2;    // half2 [16][R], or [16][N2] then [16][N3] when split
-  static constexpr int T1_BYTES = SPLIT_T1 ? 64 * (N2 + N3) : 64 * R;
-  static constexpr int T2A_OFF = T1_OFF + T1_BYTES;      // half2 [N2][N3]  (k2 major)
-  static constexpr int T2B_OFF = T2A_OFF + 4 * R;        // half2 [N3][N2]  (n3 major)
-  static constexpr int HDR_BYTES = T2B_OFF + 4 * R;
+  // header of the spectrum table (bytes): constant matrices (core-matrix layout, K-major B operands) and
+  // twiddle tables (fp16, planar: 16-byte runs of Re then of Im)
+  static constexpr int F1_OFF = 0;                       // [32 (ri, k1)] x [16 n1]
+  static constexpr int I1_OFF = F1_OFF + 1024;           // [16 n1] x [32 (ri, k1)]
+  static constexpr int F2_OFF = I1_OFF + 1024;           // [K2 (ri', k2)] x [K2 (ri, n2)]
+  static constexpr int F3_OFF = F2_OFF + K2 * K2 * 2;    // [K3] x [K3]
+  static constexpr int TA1_OFF = F3_OFF + K3 * K3 * 2;   // [n2][Re k1 x16 | Im k1 x16]: w^{N3 n2 (k1 + 1/2)}
+  static constexpr int TB1_PITCH = 64 + 16;              // rows read by 8 lanes at once are padded by 16 bytes: no two
+  static constexpr int T2B_PITCH = K3 * 2 + 16;          // of the 8 rows start in the same 16-byte bank group
+  static constexpr int TB1_OFF = TA1_OFF + N2 * 64;      // [n3][Re k1 x16 | Im k1 x16 | pad]: w^{n3 (k1 + 1/2)}
+  static constexpr int TA5_OFF = TB1_OFF + N3 * TB1_PITCH;   // [k1][Re n2 x N2 | Im n2 x N2]
+  static constexpr int TB5_OFF = TA5_OFF + 16 * K2 * 2;  // [k1][n3] half2 (Re, Im)
+  static constexpr int T2A_OFF = TB5_OFF + 16 * N3 * 4;  // [n3][Re k2 x N2 | Im k2 x N2]: w^{32 n3 k2}
+  static constexpr int T2B_OFF = T2A_OFF + 4 * R;        // [k2][Re n3 x N3 | Im n3 x N3 | pad]
+  static constexpr int HDR_BYTES = T2B_OFF + N2 * T2B_PITCH;
   static constexpr int HDR_FLOATS = HDR_BYTES / 4;
   static constexpr int SMEM = SLOTS * DATA_BYTES + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
-  static_assert(R % 128 == 0 && (16 * N3) % 128 == 0 && (16 * N2) % 128 == 0, "row tiles must be full");
+  static_assert(R % 128 == 0 && N3 % 8 == 0 && N2 % 8 == 0, "row tiles must be full");
   static_assert(SLOTS * COLS <= 512, "accumulators exceed tensor memory");
-  static_assert(TR % TS == 0 && T2T % TS == 0 && T3T % TS == 0, "tile split must divide every stage");
-  static_assert((R / 4) % TPS == 0 || TPS % (R / 4) == 0, "load mapping");
+  static_assert(T1T % TS == 0 && T2T % TS == 0 && T3T % TS == 0, "tile split must divide every stage");
+  static_assert((2 * R) % TPS == 0 && (4 * R) % TPS == 0, "load / store mapping");
+  static_assert(HDR_BYTES % 16 == 0, "header is copied in 16-byte pieces");
   static_assert(SMEM <= 227 * 1024, "shared memory");
 };
 
-// byte offset of element (row, k) of a constant matrix with K columns (un-padded layout)
+// byte offset of element (row, k) of a constant matrix with K columns (K-major B operand, un-padded)
 template <int K>
 __host__ __device__ constexpr int mat_off(int row, int k) {
   return (row >> 3) * (K * 16) + (k >> 3) * 128 + (row & 7) * 16 + (k & 7) * 2;
 }
 
 // ---------------------------------------------------------------------------------------
-// Spectrum table (kind 2): [HDR_FLOATS floats: matrices + twiddles] then per channel
-// G[(k1 N2 + k2)][k3] as half2, multiplied by KAPPA * 2^e, then one float 2^-e per channel.
+// Spectrum table (kind 2): [HDR_FLOATS floats: matrices + twiddles], then per channel N fp16 values -- for
+// row tile t3 = k2 / 8 and row m = 8 k1 + (k2 % 8): [Re G[k3] x N3 | Im G[k3] x N3], bins
+// k = k1 + 32 k2 + 32 N2 k3, multiplied by KAPPA * 2^e -- then one float 2^-e per channel.
 // ---------------------------------------------------------------------------------------
 template <typename G>
 __device__ void write_header(float* spec, int tid, int nt) {
-  constexpr int N = G::N, N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3;
+  constexpr int N = G::N, N2 = G::N2, N3 = G::N3, K2 = G::K2, K3 = G::K3;
+  unsigned char* base = reinterpret_cast<unsigned char*>(spec);
   __half* m = reinterpret_cast<__half*>(spec);
   for (int idx = tid; idx < 16 * 16; idx += nt) {
-    // F1 rows 2k1+ri: W32^{n1 (k1+1/2)}.  I1 columns 2k1+ri act on the CONJUGATE of the last
-    // inverse stage's input: y = sum cos * Qr + sin * Qi.
+    // F1 rows (ri, k1): W32^{n1 (k1+1/2)} = cos - i sin.  I1 acts on the CONJUGATE of the last inverse stage's
+    // input: y = sum cos * Qr + sin * Qi.
     const int k1 = idx / 16, n1 = idx % 16;
     double sn, cs;
     sincospi(2.0 * n1 * (k1 + 0.5) / 32.0, &sn, &cs);
-    m[(G::F1_OFF + mat_off<16>(2 * k1, n1)) / 2] = __double2half(S1 * cs);
-    m[(G::F1_OFF + mat_off<16>(2 * k1 + 1, n1)) / 2] = __double2half(-S1 * sn);
-    m[(G::I1_OFF + mat_off<32>(n1, 2 * k1)) / 2] = __double2half(S1 * cs);
-    m[(G::I1_OFF + mat_off<32>(n1, 2 * k1 + 1)) / 2] = __double2half(S1 * sn);
+    m[(G::F1_OFF + mat_off<16>(k1, n1)) / 2] = __double2half(S1 * cs);
+    m[(G::F1_OFF + mat_off<16>(16 + k1, n1)) / 2] = __double2half(-S1 * sn);
+    m[(G::I1_OFF + mat_off<32>(n1, k1)) / 2] = __double2half(S1 * cs);
+    m[(G::I1_OFF + mat_off<32>(n1, 16 + k1)) / 2] = __double2half(S1 * sn);
   }
-  for (int idx = tid; idx < N2 * N2; idx += nt) {            // forward DFT_N2 in real form
+  for (int idx = tid; idx < N2 * N2; idx += nt) {            // forward DFT_N2, planar real form
     const int ko = idx / N2, ni = idx % N2;
     double sn, cs;
     sincospi(2.0 * ((ko * ni) % N2) / N2, &sn, &cs);
     const double c = G::S2 * cs, s = G::S2 * sn;             // w = c - i s
     __half* f = m + G::F2_OFF / 2;
-    f[mat_off<K2>(2 * ko, 2 * ni) / 2] = __double2half(c);
-    f[mat_off<K2>(2 * ko, 2 * ni + 1) / 2] = __double2half(s);
-    f[mat_off<K2>(2 * ko + 1, 2 * ni) / 2] = __double2half(-s);
-    f[mat_off<K2>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
+    f[mat_off<K2>(ko, ni) / 2] = __double2half(c);
+    f[mat_off<K2>(ko, N2 + ni) / 2] = __double2half(s);
+    f[mat_off<K2>(N2 + ko, ni) / 2] = __double2half(-s);
+    f[mat_off<K2>(N2 + ko, N2 + ni) / 2] = __double2half(c);
   }
   for (int idx = tid; idx < N3 * N3; idx += nt) {            // forward DFT_N3
     const int ko = idx / N3, ni = idx % N3;
@@ -134,42 +143,37 @@ __device__ void write_header(float* spec, int tid, int nt) {
     sincospi(2.0 * ((ko * ni) % N3) / N3, &sn, &cs);
     const double c = G::S3 * cs, s = G::S3 * sn;
     __half* f = m + G::F3_OFF / 2;
-    f[mat_off<K3>(2 * ko, 2 * ni) / 2] = __double2half(c);
-    f[mat_off<K3>(2 * ko, 2 * ni + 1) / 2] = __double2half(s);
-    f[mat_off<K3>(2 * ko + 1, 2 * ni) / 2] = __double2half(-s);
-    f[mat_off<K3>(2 * ko + 1, 2 * ni + 1) / 2] = __double2half(c);
+    f[mat_off<K3>(ko, ni) / 2] = __double2half(c);
+    f[mat_off<K3>(ko, N3 + ni) / 2] = __double2half(s);
+    f[mat_off<K3>(N3 + ko, ni) / 2] = __double2half(-s);
+    f[mat_off<K3>(N3 + ko, N3 + ni) / 2] = __double2half(c);
   }
-  __half2* t1 = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T1_OFF);
-  if (G::SPLIT_T1) {
-    for (int idx = tid; idx < 16 * N2; idx += nt) {          // Ta[k1][n2] = w^{N3 n2 (k1 + 1/2)}
-      const int k1 = idx / N2, n2 = idx % N2;
-      double sn, cs;
-      sincospi(2.0 * N3 * n2 * (k1 + 0.5) / N, &sn, &cs);
-      t1[idx] = __floats2half2_rn((float)cs, (float)(-sn));
-    }
-    for (int idx = tid; idx < 16 * N3; idx += nt) {          // Tb[k1][n3] = w^{n3 (k1 + 1/2)}
-      const int k1 = idx / N3, n3 = idx % N3;
-      double sn, cs;
-      sincospi(2.0 * n3 * (k1 + 0.5) / N, &sn, &cs);
-      t1[16 * N2 + idx] = __floats2half2_rn((float)cs, (float)(-sn));
-    }
-  } else {
-    for (int idx = tid; idx < 16 * R; idx += nt) {           // T1[k1][r] = w^{r (k1 + 1/2)}
-      const int k1 = idx / R, r = idx % R;
-      double sn, cs;
-      sincospi(2.0 * r * (k1 + 0.5) / N, &sn, &cs);
-      t1[idx] = __floats2half2_rn((float)cs, (float)(-sn));
-    }
+  __half* ta1 = reinterpret_cast<__half*>(base + G::TA1_OFF);
+  __half* ta5 = reinterpret_cast<__half*>(base + G::TA5_OFF);
+  for (int idx = tid; idx < 16 * N2; idx += nt) {            // w^{N3 n2 (k1 + 1/2)} in both index orders
+    const int k1 = idx / N2, n2 = idx % N2;
+    double sn, cs;
+    sincospi(2.0 * N3 * n2 * (k1 + 0.5) / N, &sn, &cs);
+    ta1[n2 * 32 + k1] = __double2half(cs);  ta1[n2 * 32 + 16 + k1] = __double2half(-sn);
+    ta5[k1 * K2 + n2] = __double2half(cs);  ta5[k1 * K2 + N2 + n2] = __double2half(-sn);
   }
-  __half2* t2a = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T2A_OFF);
-  __half2* t2b = reinterpret_cast<__half2*>(reinterpret_cast<unsigned char*>(spec) + G::T2B_OFF);
-  for (int idx = tid; idx < R; idx += nt) {                  // T2 = w^{32 n3 k2} in both index orders
+  __half* tb1 = reinterpret_cast<__half*>(base + G::TB1_OFF);
+  __half2* tb5 = reinterpret_cast<__half2*>(base + G::TB5_OFF);
+  for (int idx = tid; idx < 16 * N3; idx += nt) {            // w^{n3 (k1 + 1/2)}
+    const int k1 = idx / N3, n3 = idx % N3;
+    double sn, cs;
+    sincospi(2.0 * n3 * (k1 + 0.5) / N, &sn, &cs);
+    tb1[n3 * (G::TB1_PITCH / 2) + k1] = __double2half(cs);  tb1[n3 * (G::TB1_PITCH / 2) + 16 + k1] = __double2half(-sn);
+    tb5[k1 * N3 + n3] = __floats2half2_rn((float)cs, (float)(-sn));
+  }
+  __half* t2a = reinterpret_cast<__half*>(base + G::T2A_OFF);
+  __half* t2b = reinterpret_cast<__half*>(base + G::T2B_OFF);
+  for (int idx = tid; idx < N2 * N3; idx += nt) {            // w^{32 n3 k2} in both index orders
     const int k2 = idx / N3, n3 = idx % N3;
     double sn, cs;
     sincospi(2.0 * 32.0 * n3 * k2 / N, &sn, &cs);
-    const __half2 v = __floats2half2_rn((float)cs, (float)(-sn));
-    t2a[k2 * N3 + n3] = v;
-    t2b[n3 * N2 + k2] = v;
+    t2a[n3 * K2 + k2] = __double2half(cs);  t2a[n3 * K2 + N2 + k2] = __double2half(-sn);
+    t2b[k2 * (G::T2B_PITCH / 2) + n3] = __double2half(cs);  t2b[k2 * (G::T2B_PITCH / 2) + N3 + n3] = __double2half(-sn);
   }
 }
 
@@ -195,13 +199,22 @@ __device__ __forceinline__ float block_max(float v, float* red) {
   __syncthreads();
   return red[0];
 }
+// position idx of a channel's table (complex entry (t3, m, k3)) -> bin k
+template <typename G>
+__device__ __forceinline__ int table_bin(int idx) {
+  const int k3 = idx % G::N3, m = (idx / G::N3) % 128, t3 = idx / (G::N3 * 128);
+  return (m >> 3) + 32 * (8 * t3 + (m & 7)) + 32 * G::N2 * k3;
+}
+// where its real part goes, in fp16 units from the channel's start (the imaginary part follows N3 entries on)
+template <typename G>
+__device__ __forceinline__ int table_pos(int idx) { return (idx / G::N3) * G::K3 + idx % G::N3; }
 
 // One CTA per channel: N-point complex FFT (decimation in frequency) in shared memory of
 // g[n] w^{n/2}, g = the filter with its wrapped half negated; bins gathered in table order.
 template <typename G>
 __global__ void __launch_bounds__(512)
 spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D, int R) {
-  constexpr int N = G::N, N2 = G::N2, N3 = G::N3;
+  constexpr int N = G::N;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, nt = blockDim.x;
   if (blockIdx.x == (unsigned)D) { write_header<G>(spec, tid, nt); return; }
@@ -234,20 +247,19 @@ spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
   // largest |Re|, |Im| over the stored half of the spectrum decides the channel's scale 2^e (see gain_scale)
   float gmax = 0.f;
   for (int idx = tid; idx < N / 2; idx += nt) {
-    const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
-    const int p = (int)(__brev((unsigned)(k1 + 32 * k2 + 32 * N2 * k3)) >> (32 - G::LG));
+    const int p = (int)(__brev((unsigned)table_bin<G>(idx)) >> (32 - G::LG));
     gmax = fmaxf(gmax, fmaxf(fabsf(s[p].x), fabsf(s[p].y)));
   }
   __shared__ float red[32];
   gmax = block_max(gmax, red);
   const float sc = gain_scale(gmax * G::KAPPA);
   if (tid == 0) spec[G::HDR_FLOATS + (size_t)D * (N / 2) + c] = 1.0f / sc;
-  __half2* Gt = reinterpret_cast<__half2*>(spec + G::HDR_FLOATS) + (size_t)c * (N / 2);
+  __half* Gt = reinterpret_cast<__half*>(spec + G::HDR_FLOATS) + (size_t)c * N;
   for (int idx = tid; idx < N / 2; idx += nt) {
-    const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
-    const int k = k1 + 32 * k2 + 32 * N2 * k3;
-    const int p = (int)(__brev((unsigned)k) >> (32 - G::LG));
-    Gt[idx] = __floats2half2_rn(s[p].x * (G::KAPPA * sc), s[p].y * (G::KAPPA * sc));
+    const int p = (int)(__brev((unsigned)table_bin<G>(idx)) >> (32 - G::LG));
+    const int o = table_pos<G>(idx);
+    Gt[o] = __float2half_rn(s[p].x * (G::KAPPA * sc));
+    Gt[o + G::N3] = __float2half_rn(s[p].y * (G::KAPPA * sc));
   }
 }
 
@@ -263,7 +275,7 @@ template <typename G>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512)
 spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict__ spec, int D, int R) {
   namespace cg = cooperative_groups;
-  constexpr int N = G::N, M = N / 2, Mh = M / 2, N2 = G::N2, N3 = G::N3, LGM = G::LG - 1;
+  constexpr int N = G::N, M = N / 2, Mh = M / 2, LGM = G::LG - 1;
   cg::cluster_group cluster = cg::this_cluster();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float2* s = reinterpret_cast<float2*>(smem_raw);            // local half: positions q*Mh + [0, Mh)
@@ -319,7 +331,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
   cluster.sync();
   // bin kappa of the M-point transform sits at global position rev_M(kappa): CTA = kappa & 1
   const float2* other = cluster.map_shared_rank(s, q ^ 1);
-  __half2* Gt = reinterpret_cast<__half2*>(spec + G::HDR_FLOATS) + (size_t)c * (N / 2);
+  __half* Gt = reinterpret_cast<__half*>(spec + G::HDR_FLOATS) + (size_t)c * N;
   __shared__ float red[32];
   __shared__ float cta_max;
   // two passes over this CTA's bins: the first finds the channel's largest component (combined with the
@@ -328,8 +340,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
   for (int pass = 0; pass < 2; ++pass) {
     float gmax = 0.f;
     for (int idx = tid; idx < N / 2; idx += nt) {
-      const int k3 = idx % N3, k2 = (idx / N3) % N2, k1 = idx / (N3 * N2);
-      const int k = k1 + 32 * k2 + 32 * N2 * k3;
+      const int k = table_bin<G>(idx);
       const int kap = k & (M - 1);
       if ((kap & 1) != q) continue;
       const int pk = (int)(__brev((unsigned)kap) >> (32 - LGM)) - q * Mh;
@@ -343,8 +354,13 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
       const float2 wO = make_float2(O.x * cs + O.y * sn, O.y * cs - O.x * sn);
       const float sg = (k >= M) ? -1.f : 1.f;
       const float gr = E.x + sg * wO.x, gi = E.y + sg * wO.y;
-      if (pass == 0) gmax = fmaxf(gmax, fmaxf(fabsf(gr), fabsf(gi)));
-      else Gt[idx] = __floats2half2_rn(gr * (G::KAPPA * sc), gi * (G::KAPPA * sc));
+      if (pass == 0) {
+        gmax = fmaxf(gmax, fmaxf(fabsf(gr), fabsf(gi)));
+      } else {
+        const int o = table_pos<G>(idx);
+        Gt[o] = __float2half_rn(gr * (G::KAPPA * sc));
+        Gt[o + G::N3] = __float2half_rn(gi * (G::KAPPA * sc));
+      }
     }
     if (pass == 0) {
       gmax = block_max(gmax, red);
@@ -362,6 +378,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
 struct Params {
   int B, L, D, nf, rows;
   int u_f16, yu_bf16;                               // 2-byte u holds fp16 (not bf16); round the residual conv to bf16
+  int al16;                                         // rows of xin / u / out start on 16-byte boundaries
   const __nv_bfloat16* xin; long long xsb, xsc;      // (b, channel) row start = xin + b*xsb + ch*xsc, time stride 1
   const void* u; long long usb, usc;
   __nv_bfloat16* out; long long osb, osc;
@@ -373,30 +390,89 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
   __half2 v = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ float2 unpack_h2(uint32_t u) { return __half22float2(*reinterpret_cast<__half2*>(&u)); }
 __device__ __forceinline__ float bf_lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf_hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
 __device__ __forceinline__ uint32_t pack_bf2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-__device__ __forceinline__ void sts32(uint32_t addr, uint32_t a) {
-  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(a) : "memory");
-}
-__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
-  asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
-}
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
 }
 __device__ __forceinline__ uint32_t lds32(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
   return v;
 }
-__device__ __forceinline__ float2 cmulf(float2 x, float2 w) { return make_float2(x.x * w.x - x.y * w.y, x.x * w.y + x.y * w.x); }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr));
+}
+// packed half2 arithmetic on 32-bit registers
+__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b) {
+  uint32_t d; asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d; asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ uint32_t h2_neg(uint32_t a) {
+  uint32_t d; asm("neg.f16x2 %0, %1;" : "=r"(d) : "r"(a)); return d;
+}
+__device__ __forceinline__ uint32_t h2_add(uint32_t a, uint32_t b) {
+  uint32_t d; asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b)); return d;
+}
+// (re + i im) * (tr + i ti) for two packed complex numbers
+__device__ __forceinline__ void cmul_h2(uint32_t re, uint32_t im, uint32_t tr, uint32_t ti, uint32_t& ore, uint32_t& oim) {
+  ore = h2_fma(h2_neg(im), ti, h2_mul(re, tr));
+  oim = h2_fma(re, ti, h2_mul(im, tr));
+}
+// body(g, re, im) for every group g of 8 complex columns of one TMEM row, planar: Re in columns [8g, 8g+8), Im in
+// columns [nc + 8g, ...), converted to half2 pairs.  Columns are fetched 16 complex at a time (one wait per 32
+// registers) so that the TMEM latency is paid once per batch, not once per group.
+template <int NC, typename F>
+__device__ __forceinline__ void for_each_c8(uint32_t tl, F&& body) {
+  if constexpr (NC % 16 == 0) {
+#pragma unroll
+    for (int c = 0; c < NC; c += 16) {
+      uint32_t a[16], b[16];
+      tc::tmem_ld16(tl + c, a);
+      tc::tmem_ld16(tl + NC + c, b);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t re[4], im[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          re[i] = pack_h2(__uint_as_float(a[8 * h + 2 * i]), __uint_as_float(a[8 * h + 2 * i + 1]));
+          im[i] = pack_h2(__uint_as_float(b[8 * h + 2 * i]), __uint_as_float(b[8 * h + 2 * i + 1]));
+        }
+        body(c / 8 + h, re, im);
+      }
+    }
+  } else {
+    static_assert(NC == 8, "column count");
+    uint32_t a[8], b[8];
+    tmem_ld8(tl, a);
+    tmem_ld8(tl + NC, b);
+    tc::tmem_ld_wait();
+    uint32_t re[4], im[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      re[i] = pack_h2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
+      im[i] = pack_h2(__uint_as_float(b[2 * i]), __uint_as_float(b[2 * i + 1]));
+    }
+    body(0, re, im);
+  }
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
-// depthwise 3-tap conv over 4 consecutive time steps of one channel
+// depthwise 3-tap conv taps of one channel, rounded to bf16 as autocast rounds the conv's parameters
 struct Taps { float w0, w1, w2, b; };
 __device__ __forceinline__ Taps load_taps(const float* sw, const float* sb, int ch) {
   Taps T;
@@ -404,55 +480,103 @@ __device__ __forceinline__ Taps load_taps(const float* sw, const float* sb, int 
   T.b = bf16r(__ldg(sb + ch));
   return T;
 }
-// x6 = {x[t0-2], x[t0-1], x[t0], .., x[t0+3]} -> bf16-rounded conv outputs at t0..t0+3
-__device__ __forceinline__ void conv4(const Taps& T, const float (&x6)[6], float (&y)[4]) {
+// raw words of x[t0-2 .. t0+NV-1] of a time-contiguous bf16 row (w[0] = the two steps before t0; t0 % 8 == 0 for
+// NV = 8, % 4 for NV = 4); positions outside [0, L) read as 0.  L % 4 == 0, rows 8-byte aligned (16-byte when al16).
+// Split from the unpacking so that a caller can issue the loads of several chunks before using any of them.
+template <int NV>
+__device__ __forceinline__ void load_raw(const __nv_bfloat16* row, int t0, int L, bool al16, uint32_t (&w)[NV / 2 + 1]) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) y[j] = bf16r(fmaf(T.w2, x6[j + 2], fmaf(T.w1, x6[j + 1], fmaf(T.w0, x6[j], T.b))));
+  for (int i = 0; i <= NV / 2; ++i) w[i] = 0u;
+  if (t0 < L) {
+    if (t0 >= 2) w[0] = __ldg(reinterpret_cast<const uint32_t*>(row + t0 - 2));
+    if (NV == 8 && al16 && t0 + 8 <= L) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(row + t0));
+      w[1] = v.x; w[2] = v.y; w[NV / 2 - 1] = v.z; w[NV / 2] = v.w;
+    } else {
+#pragma unroll
+      for (int q = 0; q < NV / 4; ++q)
+        if (t0 + 4 * q < L) {
+          const uint2 v = __ldg(reinterpret_cast<const uint2*>(row + t0 + 4 * q));
+          w[1 + 2 * q] = v.x; w[2 + 2 * q] = v.y;
+        }
+    }
+  }
 }
-// loads x[t0-2 .. t0+3] of a time-contiguous bf16 row (t0 % 4 == 0); positions outside [0, L) read as 0
-__device__ __forceinline__ void load6(const __nv_bfloat16* row, int t0, int L, float (&x6)[6]) {
-  uint32_t h = 0;
-  uint2 v = make_uint2(0u, 0u);
-  if (t0 >= 2 && t0 - 2 < L) h = __ldg(reinterpret_cast<const uint32_t*>(row + t0 - 2));
-  if (t0 < L) v = __ldg(reinterpret_cast<const uint2*>(row + t0));
-  x6[0] = bf_lo(h); x6[1] = bf_hi(h);
-  x6[2] = bf_lo(v.x); x6[3] = bf_hi(v.x); x6[4] = bf_lo(v.y); x6[5] = bf_hi(v.y);
+template <int NV>
+__device__ __forceinline__ void unpack_raw(const uint32_t (&w)[NV / 2 + 1], float (&x)[NV + 2]) {
+#pragma unroll
+  for (int i = 0; i <= NV / 2; ++i) { x[2 * i] = bf_lo(w[i]); x[2 * i + 1] = bf_hi(w[i]); }
 }
+// The depthwise 3-tap conv on NV consecutive steps from the raw words of load_raw, two outputs per packed float32
+// FMA: out[p] = bf16x2 of (y[2p], y[2p+1]), y[t] = b + w0 x[t-2] + w1 x[t-1] + w2 x[t] accumulated in float32 and
+// rounded to bf16 once, as the reference's conv1d under autocast.
+struct Taps2 { f32x2 w0, w1, w2, b; };
+__device__ __forceinline__ Taps2 load_taps2(const float* sw, const float* sb, int ch) {
+  const Taps T = load_taps(sw, sb, ch);
+  Taps2 P;
+  P.w0 = f2_splat(T.w0); P.w1 = f2_splat(T.w1); P.w2 = f2_splat(T.w2); P.b = f2_splat(T.b);
+  return P;
+}
+template <int NV>
+__device__ __forceinline__ void conv_packed(const Taps2& T, const uint32_t (&w)[NV / 2 + 1], uint32_t (&out)[NV / 2]) {
+  float f[NV + 2];
+  unpack_raw<NV>(w, f);
+#pragma unroll
+  for (int p = 0; p < NV / 2; ++p) {
+    f32x2 acc = f2_fma(f2_pack(f[2 * p], f[2 * p + 1]), T.w0, T.b);
+    acc = f2_fma(f2_pack(f[2 * p + 1], f[2 * p + 2]), T.w1, acc);
+    acc = f2_fma(f2_pack(f[2 * p + 2], f[2 * p + 3]), T.w2, acc);
+    float lo, hi;
+    f2_unpack(acc, lo, hi);
+    out[p] = pack_bf2(lo, hi);
+  }
+}
+// bf16x2 -> fp16x2 (exact for values inside fp16's range)
+__device__ __forceinline__ uint32_t bf2_to_h2(uint32_t v) { return pack_h2(bf_lo(v), bf_hi(v)); }
 
-// MMAs of one stage: 0 F1, 1 DFT_N2, 2 DFT_N3, 3 DFT_N3 (on conjugated data = inverse),
-// 4 DFT_N2 (inverse), 5 I1
+// MMAs of one stage: 0 F1, 1 DFT_N2, 2 DFT_N3, 3 DFT_N3 on conjugated data (= inverse), 4 DFT_N2 (inverse), 5 I1.
+// A operands: MN-major (row groups `sbo` apart, K core matrices 128 bytes apart) except stage 3 (K-major rows).
 template <typename G>
 __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t data, uint32_t hdr) {
   constexpr int K2 = G::K2, K3 = G::K3;
   if (stage == 0) {
-    constexpr uint32_t id = tc::make_idesc(128, 32, 0);
+    constexpr uint32_t id = tc::make_idesc_major(128, 32, 0, 1, 0);
     const uint64_t dB = tc::smem_desc_k_nosw(hdr + G::F1_OFF, 128, 16 * 16);
 #pragma unroll
-    for (int t = 0; t < G::TR; ++t)
-      tc::mma_ss(tm + 32 * t, tc::smem_desc_k_nosw(data + t * G::A1_TILE, G::A1_LBO, G::A1_SBO), dB, id, 0);
+    for (int t = 0; t < G::T1T; ++t)
+      tc::mma_ss(tm + 32 * t, tc::smem_desc_k_nosw(data + t * 16 * G::SBO1, 128, G::SBO1), dB, id, 0);
   } else if (stage == 1 || stage == 4) {
-    constexpr uint32_t id = tc::make_idesc(128, K2, 0);
+    constexpr uint32_t id = tc::make_idesc_major(128, K2, 0, 1, 0);
+    const uint32_t sbo = stage == 1 ? G::SBO2 : G::SBO4;
 #pragma unroll
     for (int t = 0; t < G::T2T; ++t)
 #pragma unroll
       for (int s = 0; s < K2 / 16; ++s)
-        tc::mma_ss(tm + K2 * t, tc::smem_desc_k_nosw(data + t * G::A2_TILE + s * 2 * G::A2_LBO, G::A2_LBO, G::A2_SBO),
+        tc::mma_ss(tm + K2 * t, tc::smem_desc_k_nosw(data + t * 16 * sbo + s * 256, 128, sbo),
                    tc::smem_desc_k_nosw(hdr + G::F2_OFF + s * 256, 128, K2 * 16), id, s ? 1u : 0u);
-  } else if (stage == 2 || stage == 3) {
+  } else if (stage == 2) {
+    constexpr uint32_t id = tc::make_idesc_major(128, K3, 0, 1, 0);
+#pragma unroll
+    for (int t = 0; t < G::T3T; ++t)
+#pragma unroll
+      for (int s = 0; s < K3 / 16; ++s)
+        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * 16 * G::SBO3 + s * 256, 128, G::SBO3),
+                   tc::smem_desc_k_nosw(hdr + G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
+  } else if (stage == 3) {
     constexpr uint32_t id = tc::make_idesc(128, K3, 0);
 #pragma unroll
     for (int t = 0; t < G::T3T; ++t)
 #pragma unroll
       for (int s = 0; s < K3 / 16; ++s)
-        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * G::A3_TILE + s * 2 * G::A3_LBO, G::A3_LBO, G::A3_SBO),
+        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * G::TILE3 + s * 256, 128, G::SBO3K),
                    tc::smem_desc_k_nosw(hdr + G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
   } else {
-    constexpr uint32_t id = tc::make_idesc(128, 16, 0);
+    constexpr uint32_t id = tc::make_idesc_major(128, 16, 0, 1, 0);
 #pragma unroll
-    for (int t = 0; t < G::TR; ++t)
+    for (int t = 0; t < G::T1T; ++t)
 #pragma unroll
       for (int s = 0; s < 2; ++s)
-        tc::mma_ss(tm + 16 * t, tc::smem_desc_k_nosw(data + t * G::A6_TILE + s * 2 * G::A6_LBO, G::A6_LBO, G::A6_SBO),
+        tc::mma_ss(tm + 16 * t, tc::smem_desc_k_nosw(data + t * 16 * G::SBO5 + s * 256, 128, G::SBO5),
                    tc::smem_desc_k_nosw(hdr + G::I1_OFF + s * 256, 128, 32 * 16), id, s ? 1u : 0u);
   }
 }
@@ -461,11 +585,11 @@ template <typename G, typename TU>
 __global__ void __launch_bounds__(G::THREADS, 1)
 longconv_tcl_kernel(const Params P) {
   constexpr int N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3, TS = G::TS, TPS = G::TPS;
-  constexpr int CH = R / 4;                                  // 4-wide time chunks per n1 block
-  constexpr int GROUPS = (TPS > CH) ? TPS / CH : 1;          // n1 groups when a slot has more threads than chunks
-  constexpr int NP = 16 / GROUPS;                            // n1 values per thread and chunk in the load / store phases
-  constexpr int CPT = (CH > TPS) ? CH / TPS : 1;             // chunks per thread
-  static_assert(NP >= 4 && NP % 4 == 0, "n1 group must be a multiple of 4");
+  constexpr int LIT = 2 * R / TPS;                 // 8-step chunks per thread in the load phase
+  constexpr int LB = LIT < 4 ? LIT : 4;            // ... of which this many have their global loads in flight together
+  constexpr int EIT = 4 * R / TPS;                 // 4-step chunks per thread in the epilogue
+  constexpr int EB = EIT < 8 ? EIT : 8;
+  static_assert(LIT % LB == 0 && EIT % EB == 0, "batching of the memory phases");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
   unsigned char* hdrb = smem + G::SLOTS * G::DATA_BYTES;
@@ -473,7 +597,7 @@ longconv_tcl_kernel(const Params P) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * G::SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int slot = tid / TPS;
   const int sl = tid % TPS;                      // thread index inside the slot
   const int l = sl & 127;                        // TMEM lane = row within every 128-row tile
@@ -508,8 +632,6 @@ longconv_tcl_kernel(const Params P) {
   const uint32_t data = tc::smem_u32(smem + slot * G::DATA_BYTES);
   float* Y = reinterpret_cast<float*>(smem + slot * G::DATA_BYTES);
   const uint32_t hdr = tc::smem_u32(hdrb);
-  const uint32_t t1s = hdr + G::T1_OFF, t2a = hdr + G::T2A_OFF, t2b = hdr + G::T2B_OFF;
-  const uint32_t lrow = (uint32_t)((l >> 3) * 1 /* x SBO */), lsub = (uint32_t)((l & 7) * 16);
   uint32_t ph_ops = 0, ph_mma = 0, ph_w = 0;
   bool ok = true;
 
@@ -532,269 +654,327 @@ longconv_tcl_kernel(const Params P) {
   if (!__all_sync(0xffffffffu, tc::mbar_wait(bar_w, ph_w, abort_flag, tc::ST_TIMEOUT_EPI))) { ok = false; break; } \
   ph_w ^= 1;
 
-  for (int rowid = blockIdx.x * G::SLOTS + slot; rowid < P.rows && ok; rowid += gridDim.x * G::SLOTS) {
-    const int ch = rowid % P.D, b = rowid / P.D;
+  // position of chunk q of the load phase: a warp covers 8 n1 x 4 row groups -- 64 contiguous bytes per n1 from
+  // global memory, and each quarter warp fills one 128-byte core matrix of the F1 operand
+  auto chunk_of = [&](int q, int& n1, int& rg) {
+    n1 = ((q >> 5) & 1) * 8 + (q & 7);
+    rg = (q >> 6) * 4 + ((q >> 3) & 3);
+  };
+  const int stride = gridDim.x * G::SLOTS;
+  // rows of one channel are neighbours in the walk (batch index fastest): the slots working at the same time share
+  // a few channels' spectrum tables, which then come from L2
+  for (int rowid = blockIdx.x * G::SLOTS + slot; rowid < P.rows && ok; rowid += stride) {
+    const int ch = rowid / P.B, b = rowid % P.B;
     const __nv_bfloat16* x1row = P.xin + (long long)b * P.xsb + (long long)ch * P.xsc;
     const __nv_bfloat16* x2row = x1row + (long long)P.D * P.xsc;
     const __nv_bfloat16* vrow = x2row + (long long)P.D * P.xsc;
     __nv_bfloat16* orow = P.out + (long long)b * P.osb + (long long)ch * P.osc;
     const TU* urow = reinterpret_cast<const TU*>(P.u) + (long long)b * P.usb + (long long)ch * P.usc;
+    if (rowid + stride < P.rows) {
+      // the next sequence of this slot: ask for its rows now, they are in L2 when its turn comes
+      const int nr = rowid + stride, nch = nr / P.B, nb = nr % P.B;
+      const __nv_bfloat16* nx = P.xin + (long long)nb * P.xsb + (long long)nch * P.xsc;
+      const unsigned char* nu = reinterpret_cast<const unsigned char*>(reinterpret_cast<const TU*>(P.u) + (long long)nb * P.usb + (long long)nch * P.usc);
+      for (int o = sl * 64; o < P.L; o += TPS * 64) {                      // 128-byte lines of the bf16 rows
+        prefetch_l2(nx + o);
+        prefetch_l2(nx + (long long)P.D * P.xsc + o);
+        prefetch_l2(nx + 2 * (long long)P.D * P.xsc + o);
+      }
+      if (P.nf == 2)
+        for (int o = sl * 128; o < P.L * (int)sizeof(TU); o += TPS * 128) prefetch_l2(nu + o);
+    }
 
     for (int f = 0; f < P.nf && ok; ++f) {
-      // ---------------- F1 operands: a[R n1 + r] as fp16 at (row r, k = n1) ----------------
+      // ---------------- F1 operand: a[R n1 + r] as fp16, one 16-byte chunk = 8 consecutive r of one n1 ----------------
+      if (f == 0) {
+        const Taps2 Tx = load_taps2(P.sw, P.sb, ch), Tv = load_taps2(P.sw, P.sb, 2 * P.D + ch);
 #pragma unroll 1
-      for (int cc = 0; cc < CPT; ++cc) {
-        const int pc = (sl % CH) + cc * TPS, pg = (CH >= TPS) ? 0 : sl / CH;
-        const int r0 = 4 * pc, n1_0 = pg * NP;
-        uint32_t hv[4][NP / 2];                              // [j = r - r0][n1 pair]
-        if (f == 0) {
-          const Taps Tx = load_taps(P.sw, P.sb, ch), Tv = load_taps(P.sw, P.sb, 2 * P.D + ch);
+        for (int it0 = 0; it0 < LIT; it0 += LB) {
+          uint32_t xr[LB][5], vr[LB][5];
 #pragma unroll
-          for (int i = 0; i < NP; i += 2) {
-            float a[2][4];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int t0 = R * (n1_0 + i + e) + r0;
-              float x6[6], v6[6], cx[4], cv[4];
-              load6(x1row, t0, P.L, x6);
-              load6(vrow, t0, P.L, v6);
-              conv4(Tx, x6, cx);
-              conv4(Tv, v6, cv);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) a[e][j] = (t0 < P.L) ? bf16r(cv[j] * cx[j]) : 0.f;
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) hv[j][i >> 1] = pack_h2(a[0][j], a[1][j]);
+          for (int i = 0; i < LB; ++i) {
+            int n1, rg;
+            chunk_of((it0 + i) * TPS + sl, n1, rg);
+            load_raw<8>(x1row, R * n1 + 8 * rg, P.L, P.al16, xr[i]);
+            load_raw<8>(vrow, R * n1 + 8 * rg, P.L, P.al16, vr[i]);
           }
-        } else {
 #pragma unroll
-          for (int i = 0; i < NP; i += 2) {
-            float a[2][4];
+          for (int i = 0; i < LB; ++i) {
+            int n1, rg;
+            chunk_of((it0 + i) * TPS + sl, n1, rg);
+            const int t0 = R * n1 + 8 * rg;
+            uint32_t cx[4], cv[4], h[4];
+            conv_packed<8>(Tx, xr[i], cx);
+            conv_packed<8>(Tv, vr[i], cv);
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int t0 = R * (n1_0 + i + e) + r0;
-              a[e][0] = a[e][1] = a[e][2] = a[e][3] = 0.f;
-              if (t0 < P.L) {
-                if (sizeof(TU) == 4) {
-                  const float4 v = __ldg(reinterpret_cast<const float4*>(urow + t0));
-                  a[e][0] = v.x; a[e][1] = v.y; a[e][2] = v.z; a[e][3] = v.w;
-                } else {
-                  const uint2 v = __ldg(reinterpret_cast<const uint2*>(urow + t0));
-                  if (P.u_f16) {
-                    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&v.x));
-                    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&v.y));
-                    a[e][0] = lo.x; a[e][1] = lo.y; a[e][2] = hi.x; a[e][3] = hi.y;
-                  } else {
-                    a[e][0] = bf_lo(v.x); a[e][1] = bf_hi(v.x); a[e][2] = bf_lo(v.y); a[e][3] = bf_hi(v.y);
-                  }
-                }
+            for (int j = 0; j < 4; ++j) h[j] = bf2_to_h2(bf2_mul(cv[j], cx[j]));     // v * x1: the exact product, rounded to bf16
+            if (t0 + 8 > P.L) {                                                     // steps at and beyond L are zero padding
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (t0 + 2 * j >= P.L) h[j] = 0u;
+                else if (t0 + 2 * j + 1 >= P.L) h[j] &= 0xffffu;
               }
             }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) hv[j][i >> 1] = pack_h2(a[0][j], a[1][j]);
+            sts128(data + rg * G::SBO1 + n1 * 16, h[0], h[1], h[2], h[3]);
           }
         }
+      } else {
+#pragma unroll 1
+        for (int it0 = 0; it0 < LIT; it0 += LB) {
+          uint32_t w[LB][sizeof(TU) == 4 ? 8 : 4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = r0 + j;
-          const uint32_t ro = data + (r >> 7) * G::A1_TILE + ((r & 127) >> 3) * G::A1_SBO + (r & 7) * 16;
+          for (int i = 0; i < LB; ++i) {
+            int n1, rg;
+            chunk_of((it0 + i) * TPS + sl, n1, rg);
+            const int t0 = R * n1 + 8 * rg;
 #pragma unroll
-          for (int q = 0; q < NP / 4; ++q) {
-            const int k = n1_0 + 4 * q;
-            sts64(ro + (k >> 3) * G::A1_LBO + (k & 7) * 2, hv[j][2 * q], hv[j][2 * q + 1]);
+            for (int j = 0; j < (sizeof(TU) == 4 ? 8 : 4); ++j) w[i][j] = 0u;
+            if (sizeof(TU) == 4) {
+#pragma unroll
+              for (int q4 = 0; q4 < 2; ++q4)
+                if (t0 + 4 * q4 < P.L) {
+                  const uint4 v = __ldg(reinterpret_cast<const uint4*>(urow + t0 + 4 * q4));
+                  w[i][4 * q4] = v.x; w[i][4 * q4 + 1] = v.y; w[i][4 * q4 + 2] = v.z; w[i][4 * q4 + 3] = v.w;
+                }
+            } else if (P.al16 && t0 + 8 <= P.L) {
+              const uint4 v = __ldg(reinterpret_cast<const uint4*>(urow + t0));
+              w[i][0] = v.x; w[i][1] = v.y; w[i][2] = v.z; w[i][3] = v.w;
+            } else {
+#pragma unroll
+              for (int q4 = 0; q4 < 2; ++q4)
+                if (t0 + 4 * q4 < P.L) {
+                  const uint2 v = __ldg(reinterpret_cast<const uint2*>(urow + t0 + 4 * q4));
+                  w[i][2 * q4] = v.x; w[i][2 * q4 + 1] = v.y;
+                }
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < LB; ++i) {
+            int n1, rg;
+            chunk_of((it0 + i) * TPS + sl, n1, rg);
+            uint32_t h[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (sizeof(TU) == 4) h[j] = pack_h2(__uint_as_float(w[i][2 * j]), __uint_as_float(w[i][2 * j + 1]));
+              else h[j] = P.u_f16 ? w[i][j] : pack_h2(bf_lo(w[i][j]), bf_hi(w[i][j]));
+            }
+            sts128(data + rg * G::SBO1 + n1 * 16, h[0], h[1], h[2], h[3]);
           }
         }
       }
       LCL_STAGE(0)
 
-      // ---------------- hop 1: x T1, rows (n2, n3) -> rows (k1, n3), k = (n2, ri) ----------------
+      // ---------------- hop 1: x w^{r (k1 + 1/2)}; rows r = (n2, n3) -> operand rows (k1, n3), K = (ri, n2) ----------------
 #pragma unroll 1
-      for (int t = ts; t < G::TR; t += TS) {
+      for (int t = ts; t < G::T1T; t += TS) {
         const int r = 128 * t + l, n2 = r / N3, n3 = r % N3;
-        // thread part of the destination: row group / row of n3, K position of n2
-        const uint32_t dst = data + (n3 >> 3) * G::A2_SBO + (n3 & 7) * 16 + (n2 >> 2) * G::A2_LBO + (n2 & 3) * 4;
-        const uint32_t tw = G::SPLIT_T1 ? 0u : t1s + r * 4;
+        const uint32_t ta = hdr + G::TA1_OFF + n2 * 64, tb = hdr + G::TB1_OFF + n3 * G::TB1_PITCH;
+        const uint32_t dst = data + n3 * G::SBO2 + (n2 >> 3) * 128 + (n2 & 7) * 16;
+        for_each_c8<16>(tml + 32 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k1 = 8 g ..
+          const uint4 ar = lds128(ta + 16 * g), ai = lds128(ta + 32 + 16 * g);
+          const uint4 br = lds128(tb + 16 * g), bi = lds128(tb + 32 + 16 * g);
+          const uint32_t arr[4] = {ar.x, ar.y, ar.z, ar.w}, aii[4] = {ai.x, ai.y, ai.z, ai.w};
+          const uint32_t brr[4] = {br.x, br.y, br.z, br.w}, bii[4] = {bi.x, bi.y, bi.z, bi.w};
+          uint32_t orr[4], oi[4];
 #pragma unroll
-        for (int hq = 0; hq < 2; ++hq) {
-          uint32_t z[16];
-          tc::tmem_ld16(tml + 32 * t + 16 * hq, z);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            constexpr int KPT = 128 / N3;                    // k1 values per 128-row tile of the destination
-            const int k1 = 8 * hq + kk;
-            float2 w;
-            if (G::SPLIT_T1) w = cmulf(unpack_h2(lds32(t1s + (k1 * N2 + n2) * 4)), unpack_h2(lds32(t1s + (16 * N2 + k1 * N3 + n3) * 4)));
-            else w = unpack_h2(lds32(tw + k1 * R * 4));
-            const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(dst + (k1 / KPT) * G::A2_TILE + (k1 % KPT) * G::G3 * G::A2_SBO, pack_h2(y.x, y.y));
+          for (int i = 0; i < 4; ++i) {
+            uint32_t wr, wi;
+            cmul_h2(arr[i], aii[i], brr[i], bii[i], wr, wi);
+            cmul_h2(re[i], im[i], wr, wi, orr[i], oi[i]);
           }
-        }
+          const uint32_t d = dst + g * N3 * G::SBO2;              // row group j = k1hi N3 + n3
+          sts128(d, orr[0], orr[1], orr[2], orr[3]);
+          sts128(d + (N2 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);   // K index N2 + n2: the imaginary plane
+        });
       }
       tc::tc_fence_before();
       LCL_STAGE(1)
 
-      // ---------------- hop 2: x T2, rows (k1, n3) -> rows (k1, k2), k = (n3, ri) ----------------
+      // ---------------- hop 2: x w^{32 n3 k2}; rows (k1, n3) -> operand rows (k1, k2), K = (ri, n3) ----------------
 #pragma unroll 1
       for (int t = ts; t < G::T2T; t += TS) {
-        constexpr int KPT = 128 / N2 > 0 ? 128 / N2 : 1;     // k1 values per 128-row tile of the destination (N2 <= 128)
-        const int rho = 128 * t + l, k1 = rho / N3, n3 = rho % N3;
-        const uint32_t dst = data + (k1 / KPT) * G::A3_TILE + (k1 % KPT) * G::G2 * G::A3_SBO +
-                             (n3 >> 2) * G::A3_LBO + (n3 & 3) * 4;
-        const uint32_t tw = t2a + n3 * 4;
+        const int j = 16 * t + (l >> 3), k1 = 8 * (j / N3) + (l & 7), n3 = j % N3;
+        const uint32_t tw = hdr + G::T2A_OFF + n3 * (K2 * 2);
+        const uint32_t dst = data + k1 * G::SBO3 + (n3 >> 3) * 128 + (n3 & 7) * 16;
+        for_each_c8<N2>(tml + K2 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k2 = 8 g ..
+          const uint4 wr4 = lds128(tw + 16 * g), wi4 = lds128(tw + N2 * 2 + 16 * g);
+          const uint32_t wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w}, wi[4] = {wi4.x, wi4.y, wi4.z, wi4.w};
+          uint32_t orr[4], oi[4];
 #pragma unroll
-        for (int c0 = 0; c0 < K2; c0 += 16) {
-          uint32_t z[16];
-          tc::tmem_ld16(tml + K2 * t + c0, z);
-          tc::tmem_ld_wait();
+          for (int i = 0; i < 4; ++i) cmul_h2(re[i], im[i], wr[i], wi[i], orr[i], oi[i]);
+          const uint32_t d = dst + g * 16 * G::SBO3;              // row group j3 = k2hi 16 + k1
+          sts128(d, orr[0], orr[1], orr[2], orr[3]);
+          sts128(d + (N3 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
+        });
+      }
+      // this row's slice of the spectrum comes from global memory (L2 for all but the first sequence of a channel):
+      // the first tile's slice is requested before the wait for stage 2's MMAs, every further tile's while the
+      // one before it is being multiplied (when the slices of two tiles fit the register budget)
+      constexpr int NG = K3 / 8;
+      const __half* Gc = reinterpret_cast<const __half*>(P.spec[f] + G::HDR_FLOATS) + (size_t)ch * G::N;
+      uint4 gv[NG];
+      {
+        const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)(ts * 128 + l) * K3);
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const int k2 = c0 / 2 + kk;
-            const float2 w = unpack_h2(lds32(tw + k2 * N3 * 4));
-            const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(dst + (k2 >> 3) * G::A3_SBO + (k2 & 7) * 16, pack_h2(y.x, y.y));
-          }
-        }
+        for (int i = 0; i < NG; ++i) gv[i] = __ldg(gp + i);
       }
       tc::tc_fence_before();
       LCL_STAGE(2)
 
-      // ---------------- hop 3: conj(Z (G + bias)); rows (k1, k2) keep their place, k = (k3, ri) ----------------
+      // ---------------- hop 3: conj(Z (G + bias)); rows (k1, k2) keep their place (K-major), K = (ri, k3) ----------------
       {
-        const uint32_t* Gt = reinterpret_cast<const uint32_t*>(P.spec[f] + G::HDR_FLOATS) + (size_t)ch * (G::N / 2);
         const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);   // 2^-e of this channel
-        const float bk = __ldg(P.bias[f] + ch) * G::KAPPA / inv_gain;
+        const float bkf = __ldg(P.bias[f] + ch) * G::KAPPA / inv_gain;
+        const uint32_t bk = pack_h2(bkf, bkf);
 #pragma unroll 1
         for (int t = ts; t < G::T3T; t += TS) {
-          const int rho = 128 * t + l;
-          const uint32_t dst = data + t * G::A3_TILE + (l >> 3) * G::A3_SBO + (l & 7) * 16;
+          uint4 gn[NG <= 4 ? NG : 1];
+          if (NG <= 4 && t + TS < G::T3T) {
+            const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)((t + TS) * 128 + l) * K3);
 #pragma unroll
-          for (int c0 = 0; c0 < K3; c0 += 16) {
-            uint32_t z[16];
-            tc::tmem_ld16(tml + K3 * t + c0, z);
-            const uint4 g0 = __ldg(reinterpret_cast<const uint4*>(Gt + rho * N3 + c0 / 2));
-            const uint4 g1 = __ldg(reinterpret_cast<const uint4*>(Gt + rho * N3 + c0 / 2 + 4));
-            tc::tmem_ld_wait();
-            const uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            uint32_t o[8];
+            for (int i = 0; i < (NG <= 4 ? NG : 1); ++i) gn[i] = __ldg(gp + i);
+          }
+          const uint32_t dst = data + t * G::TILE3 + (l >> 3) * G::SBO3K + (l & 7) * 16;
+          for_each_c8<N3>(tml + K3 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {  // k3 = 8 g ..
+            const uint32_t gr[4] = {gv[g].x, gv[g].y, gv[g].z, gv[g].w};
+            const uint32_t gi[4] = {gv[N3 / 8 + g].x, gv[N3 / 8 + g].y, gv[N3 / 8 + g].z, gv[N3 / 8 + g].w};
+            uint32_t orr[4], oi[4];
 #pragma unroll
-            for (int kk = 0; kk < 8; ++kk) {
-              float2 g = unpack_h2(gw[kk]);
-              g.x += bk;
-              const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), g);
-              o[kk] = pack_h2(y.x, -y.y);
+            for (int i = 0; i < 4; ++i) {
+              cmul_h2(re[i], im[i], h2_add(gr[i], bk), gi[i], orr[i], oi[i]);
+              oi[i] = h2_neg(oi[i]);
             }
-            sts128(dst + (c0 >> 3) * G::A3_LBO, o[0], o[1], o[2], o[3]);
-            sts128(dst + ((c0 >> 3) + 1) * G::A3_LBO, o[4], o[5], o[6], o[7]);
+            sts128(dst + g * 128, orr[0], orr[1], orr[2], orr[3]);
+            sts128(dst + (N3 / 8 + g) * 128, oi[0], oi[1], oi[2], oi[3]);
+          });
+          if (t + TS < G::T3T) {
+            if (NG <= 4) {
+#pragma unroll
+              for (int i = 0; i < (NG <= 4 ? NG : 1); ++i) gv[i] = gn[i];
+            } else {
+              const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)((t + TS) * 128 + l) * K3);
+#pragma unroll
+              for (int i = 0; i < NG; ++i) gv[i] = __ldg(gp + i);
+            }
           }
         }
       }
       tc::tc_fence_before();
       LCL_STAGE(3)
 
-      // ---------------- hop 4: x T2, rows (k1, k2) -> rows (k1, n3), k = (k2, ri) ----------------
+      // ---------------- hop 4: x w^{32 n3 k2}; rows (k1, k2) -> operand rows (k1, n3), K = (ri, k2) ----------------
 #pragma unroll 1
       for (int t = ts; t < G::T3T; t += TS) {
-        constexpr int KPT = 128 / N3;
-        const int rho = 128 * t + l, k1 = rho / N2, k2 = rho % N2;
-        const uint32_t dst = data + (k1 / KPT) * G::A2_TILE + (k1 % KPT) * G::G3 * G::A2_SBO +
-                             (k2 >> 2) * G::A2_LBO + (k2 & 3) * 4;
-        const uint32_t tw = t2b + k2 * 4;
+        const int k1 = l >> 3, k2 = 8 * t + (l & 7);
+        const uint32_t tw = hdr + G::T2B_OFF + k2 * G::T2B_PITCH;
+        const uint32_t dst = data + k1 * G::SBO4 + (k2 >> 3) * 128 + (k2 & 7) * 16;
+        for_each_c8<N3>(tml + K3 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // n3 = 8 g ..
+          const uint4 wr4 = lds128(tw + 16 * g), wi4 = lds128(tw + N3 * 2 + 16 * g);
+          const uint32_t wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w}, wi[4] = {wi4.x, wi4.y, wi4.z, wi4.w};
+          uint32_t orr[4], oi[4];
 #pragma unroll
-        for (int c0 = 0; c0 < K3; c0 += 16) {
-          uint32_t z[16];
-          tc::tmem_ld16(tml + K3 * t + c0, z);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const int n3 = c0 / 2 + kk;
-            const float2 w = unpack_h2(lds32(tw + n3 * N2 * 4));
-            const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(dst + (n3 >> 3) * G::A2_SBO + (n3 & 7) * 16, pack_h2(y.x, y.y));
-          }
-        }
+          for (int i = 0; i < 4; ++i) cmul_h2(re[i], im[i], wr[i], wi[i], orr[i], oi[i]);
+          const uint32_t d = dst + g * 16 * G::SBO4;              // row group j4 = n3hi 16 + k1
+          sts128(d, orr[0], orr[1], orr[2], orr[3]);
+          sts128(d + (N2 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
+        });
       }
       tc::tc_fence_before();
       LCL_STAGE(4)
 
-      // ---------------- hop 5: x T1, rows (k1, n3) -> rows r = (n2, n3), k = (k1, ri) ----------------
+      // ---------------- hop 5: x w^{r (k1 + 1/2)}; rows (k1, n3) -> operand rows r = (n2, n3), K = (ri, k1) ----------------
 #pragma unroll 1
       for (int t = ts; t < G::T2T; t += TS) {
-        constexpr int NPT = 128 / N3;                        // n2 values per 128-row tile of the destination
-        const int rho = 128 * t + l, k1 = rho / N3, n3 = rho % N3;
-        const uint32_t dst = data + (n3 >> 3) * G::A6_SBO + (n3 & 7) * 16 + (k1 >> 2) * G::A6_LBO + (k1 & 3) * 4;
-        const uint32_t tw = G::SPLIT_T1 ? t1s + (k1 * N2) * 4 : t1s + (k1 * R + n3) * 4;
-        float2 wb = make_float2(1.f, 0.f);
-        if (G::SPLIT_T1) wb = unpack_h2(lds32(t1s + (16 * N2 + k1 * N3 + n3) * 4));
+        const int k1 = l >> 3, n3 = 8 * t + (l & 7);
+        const uint32_t ta = hdr + G::TA5_OFF + k1 * (K2 * 2);
+        const uint32_t tbs = lds32(hdr + G::TB5_OFF + (k1 * N3 + n3) * 4);          // (Re, Im) of the n3 part
+        const uint32_t tbr = __byte_perm(tbs, tbs, 0x1010), tbi = __byte_perm(tbs, tbs, 0x3232);
+        const uint32_t dst = data + n3 * G::SBO5 + (k1 >> 3) * 128 + (k1 & 7) * 16;
+        for_each_c8<N2>(tml + K2 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // n2 = 8 g ..
+          const uint4 ar4 = lds128(ta + 16 * g), ai4 = lds128(ta + N2 * 2 + 16 * g);
+          const uint32_t ar[4] = {ar4.x, ar4.y, ar4.z, ar4.w}, ai[4] = {ai4.x, ai4.y, ai4.z, ai4.w};
+          uint32_t orr[4], oi[4];
 #pragma unroll
-        for (int c0 = 0; c0 < K2; c0 += 16) {
-          uint32_t z[16];
-          tc::tmem_ld16(tml + K2 * t + c0, z);
-          tc::tmem_ld_wait();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const int n2 = c0 / 2 + kk;
-            float2 w;
-            if (G::SPLIT_T1) w = cmulf(unpack_h2(lds32(tw + n2 * 4)), wb);
-            else w = unpack_h2(lds32(tw + n2 * N3 * 4));
-            const float2 y = cmulf(make_float2(__uint_as_float(z[2 * kk]), __uint_as_float(z[2 * kk + 1])), w);
-            sts32(dst + (n2 / NPT) * G::A6_TILE + (n2 % NPT) * G::G3 * G::A6_SBO, pack_h2(y.x, y.y));
+          for (int i = 0; i < 4; ++i) {
+            uint32_t wr, wi;
+            cmul_h2(ar[i], ai[i], tbr, tbi, wr, wi);
+            cmul_h2(re[i], im[i], wr, wi, orr[i], oi[i]);
           }
-        }
+          const uint32_t d = dst + g * N3 * G::SBO5;              // row group j5 = n2hi N3 + n3
+          sts128(d, orr[0], orr[1], orr[2], orr[3]);
+          sts128(d + 2 * 128, oi[0], oi[1], oi[2], oi[3]);          // K index 16 + k1
+        });
       }
       tc::tc_fence_before();
       LCL_STAGE(5)
 
-      // ---------------- hop 6: y[R n1 + r] (float32) into shared memory in time order ----------------
+      // ---------------- hop 6: y[R n1 + r] (float32) into shared memory in time order, 4 floats of padding after every 32
+      // (position t lives at t + 4 (t / 32): the scattered writes below and the float4 reads of the epilogue are both
+      // free of bank conflicts) ----------------
 #pragma unroll 1
-      for (int t = ts; t < G::TR; t += TS) {
+      for (int t = ts; t < G::T1T; t += TS) {
         uint32_t z[16];
         tc::tmem_ld16(tml + 16 * t, z);
         tc::tmem_ld_wait();
+        const int j5 = 16 * t + (l >> 3), n2 = 8 * (j5 / N3) + (l & 7), n3 = j5 % N3;
+        const int r = N3 * n2 + n3;
+        float* yp = Y + r + 4 * (r >> 5);
 #pragma unroll
-        for (int n1 = 0; n1 < 16; ++n1) Y[R * n1 + 128 * t + l] = __uint_as_float(z[n1]);
+        for (int n1 = 0; n1 < 16; ++n1) yp[n1 * (R + R / 8)] = __uint_as_float(z[n1]);
       }
       tc::tc_fence_before();
       LCL_BARRIER()
 
       // ---------------- epilogue: gate / residual add; 8-byte stores along time ----------------
       const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);     // undo the table's 2^e
+      const f32x2 gain2 = f2_splat(inv_gain);
+      if (f == 0) {
+        const Taps2 T2 = load_taps2(P.sw, P.sb, P.D + ch);
 #pragma unroll 1
-      for (int cc = 0; cc < CPT; ++cc) {
-        const int pc = (sl % CH) + cc * TPS, pg = (CH >= TPS) ? 0 : sl / CH;
-        const int r0 = 4 * pc, n1_0 = pg * NP;
-        if (f == 0) {
-          const Taps T2 = load_taps(P.sw, P.sb, P.D + ch);
+        for (int it0 = 0; it0 < EIT; it0 += EB) {
+          uint32_t xr[EB][3];
 #pragma unroll
-          for (int i = 0; i < NP; ++i) {
-            const int t0 = R * (n1_0 + i) + r0;
+          for (int i = 0; i < EB; ++i) load_raw<4>(x2row, 4 * ((it0 + i) * TPS + sl), P.L, false, xr[i]);
+#pragma unroll
+          for (int i = 0; i < EB; ++i) {
+            const int t0 = 4 * ((it0 + i) * TPS + sl);
             if (t0 < P.L) {
-              float x6[6], c2[4];
-              load6(x2row, t0, P.L, x6);
-              conv4(T2, x6, c2);
-              const float4 y = *reinterpret_cast<const float4*>(Y + t0);
-              const float yv[4] = {y.x * inv_gain, y.y * inv_gain, y.z * inv_gain, y.w * inv_gain};
-              float o[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) o[j] = bf16r(yv[j]) * c2[j];      // (conv + bias term) cast, then the gate
-              *reinterpret_cast<uint2*>(orow + t0) = make_uint2(pack_bf2(o[0], o[1]), pack_bf2(o[2], o[3]));
+              uint32_t c2[2], o[2];
+              conv_packed<4>(T2, xr[i], c2);
+              const float4 y = *reinterpret_cast<const float4*>(Y + t0 + 4 * (t0 >> 5));
+              float a0, a1, a2, a3;
+              f2_unpack(f2_mul(f2_pack(y.x, y.y), gain2), a0, a1);
+              f2_unpack(f2_mul(f2_pack(y.z, y.w), gain2), a2, a3);
+              o[0] = bf2_mul(pack_bf2(a0, a1), c2[0]);                  // (conv + bias term) cast to bf16, then the gate
+              o[1] = bf2_mul(pack_bf2(a2, a3), c2[1]);
+              *reinterpret_cast<uint2*>(orow + t0) = make_uint2(o[0], o[1]);
             }
           }
-        } else {
+        }
+      } else {
+#pragma unroll 1
+        for (int it0 = 0; it0 < EIT; it0 += EB) {
+          uint2 prev[EB];                                    // y * x2 written by this thread for f == 0
 #pragma unroll
-          for (int i = 0; i < NP; ++i) {
-            const int t0 = R * (n1_0 + i) + r0;
+          for (int i = 0; i < EB; ++i) {
+            const int t0 = 4 * ((it0 + i) * TPS + sl);
+            prev[i] = t0 < P.L ? *reinterpret_cast<const uint2*>(orow + t0) : make_uint2(0u, 0u);
+          }
+#pragma unroll
+          for (int i = 0; i < EB; ++i) {
+            const int t0 = 4 * ((it0 + i) * TPS + sl);
             if (t0 < P.L) {
-              const float4 y = *reinterpret_cast<const float4*>(Y + t0);
-              float yv[4] = {y.x * inv_gain, y.y * inv_gain, y.z * inv_gain, y.w * inv_gain};
+              const float4 y = *reinterpret_cast<const float4*>(Y + t0 + 4 * (t0 >> 5));
+              float yv[4];
+              f2_unpack(f2_mul(f2_pack(y.x, y.y), gain2), yv[0], yv[1]);
+              f2_unpack(f2_mul(f2_pack(y.z, y.w), gain2), yv[2], yv[3]);
               if (P.yu_bf16) {                                 // bf16 layer input: yu is cast to bf16 first
 #pragma unroll
                 for (int j = 0; j < 4; ++j) yv[j] = bf16r(yv[j]);
               }
-              uint2* po = reinterpret_cast<uint2*>(orow + t0);
-              const uint2 prev = *po;                          // y * x2 written by this thread for f == 0
-              *po = make_uint2(pack_bf2(bf_lo(prev.x) + yv[0], bf_hi(prev.x) + yv[1]),
-                               pack_bf2(bf_lo(prev.y) + yv[2], bf_hi(prev.y) + yv[3]));
+              *reinterpret_cast<uint2*>(orow + t0) =
+                  make_uint2(pack_bf2(bf_lo(prev[i].x) + yv[0], bf_hi(prev[i].x) + yv[1]),
+                             pack_bf2(bf_lo(prev[i].y) + yv[2], bf_hi(prev[i].y) + yv[3]));
             }
           }
         }
@@ -804,7 +984,6 @@ longconv_tcl_kernel(const Params P) {
   }
 #undef LCL_STAGE
 #undef LCL_BARRIER
-  (void)lrow; (void)lsub;
 
   __syncthreads();
   if (warp == 0) {
@@ -814,7 +993,7 @@ longconv_tcl_kernel(const Params P) {
 }
 
 using Geo4k = Geo<16, 8, 4, 1>;
-using Geo16k = Geo<32, 16, 4, 2>;
+using Geo16k = Geo<32, 16, 4, 1>;
 using Geo64k = Geo<64, 32, 1, 4>;
 
 template <typename G>
@@ -889,6 +1068,9 @@ int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
   P.u = a->u; P.usb = a->u_sb; P.usc = a->u_sc;
   P.out = (__nv_bfloat16*)a->out; P.osb = a->out_sb; P.osc = a->out_sc;
   P.sw = a->short_w; P.sb = a->short_b;
+  // 16-byte row starts allow one 16-byte load per 8 time steps; otherwise two 8-byte loads
+  P.al16 = a->xin_sc % 8 == 0 && a->xin_sb % 8 == 0 && m2_aligned(a->xin, 16) &&
+           (a->n_filters == 1 || a->u_dtype == M2_F32 || (a->u_sc % 8 == 0 && a->u_sb % 8 == 0 && m2_aligned(a->u, 16)));
   for (int f = 0; f < 2; ++f) { P.spec[f] = a->spec[f]; P.bias[f] = a->bias[f]; }
   // 2-byte residual input: bf16, or the fp16 time-major copy a LayerNorm / m2_time_major_f16 wrote
   const bool ubf = a->n_filters == 2 && (a->u_dtype == M2_BF16 || a->u_dtype == M2_F16);
