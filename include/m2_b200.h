@@ -101,7 +101,7 @@ int m2_hyena_filter(const m2_filter_args* args, void* stream);
  * m2_longconv_kind() names the kernel family used for (seq_len, act_dtype, d_model): 0 = float32
  * arithmetic on CUDA cores (any shape), 1 = tcgen05 tensor cores (bf16, 64 < seq_len <= 128,
  * d_model a multiple of 128, channel-contiguous tensors), 2 = tcgen05 tensor cores for long rows
- * (bf16, 512 < seq_len <= 32768, a multiple of 4, transform length 4096 / 16384 / 65536 for
+ * (bf16, 128 < seq_len <= 32768, a multiple of 4, transform length 4096 / 16384 / 65536 for
  * seq_len up to 2048 / 8192 / 32768; needs time-contiguous tensors, i.e. xin_st == u_st ==
  * out_st == 1);
  * 3 = tcgen05 Toeplitz GEMMs with the batch as the M dimension (bf16, 16 <= seq_len <= 128, a

@@ -1,6 +1,6 @@
 // Fused gated long convolution on tcgen05 tensor cores for long rows (kernel family 2):
 // bf16 activations stored time-contiguous ((B, channels, L) layout), transform length
-// N = 32 * N2 * N3 = 4096 (L <= 2048), 16384 (L <= 8192) or 65536 (L <= 32768).
+// N = 32 * N2 * N3 = 4096 (128 < L <= 2048), 16384 (L <= 8192) or 65536 (L <= 32768).
 //
 // One (batch row, channel) sequence is processed at a time by a "slot" of 128 * TS threads; a CTA holds several
 // slots that run independently (own barriers, own TMEM columns, own shared-memory region) so that one slot's loads
@@ -432,42 +432,38 @@ __device__ __forceinline__ void cmul_h2(uint32_t re, uint32_t im, uint32_t tr, u
   ore = h2_fma(h2_neg(im), ti, h2_mul(re, tr));
   oim = h2_fma(re, ti, h2_mul(im, tr));
 }
-// body(g, re, im) for every group g of 8 complex columns of one TMEM row, planar: Re in columns [8g, 8g+8), Im in
-// columns [nc + 8g, ...), converted to half2 pairs.  Columns are fetched 16 complex at a time (one wait per 32
-// registers) so that the TMEM latency is paid once per batch, not once per group.
-template <int NC, typename F>
-__device__ __forceinline__ void for_each_c8(uint32_t tl, F&& body) {
-  if constexpr (NC % 16 == 0) {
+// One re-layout step ("hop") of a thread: for each of its NT row tiles (tile index t = ts + TS i, accumulator at
+// column tile_cols * t of the thread's TMEM lane) and each group g of 8 complex columns of that row -- planar: Re in
+// columns [8g, 8g+8), Im in columns [NC + 8g, ...) -- calls body(t, g, re, im) with the values as half2 pairs.
+// Columns are fetched 16 complex at a time (8 when NC = 8) and the fetch of the next batch is issued before the
+// current one is processed, so the TMEM latency is exposed once per hop instead of once per batch.
+template <int NC, int NT, int TS, typename F>
+__device__ __forceinline__ void hop_rows(uint32_t tml, int tile_cols, int ts, F&& body) {
+  constexpr int W = NC >= 16 ? 16 : 8;                  // complex columns per batch
+  constexpr int BPT = NC / W;                           // batches per tile
+  constexpr int NB = NT * BPT;
+  uint32_t a[2][W], b[2][W];
+  auto issue = [&](int buf, int i) {
+    const uint32_t tl = tml + tile_cols * (ts + TS * (i / BPT)) + W * (i % BPT);
+    if constexpr (W == 16) { tc::tmem_ld16(tl, a[buf]); tc::tmem_ld16(tl + NC, b[buf]); }
+    else { tmem_ld8(tl, a[buf]); tmem_ld8(tl + NC, b[buf]); }
+  };
+  issue(0, 0);
 #pragma unroll
-    for (int c = 0; c < NC; c += 16) {
-      uint32_t a[16], b[16];
-      tc::tmem_ld16(tl + c, a);
-      tc::tmem_ld16(tl + NC + c, b);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t re[4], im[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          re[i] = pack_h2(__uint_as_float(a[8 * h + 2 * i]), __uint_as_float(a[8 * h + 2 * i + 1]));
-          im[i] = pack_h2(__uint_as_float(b[8 * h + 2 * i]), __uint_as_float(b[8 * h + 2 * i + 1]));
-        }
-        body(c / 8 + h, re, im);
-      }
-    }
-  } else {
-    static_assert(NC == 8, "column count");
-    uint32_t a[8], b[8];
-    tmem_ld8(tl, a);
-    tmem_ld8(tl + NC, b);
+  for (int i = 0; i < NB; ++i) {
     tc::tmem_ld_wait();
-    uint32_t re[4], im[4];
+    if (i + 1 < NB) issue((i + 1) & 1, i + 1);
+    const int t = ts + TS * (i / BPT);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      re[i] = pack_h2(__uint_as_float(a[2 * i]), __uint_as_float(a[2 * i + 1]));
-      im[i] = pack_h2(__uint_as_float(b[2 * i]), __uint_as_float(b[2 * i + 1]));
+    for (int h = 0; h < W / 8; ++h) {
+      uint32_t re[4], im[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        re[k] = pack_h2(__uint_as_float(a[i & 1][8 * h + 2 * k]), __uint_as_float(a[i & 1][8 * h + 2 * k + 1]));
+        im[k] = pack_h2(__uint_as_float(b[i & 1][8 * h + 2 * k]), __uint_as_float(b[i & 1][8 * h + 2 * k + 1]));
+      }
+      body(t, (W / 8) * (i % BPT) + h, re, im);
     }
-    body(0, re, im);
   }
 }
 __device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
@@ -536,48 +532,65 @@ __device__ __forceinline__ uint32_t bf2_to_h2(uint32_t v) { return pack_h2(bf_lo
 
 // MMAs of one stage: 0 F1, 1 DFT_N2, 2 DFT_N3, 3 DFT_N3 on conjugated data (= inverse), 4 DFT_N2 (inverse), 5 I1.
 // A operands: MN-major (row groups `sbo` apart, K core matrices 128 bytes apart) except stage 3 (K-major rows).
+// The issuing thread is on every stage's critical path, so descriptors are not rebuilt per MMA: an un-swizzled
+// descriptor is {start address >> 4 | LBO field, SBO field | version}, the two high parts are compile-time
+// constants per operand and moving to another tile or K step adds a constant to the 14-bit address field
+// (shared-memory addresses stay below 2^18, so the field cannot overflow into its neighbour).
+__device__ __forceinline__ uint64_t desc_at(uint32_t lo_base, uint32_t byte_off, uint32_t lbo, uint32_t sbo) {
+  const uint32_t lo = lo_base + (byte_off >> 4) + ((lbo >> 4) << 16);
+  const uint32_t hi = (sbo >> 4) | (1u << 14);          // bits 32..45 SBO, bit 46 descriptor version
+  return ((uint64_t)hi << 32) | lo;
+}
 template <typename G>
 __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t data, uint32_t hdr) {
   constexpr int K2 = G::K2, K3 = G::K3;
+  const uint32_t dlo = data >> 4, hlo = hdr >> 4;        // both bases are 16-byte aligned and below 2^18
   if (stage == 0) {
     constexpr uint32_t id = tc::make_idesc_major(128, 32, 0, 1, 0);
-    const uint64_t dB = tc::smem_desc_k_nosw(hdr + G::F1_OFF, 128, 16 * 16);
+    const uint64_t dB = desc_at(hlo, G::F1_OFF, 128, 16 * 16);
 #pragma unroll
     for (int t = 0; t < G::T1T; ++t)
-      tc::mma_ss(tm + 32 * t, tc::smem_desc_k_nosw(data + t * 16 * G::SBO1, 128, G::SBO1), dB, id, 0);
-  } else if (stage == 1 || stage == 4) {
+      tc::mma_ss(tm + 32 * t, desc_at(dlo, t * 16 * G::SBO1, 128, G::SBO1), dB, id, 0);
+  } else if (stage == 1) {
     constexpr uint32_t id = tc::make_idesc_major(128, K2, 0, 1, 0);
-    const uint32_t sbo = stage == 1 ? G::SBO2 : G::SBO4;
 #pragma unroll
     for (int t = 0; t < G::T2T; ++t)
 #pragma unroll
       for (int s = 0; s < K2 / 16; ++s)
-        tc::mma_ss(tm + K2 * t, tc::smem_desc_k_nosw(data + t * 16 * sbo + s * 256, 128, sbo),
-                   tc::smem_desc_k_nosw(hdr + G::F2_OFF + s * 256, 128, K2 * 16), id, s ? 1u : 0u);
+        tc::mma_ss(tm + K2 * t, desc_at(dlo, t * 16 * G::SBO2 + s * 256, 128, G::SBO2),
+                   desc_at(hlo, G::F2_OFF + s * 256, 128, K2 * 16), id, s ? 1u : 0u);
+  } else if (stage == 4) {
+    constexpr uint32_t id = tc::make_idesc_major(128, K2, 0, 1, 0);
+#pragma unroll
+    for (int t = 0; t < G::T2T; ++t)
+#pragma unroll
+      for (int s = 0; s < K2 / 16; ++s)
+        tc::mma_ss(tm + K2 * t, desc_at(dlo, t * 16 * G::SBO4 + s * 256, 128, G::SBO4),
+                   desc_at(hlo, G::F2_OFF + s * 256, 128, K2 * 16), id, s ? 1u : 0u);
   } else if (stage == 2) {
     constexpr uint32_t id = tc::make_idesc_major(128, K3, 0, 1, 0);
 #pragma unroll
     for (int t = 0; t < G::T3T; ++t)
 #pragma unroll
       for (int s = 0; s < K3 / 16; ++s)
-        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * 16 * G::SBO3 + s * 256, 128, G::SBO3),
-                   tc::smem_desc_k_nosw(hdr + G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
+        tc::mma_ss(tm + K3 * t, desc_at(dlo, t * 16 * G::SBO3 + s * 256, 128, G::SBO3),
+                   desc_at(hlo, G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
   } else if (stage == 3) {
     constexpr uint32_t id = tc::make_idesc(128, K3, 0);
 #pragma unroll
     for (int t = 0; t < G::T3T; ++t)
 #pragma unroll
       for (int s = 0; s < K3 / 16; ++s)
-        tc::mma_ss(tm + K3 * t, tc::smem_desc_k_nosw(data + t * G::TILE3 + s * 256, 128, G::SBO3K),
-                   tc::smem_desc_k_nosw(hdr + G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
+        tc::mma_ss(tm + K3 * t, desc_at(dlo, t * G::TILE3 + s * 256, 128, G::SBO3K),
+                   desc_at(hlo, G::F3_OFF + s * 256, 128, K3 * 16), id, s ? 1u : 0u);
   } else {
     constexpr uint32_t id = tc::make_idesc_major(128, 16, 0, 1, 0);
 #pragma unroll
     for (int t = 0; t < G::T1T; ++t)
 #pragma unroll
       for (int s = 0; s < 2; ++s)
-        tc::mma_ss(tm + 16 * t, tc::smem_desc_k_nosw(data + t * 16 * G::SBO5 + s * 256, 128, G::SBO5),
-                   tc::smem_desc_k_nosw(hdr + G::I1_OFF + s * 256, 128, 32 * 16), id, s ? 1u : 0u);
+        tc::mma_ss(tm + 16 * t, desc_at(dlo, t * 16 * G::SBO5 + s * 256, 128, G::SBO5),
+                   desc_at(hlo, G::I1_OFF + s * 256, 128, 32 * 16), id, s ? 1u : 0u);
   }
 }
 
@@ -765,54 +778,48 @@ longconv_tcl_kernel(const Params P) {
       LCL_STAGE(0)
 
       // ---------------- hop 1: x w^{r (k1 + 1/2)}; rows r = (n2, n3) -> operand rows (k1, n3), K = (ri, n2) ----------------
-#pragma unroll 1
-      for (int t = ts; t < G::T1T; t += TS) {
+      hop_rows<16, G::T1T / TS, TS>(tml, 32, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k1 = 8 g ..
         const int r = 128 * t + l, n2 = r / N3, n3 = r % N3;
         const uint32_t ta = hdr + G::TA1_OFF + n2 * 64, tb = hdr + G::TB1_OFF + n3 * G::TB1_PITCH;
-        const uint32_t dst = data + n3 * G::SBO2 + (n2 >> 3) * 128 + (n2 & 7) * 16;
-        for_each_c8<16>(tml + 32 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k1 = 8 g ..
-          const uint4 ar = lds128(ta + 16 * g), ai = lds128(ta + 32 + 16 * g);
-          const uint4 br = lds128(tb + 16 * g), bi = lds128(tb + 32 + 16 * g);
-          const uint32_t arr[4] = {ar.x, ar.y, ar.z, ar.w}, aii[4] = {ai.x, ai.y, ai.z, ai.w};
-          const uint32_t brr[4] = {br.x, br.y, br.z, br.w}, bii[4] = {bi.x, bi.y, bi.z, bi.w};
-          uint32_t orr[4], oi[4];
+        const uint4 ar = lds128(ta + 16 * g), ai = lds128(ta + 32 + 16 * g);
+        const uint4 br = lds128(tb + 16 * g), bi = lds128(tb + 32 + 16 * g);
+        const uint32_t arr[4] = {ar.x, ar.y, ar.z, ar.w}, aii[4] = {ai.x, ai.y, ai.z, ai.w};
+        const uint32_t brr[4] = {br.x, br.y, br.z, br.w}, bii[4] = {bi.x, bi.y, bi.z, bi.w};
+        uint32_t orr[4], oi[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t wr, wi;
-            cmul_h2(arr[i], aii[i], brr[i], bii[i], wr, wi);
-            cmul_h2(re[i], im[i], wr, wi, orr[i], oi[i]);
-          }
-          const uint32_t d = dst + g * N3 * G::SBO2;              // row group j = k1hi N3 + n3
-          sts128(d, orr[0], orr[1], orr[2], orr[3]);
-          sts128(d + (N2 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);   // K index N2 + n2: the imaginary plane
-        });
-      }
+        for (int i = 0; i < 4; ++i) {
+          uint32_t wr, wi;
+          cmul_h2(arr[i], aii[i], brr[i], bii[i], wr, wi);
+          cmul_h2(re[i], im[i], wr, wi, orr[i], oi[i]);
+        }
+        // row group j = k1hi N3 + n3, K index n2 (real plane) and N2 + n2 (imaginary plane)
+        const uint32_t d = data + (g * N3 + n3) * G::SBO2 + (n2 >> 3) * 128 + (n2 & 7) * 16;
+        sts128(d, orr[0], orr[1], orr[2], orr[3]);
+        sts128(d + (N2 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
+      });
       tc::tc_fence_before();
       LCL_STAGE(1)
 
       // ---------------- hop 2: x w^{32 n3 k2}; rows (k1, n3) -> operand rows (k1, k2), K = (ri, n3) ----------------
-#pragma unroll 1
-      for (int t = ts; t < G::T2T; t += TS) {
+      hop_rows<N2, G::T2T / TS, TS>(tml, K2, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k2 = 8 g ..
         const int j = 16 * t + (l >> 3), k1 = 8 * (j / N3) + (l & 7), n3 = j % N3;
         const uint32_t tw = hdr + G::T2A_OFF + n3 * (K2 * 2);
-        const uint32_t dst = data + k1 * G::SBO3 + (n3 >> 3) * 128 + (n3 & 7) * 16;
-        for_each_c8<N2>(tml + K2 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k2 = 8 g ..
-          const uint4 wr4 = lds128(tw + 16 * g), wi4 = lds128(tw + N2 * 2 + 16 * g);
-          const uint32_t wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w}, wi[4] = {wi4.x, wi4.y, wi4.z, wi4.w};
-          uint32_t orr[4], oi[4];
+        const uint4 wr4 = lds128(tw + 16 * g), wi4 = lds128(tw + N2 * 2 + 16 * g);
+        const uint32_t wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w}, wi[4] = {wi4.x, wi4.y, wi4.z, wi4.w};
+        uint32_t orr[4], oi[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) cmul_h2(re[i], im[i], wr[i], wi[i], orr[i], oi[i]);
-          const uint32_t d = dst + g * 16 * G::SBO3;              // row group j3 = k2hi 16 + k1
-          sts128(d, orr[0], orr[1], orr[2], orr[3]);
-          sts128(d + (N3 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
-        });
-      }
+        for (int i = 0; i < 4; ++i) cmul_h2(re[i], im[i], wr[i], wi[i], orr[i], oi[i]);
+        // row group j3 = k2hi 16 + k1, K index n3 / N3 + n3
+        const uint32_t d = data + (g * 16 + k1) * G::SBO3 + (n3 >> 3) * 128 + (n3 & 7) * 16;
+        sts128(d, orr[0], orr[1], orr[2], orr[3]);
+        sts128(d + (N3 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
+      });
       // this row's slice of the spectrum comes from global memory (L2 for all but the first sequence of a channel):
       // the first tile's slice is requested before the wait for stage 2's MMAs, every further tile's while the
-      // one before it is being multiplied (when the slices of two tiles fit the register budget)
+      // one before it is being multiplied
       constexpr int NG = K3 / 8;
       const __half* Gc = reinterpret_cast<const __half*>(P.spec[f] + G::HDR_FLOATS) + (size_t)ch * G::N;
-      uint4 gv[NG];
+      uint4 gv[NG], gn[NG];
       {
         const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)(ts * 128 + l) * K3);
 #pragma unroll
@@ -826,85 +833,69 @@ longconv_tcl_kernel(const Params P) {
         const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);   // 2^-e of this channel
         const float bkf = __ldg(P.bias[f] + ch) * G::KAPPA / inv_gain;
         const uint32_t bk = pack_h2(bkf, bkf);
-#pragma unroll 1
-        for (int t = ts; t < G::T3T; t += TS) {
-          uint4 gn[NG <= 4 ? NG : 1];
-          if (NG <= 4 && t + TS < G::T3T) {
+        hop_rows<N3, G::T3T / TS, TS>(tml, K3, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k3 = 8 g ..
+          if (g == 0 && t + TS < G::T3T) {
             const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)((t + TS) * 128 + l) * K3);
 #pragma unroll
-            for (int i = 0; i < (NG <= 4 ? NG : 1); ++i) gn[i] = __ldg(gp + i);
+            for (int i = 0; i < NG; ++i) gn[i] = __ldg(gp + i);
+          }
+          const uint32_t gr[4] = {gv[g].x, gv[g].y, gv[g].z, gv[g].w};
+          const uint32_t gi[4] = {gv[N3 / 8 + g].x, gv[N3 / 8 + g].y, gv[N3 / 8 + g].z, gv[N3 / 8 + g].w};
+          uint32_t orr[4], oi[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            cmul_h2(re[i], im[i], h2_add(gr[i], bk), gi[i], orr[i], oi[i]);
+            oi[i] = h2_neg(oi[i]);
           }
           const uint32_t dst = data + t * G::TILE3 + (l >> 3) * G::SBO3K + (l & 7) * 16;
-          for_each_c8<N3>(tml + K3 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {  // k3 = 8 g ..
-            const uint32_t gr[4] = {gv[g].x, gv[g].y, gv[g].z, gv[g].w};
-            const uint32_t gi[4] = {gv[N3 / 8 + g].x, gv[N3 / 8 + g].y, gv[N3 / 8 + g].z, gv[N3 / 8 + g].w};
-            uint32_t orr[4], oi[4];
+          sts128(dst + g * 128, orr[0], orr[1], orr[2], orr[3]);
+          sts128(dst + (N3 / 8 + g) * 128, oi[0], oi[1], oi[2], oi[3]);
+          if (g == N3 / 8 - 1) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              cmul_h2(re[i], im[i], h2_add(gr[i], bk), gi[i], orr[i], oi[i]);
-              oi[i] = h2_neg(oi[i]);
-            }
-            sts128(dst + g * 128, orr[0], orr[1], orr[2], orr[3]);
-            sts128(dst + (N3 / 8 + g) * 128, oi[0], oi[1], oi[2], oi[3]);
-          });
-          if (t + TS < G::T3T) {
-            if (NG <= 4) {
-#pragma unroll
-              for (int i = 0; i < (NG <= 4 ? NG : 1); ++i) gv[i] = gn[i];
-            } else {
-              const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)((t + TS) * 128 + l) * K3);
-#pragma unroll
-              for (int i = 0; i < NG; ++i) gv[i] = __ldg(gp + i);
-            }
+            for (int i = 0; i < NG; ++i) gv[i] = gn[i];
           }
-        }
+        });
       }
       tc::tc_fence_before();
       LCL_STAGE(3)
 
       // ---------------- hop 4: x w^{32 n3 k2}; rows (k1, k2) -> operand rows (k1, n3), K = (ri, k2) ----------------
-#pragma unroll 1
-      for (int t = ts; t < G::T3T; t += TS) {
+      hop_rows<N3, G::T3T / TS, TS>(tml, K3, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // n3 = 8 g ..
         const int k1 = l >> 3, k2 = 8 * t + (l & 7);
         const uint32_t tw = hdr + G::T2B_OFF + k2 * G::T2B_PITCH;
-        const uint32_t dst = data + k1 * G::SBO4 + (k2 >> 3) * 128 + (k2 & 7) * 16;
-        for_each_c8<N3>(tml + K3 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // n3 = 8 g ..
-          const uint4 wr4 = lds128(tw + 16 * g), wi4 = lds128(tw + N3 * 2 + 16 * g);
-          const uint32_t wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w}, wi[4] = {wi4.x, wi4.y, wi4.z, wi4.w};
-          uint32_t orr[4], oi[4];
+        const uint4 wr4 = lds128(tw + 16 * g), wi4 = lds128(tw + N3 * 2 + 16 * g);
+        const uint32_t wr[4] = {wr4.x, wr4.y, wr4.z, wr4.w}, wi[4] = {wi4.x, wi4.y, wi4.z, wi4.w};
+        uint32_t orr[4], oi[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) cmul_h2(re[i], im[i], wr[i], wi[i], orr[i], oi[i]);
-          const uint32_t d = dst + g * 16 * G::SBO4;              // row group j4 = n3hi 16 + k1
-          sts128(d, orr[0], orr[1], orr[2], orr[3]);
-          sts128(d + (N2 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
-        });
-      }
+        for (int i = 0; i < 4; ++i) cmul_h2(re[i], im[i], wr[i], wi[i], orr[i], oi[i]);
+        // row group j4 = n3hi 16 + k1, K index k2 / N2 + k2
+        const uint32_t d = data + (g * 16 + k1) * G::SBO4 + (k2 >> 3) * 128 + (k2 & 7) * 16;
+        sts128(d, orr[0], orr[1], orr[2], orr[3]);
+        sts128(d + (N2 / 8) * 128, oi[0], oi[1], oi[2], oi[3]);
+      });
       tc::tc_fence_before();
       LCL_STAGE(4)
 
       // ---------------- hop 5: x w^{r (k1 + 1/2)}; rows (k1, n3) -> operand rows r = (n2, n3), K = (ri, k1) ----------------
-#pragma unroll 1
-      for (int t = ts; t < G::T2T; t += TS) {
+      hop_rows<N2, G::T2T / TS, TS>(tml, K2, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // n2 = 8 g ..
         const int k1 = l >> 3, n3 = 8 * t + (l & 7);
         const uint32_t ta = hdr + G::TA5_OFF + k1 * (K2 * 2);
         const uint32_t tbs = lds32(hdr + G::TB5_OFF + (k1 * N3 + n3) * 4);          // (Re, Im) of the n3 part
         const uint32_t tbr = __byte_perm(tbs, tbs, 0x1010), tbi = __byte_perm(tbs, tbs, 0x3232);
-        const uint32_t dst = data + n3 * G::SBO5 + (k1 >> 3) * 128 + (k1 & 7) * 16;
-        for_each_c8<N2>(tml + K2 * t, [&](int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // n2 = 8 g ..
-          const uint4 ar4 = lds128(ta + 16 * g), ai4 = lds128(ta + N2 * 2 + 16 * g);
-          const uint32_t ar[4] = {ar4.x, ar4.y, ar4.z, ar4.w}, ai[4] = {ai4.x, ai4.y, ai4.z, ai4.w};
-          uint32_t orr[4], oi[4];
+        const uint4 ar4 = lds128(ta + 16 * g), ai4 = lds128(ta + N2 * 2 + 16 * g);
+        const uint32_t ar[4] = {ar4.x, ar4.y, ar4.z, ar4.w}, ai[4] = {ai4.x, ai4.y, ai4.z, ai4.w};
+        uint32_t orr[4], oi[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t wr, wi;
-            cmul_h2(ar[i], ai[i], tbr, tbi, wr, wi);
-            cmul_h2(re[i], im[i], wr, wi, orr[i], oi[i]);
-          }
-          const uint32_t d = dst + g * N3 * G::SBO5;              // row group j5 = n2hi N3 + n3
-          sts128(d, orr[0], orr[1], orr[2], orr[3]);
-          sts128(d + 2 * 128, oi[0], oi[1], oi[2], oi[3]);          // K index 16 + k1
-        });
-      }
+        for (int i = 0; i < 4; ++i) {
+          uint32_t wr, wi;
+          cmul_h2(ar[i], ai[i], tbr, tbi, wr, wi);
+          cmul_h2(re[i], im[i], wr, wi, orr[i], oi[i]);
+        }
+        // row group j5 = n2hi N3 + n3, K index k1 / 16 + k1
+        const uint32_t d = data + (g * N3 + n3) * G::SBO5 + (k1 >> 3) * 128 + (k1 & 7) * 16;
+        sts128(d, orr[0], orr[1], orr[2], orr[3]);
+        sts128(d + 2 * 128, oi[0], oi[1], oi[2], oi[3]);
+      });
       tc::tc_fence_before();
       LCL_STAGE(5)
 
@@ -992,7 +983,7 @@ longconv_tcl_kernel(const Params P) {
   }
 }
 
-using Geo4k = Geo<16, 8, 4, 1>;
+using Geo4k = Geo<16, 8, 8, 1>;
 using Geo16k = Geo<32, 16, 4, 1>;
 using Geo64k = Geo<64, 32, 1, 4>;
 
@@ -1033,7 +1024,9 @@ static int launch_conv(const Params& P, cudaStream_t st) {
 // supply time-contiguous tensors
 int longconv_tcl_supported(int seq_len, m2_dtype act_dtype) {
   if (act_dtype != M2_BF16 || seq_len % 4 != 0) return 0;
-  return seq_len > 512 && seq_len <= 32768;      // transform length 4096 up to 2048, 16384 up to 8192, else 65536
+  // transform length 4096 up to 2048, 16384 up to 8192, else 65536; lengths from 129 on run the 4096-point
+  // transform with more zero padding (still several times faster than the float32 CUDA-core family)
+  return seq_len > 128 && seq_len <= 32768;
 }
 
 // header + per channel N/2 half2 bins + per channel one float (2^-e, see gain_scale)
@@ -1045,7 +1038,7 @@ size_t spectrum_kind2_floats(int D, int L) {
 
 int spectrum_kind2_launch(int D, int L, const float* k, float* spec, cudaStream_t st) {
   M2_REQUIRE(longconv_tcl_supported(L, M2_BF16), M2_ERR_UNSUPPORTED,
-             "m2_filter_spectrum: kind 2 covers 512 < seq_len <= 32768, multiples of 4");
+             "m2_filter_spectrum: kind 2 covers 128 < seq_len <= 32768, multiples of 4");
   const int R = m2_filter_row_len(L);
   if (L <= 2048) return lcl::launch_spectrum<lcl::Geo4k>(D, R, k, spec, st);
   if (L <= 8192) return lcl::launch_spectrum<lcl::Geo16k>(D, R, k, spec, st);
@@ -1055,7 +1048,7 @@ int spectrum_kind2_launch(int D, int L, const float* k, float* spec, cudaStream_
 int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
   using namespace lcl;
   M2_REQUIRE(longconv_tcl_supported(a->seq_len, a->act_dtype), M2_ERR_UNSUPPORTED,
-             "m2_longconv_fwd: kind 2 needs bf16 activations and 512 < seq_len <= 32768, a multiple of 4");
+             "m2_longconv_fwd: kind 2 needs bf16 activations and 128 < seq_len <= 32768, a multiple of 4");
   M2_REQUIRE(a->xin_st == 1 && a->out_st == 1 && (a->n_filters == 1 || a->u_st == 1), M2_ERR_UNSUPPORTED,
              "m2_longconv_fwd: kind 2 needs time-contiguous tensors ((batch, channel, time) layout)");
   M2_REQUIRE(a->xin_sc % 4 == 0 && a->xin_sb % 4 == 0 && a->out_sc % 4 == 0 && a->out_sb % 4 == 0 &&

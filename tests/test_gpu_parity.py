@@ -441,7 +441,9 @@ def test_longconv_tensor_core_family(L, residual, u_bf16):
 @pytest.mark.parametrize("L,D,B", [(2048, 64, 2), (1500, 16, 1), (8192, 32, 2), (6000, 8, 1), (4100, 8, 1),
                                    (32768, 4, 2), (20000, 3, 1),
                                    # lengths that leave more than half of the transform as padding
-                                   (1024, 16, 2), (600, 8, 1), (4096, 8, 1), (3000, 8, 1), (16384, 4, 1), (12000, 3, 1)])
+                                   (1024, 16, 2), (600, 8, 1), (4096, 8, 1), (3000, 8, 1), (16384, 4, 1), (12000, 3, 1),
+                                   # 129 .. 512: the 4096-point transform
+                                   (512, 16, 3), (256, 8, 5), (132, 8, 2), (384, 768, 1)])
 @pytest.mark.parametrize("residual,u_bf16", [(True, False), (True, True), (False, False)])
 def test_longconv_long_row_family(L, D, B, residual, u_bf16):
     cfg = dict(C.CASES["mixer_small"], L=L, l_max=L, D=D, B=B, order=32, residual=residual, seed=71)
