@@ -56,6 +56,7 @@ HEADLINE = "m2bert80m-L128"
 # summarised under profiles/ (file named beside each value); None where no capture of the current kernel exists
 TRAFFIC = {
     "m2bert80m-L128": (247.2e6, "profiles/longconv_tz_m2bert80m-L128.md"),
+    "m2bert80m-L8192": (3018e6, "profiles/longconv_tcl_m2bert80m-L8192.md (batch-8 capture scaled to batch 32)"),
 }
 VOCAB = 30528
 METRIC = "M2-BERT-80M fwd sequences/sec"
@@ -345,7 +346,8 @@ def measure(ctx, name, w, steps, warmup, clocks=False):
         alg_bytes = 10.0 * B * D * L + 16.0 * D * L          # bf16 activations, two filters
         peak, peak_src = measured_peaks()
         achieved = alg_bytes / (conv_ms * 1e-3) / 1e9 if conv_ms else None
-        traffic, traffic_src = TRAFFIC.get(name, (None, None)) if B == WORKLOADS[name].get("per_gpu", WORKLOADS[name].get("global_batch")) else (None, None)
+        full_batch = B == WORKLOADS[name].get("per_gpu", WORKLOADS[name].get("global_batch"))      # captures are of that batch
+        traffic, traffic_src = TRAFFIC.get(name, (None, None)) if full_batch else (None, None)
         res = {"value": world * B / (ms_per_step / 1e3), "unit": UNIT, "ms_per_step": ms_per_step, "steps": steps,
                "scaling": scaling, "config": config_of(name, w, B, world, scaling, graph=not args.no_graph),
                "e2e": {"value": world * B / (e2e_ms / steps / 1e3), "unit": UNIT,
