@@ -226,6 +226,8 @@ typedef struct {
   const void* w;
   const float* bias;
   void* out; long long ldo;
+  int variant;   /* 0: the library picks the kernel; 2: CTA-pair tiles (the kernel of m2_linear_fwd) where they apply --
+                    results are bit-identical, kept selectable for cross-checks */
 } m2_blockdiag_args;
 
 int m2_blockdiag_fwd(const m2_blockdiag_args* args, void* stream);

@@ -56,7 +56,7 @@ class BlockdiagArgs(C.Structure):
         ("m", C.c_int), ("nblocks", C.c_int), ("p", C.c_int), ("q", C.c_int),
         ("in_features", C.c_int), ("out_features", C.c_int), ("dtype", C.c_int),
         ("x", C.c_void_p), ("ldx", C.c_longlong), ("w", C.c_void_p), ("bias", C.c_void_p),
-        ("out", C.c_void_p), ("ldo", C.c_longlong),
+        ("out", C.c_void_p), ("ldo", C.c_longlong), ("variant", C.c_int),
     ]
 
 

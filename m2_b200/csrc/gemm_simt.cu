@@ -313,6 +313,8 @@ int blockdiag_tc_launch(const m2_blockdiag_args* a, cudaStream_t st);   // gemm_
 int glu_tc_launch(const m2_glu_args* a, cudaStream_t st);
 bool blockdiag_tc_supported(const m2_blockdiag_args* a);
 bool glu_tc_supported(const m2_glu_args* a);
+bool blockdiag_pair_supported(const m2_blockdiag_args* a);               // linear_tc.cu
+int blockdiag_pair_launch(const m2_blockdiag_args* a, cudaStream_t st);
 
 }  // namespace m2
 
@@ -330,7 +332,13 @@ extern "C" int m2_blockdiag_fwd(const m2_blockdiag_args* a, void* stream) {
   M2_REQUIRE(a->ldx >= a->in_features && a->ldo >= a->out_features, M2_ERR_ARG,
              "m2_blockdiag_fwd: row stride smaller than the row");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // The MLP's block-diagonal GEMMs stream a wide activation once (wo: K = intermediate size) and are bound by
+  // that read, not by operand re-use: the single-CTA kernel with its finer units (128-row tiles) is the faster
+  // one there (52 vs 62 us at M = 32768, 3072 -> 768), so CTA-pair tiles run only on request or for shapes the
+  // single-CTA kernel does not take (block widths that are not multiples of 64).
+  if (a->variant == 2 && blockdiag_pair_supported(a)) return blockdiag_pair_launch(a, st);
   if (blockdiag_tc_supported(a)) return blockdiag_tc_launch(a, st);
+  if (blockdiag_pair_supported(a)) return blockdiag_pair_launch(a, st);
   dim3 grid((a->q + GT - 1) / GT, (a->m + GT - 1) / GT, a->nblocks);
   M2_REQUIRE(grid.y <= 65535 && grid.z <= 65535, M2_ERR_UNSUPPORTED, "m2_blockdiag_fwd: too many row tiles");
   if (a->dtype == M2_BF16)

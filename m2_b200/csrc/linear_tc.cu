@@ -52,6 +52,10 @@ struct Params {
   int ksteps, m_pairs, n_tiles, total_tiles;
   int L, batch;                  // tokens are (b, t), b < batch, t < L
   int tiles_per_batch, m_tiles;  // TIMEIN: 128-token tiles per batch row, and in all
+  int nb, p, q;                  // ROWS only: block-diagonal weight, nb blocks of q outputs x p inputs (dense: nb = 1)
+  int n_tile, bh;                // UMMA N of the pair (<= 256) and the N-side rows each CTA stages (n_tile / 2)
+  int round_first;               // BlockdiagLinear's arithmetic: the product is rounded to bf16 before the bias is added
+  uint32_t idesc;
   int vec;                       // 32-byte stores are legal for every full 16-element chunk
   int flat;                      // CHANNELS: token m lives at m * 1 from the channel's row start (osb == L)
   __nv_bfloat16* out; long long osb, ost, osc;
@@ -101,9 +105,11 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   tc::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  auto decode = [&](int tile, int& mp, int& nt) {
+  auto decode = [&](int tile, int& mp, int& nt, int& kb) {
     // the weight-side tile index runs fastest, so the pairs working at the same moment share one token tile
+    kb = 0;
     if (MODE == CHANNELS) { mp = tile % P.m_pairs; nt = tile / P.m_pairs; }
+    else if (MODE == ROWS) { nt = tile % P.n_tiles; const int r = tile / P.n_tiles; kb = r % P.nb; mp = r / P.nb; }
     else { nt = tile % P.n_tiles; mp = tile / P.n_tiles; }
   };
 
@@ -113,10 +119,11 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair; tile < P.total_tiles && ok; tile += npairs) {
-        int mp, nt;
-        decode(tile, mp, nt);
+        int mp, nt, kb;
+        decode(tile, mp, nt, kb);
         const int mt = 2 * mp + (int)rank;
-        const int n0 = nt * (2 * BNH) + (int)rank * BNH;
+        const int n0 = kb * P.q + nt * P.n_tile + (int)rank * P.bh;
+        const int ka = kb * P.p;
         int tb = 0, t0 = 0;
         if (MODE == TIMEIN) {
           tb = mt < P.m_tiles ? mt / P.tiles_per_batch : P.batch;     // past the end: an all-zero (out-of-range) box
@@ -126,12 +133,12 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (!tc::mbar_wait(empty + stage, phase ^ 1, abort_flag, tc::ST_TIMEOUT_EMPTY)) { ok = false; break; }
           unsigned char* st = smem + stage * STAGE;
           const uint32_t fb = tc::mapa_shared(tc::smem_u32(full + stage), 0);
-          if (rank == 0) tc::mbar_expect_tx(full + stage, 2 * STAGE);
+          if (rank == 0) tc::mbar_expect_tx(full + stage, 2 * (A_BYTES + P.bh * (BK * 2)));
           if (MODE == TIMEIN) {
             tc::tma_load_3d_2sm(st, &tmA, fb, t0, ks * BK, tb);
             tc::tma_load_3d_2sm(st + A_BYTES / 2, &tmA, fb, t0 + 64, ks * BK, tb);
           } else {
-            tc::tma_load_2d_2sm(st, &tmA, fb, ks * BK, mt * BM);
+            tc::tma_load_2d_2sm(st, &tmA, fb, ka + ks * BK, mt * BM);
           }
           tc::tma_load_2d_2sm(st + A_BYTES, &tmB, fb, ks * BK, n0);
           if (++stage == NST) { stage = 0; phase ^= 1; }
@@ -141,7 +148,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   } else if (warp == 1) {
     // ------------------------------- MMA issue (leader CTA only) -------------------------------
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = tc::make_idesc_major(2 * BM, 2 * BNH, 1, MODE == TIMEIN ? 1 : 0, 0);
+      const uint32_t idesc = P.idesc;
       // M-side operand: K-major rows of 128 bytes, or (TIMEIN) MN-major: 64-token chunks 8 KB apart, 8-K groups 1 KB apart
       const uint64_t dA0 = MODE == TIMEIN ? tc::smem_desc_sw128(tc::smem_u32(smem), A_BYTES / 2, 1024)
                                           : tc::smem_desc_k_sw128(tc::smem_u32(smem));
@@ -176,21 +183,29 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     const uint32_t tempty_leader = tc::mapa_shared(tc::smem_u32(tempty), 0);
     int buf = 0; uint32_t bphase = 0;
     for (int tile = pair; tile < P.total_tiles; tile += npairs) {
-      int mp, nt;
-      decode(tile, mp, nt);
+      int mp, nt, kb;
+      decode(tile, mp, nt, kb);
       const int mt = 2 * mp + (int)rank;
       if (!tc::mbar_wait(tfull + buf, bphase, abort_flag, tc::ST_TIMEOUT_EPI)) break;
       tc::tc_fence_after();
       const uint32_t tacc = tmem_base + buf * ACC_COLS + ((uint32_t)(quarter * 32) << 16) + cs * CW;
+      const bool cols_live = cs * CW < P.n_tile;                 // narrower tiles leave the last column slices idle
       uint32_t acc_r[CW / 16][16];
+      if (cols_live) {
 #pragma unroll
-      for (int ch = 0; ch < CW / 16; ++ch) tc::tmem_ld16(tacc + 16 * ch, acc_r[ch]);
+        for (int ch = 0; ch < CW / 16; ++ch) tc::tmem_ld16(tacc + 16 * ch, acc_r[ch]);
+      }
       tc::tmem_ld_wait();
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive_cluster(tempty_leader + 8 * buf);
       const int lrow = mt * BM + quarter * 32 + lane;          // index on the M side
-      const int c0 = nt * ACC_COLS + cs * CW;                  // first index on the N side
+      const int c0 = kb * P.q + nt * P.n_tile + cs * CW;       // first index on the N side
+      // columns of this tile that exist: up to the end of the tile, of the block and of the tensor
+      int lim = kb * P.q + (nt + 1) * P.n_tile;
+      if (MODE == ROWS && lim > (kb + 1) * P.q) lim = (kb + 1) * P.q;
+      if (lim > P.n_rows) lim = P.n_rows;
+      if (!cols_live) lim = 0;
       if (MODE == CHANNELS) {
         // lane = output channel, columns = consecutive tokens
         const bool live = lrow < P.m_rows;
@@ -198,7 +213,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
         for (int ch = 0; ch < CW / 16; ++ch) {
           const int m0 = c0 + 16 * ch;                         // first token of the chunk
-          if (!live || m0 >= P.n_rows) continue;
+          if (!live || m0 >= lim) continue;
           uint32_t packed[8];
 #pragma unroll
           for (int j = 0; j < 16; j += 2)
@@ -206,10 +221,10 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           const int b = P.flat ? 0 : m0 / P.L;
           const int t = P.flat ? m0 : m0 - b * P.L;
           __nv_bfloat16* dst = P.out + (long long)b * P.osb + (long long)lrow * P.osc + t;
-          if (P.vec && m0 + 16 <= P.n_rows) {
+          if (P.vec && m0 + 16 <= lim) {
             stg256(dst, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
           } else {
-            for (int j = 0; j < 16 && m0 + j < P.n_rows; ++j) {
+            for (int j = 0; j < 16 && m0 + j < lim; ++j) {
               const int mj = m0 + j, bj = P.flat ? 0 : mj / P.L, tj = P.flat ? mj : mj - bj * P.L;
               const uint32_t w = packed[j >> 1];
               reinterpret_cast<uint16_t*>(P.out)[(long long)bj * P.osb + (long long)lrow * P.osc + tj] =
@@ -234,8 +249,8 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
         for (int ch = 0; ch < CW / 16; ++ch) {
           const int n0 = c0 + 16 * ch;
-          if (!live || n0 >= P.n_rows) continue;
-          const bool fullc = n0 + 16 <= P.n_rows;
+          if (!live || n0 >= lim) continue;
+          const bool fullc = n0 + 16 <= lim;
           uint32_t packed[8];
           if (bias_smem) {
             // the staged bias is padded with zeros to a multiple of 16 entries: whole-chunk vector reads
@@ -243,16 +258,20 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const float4 bq = bp[q];
-              packed[2 * q] = pack_bf16(__uint_as_float(acc_r[ch][4 * q]) + bq.x, __uint_as_float(acc_r[ch][4 * q + 1]) + bq.y);
-              packed[2 * q + 1] = pack_bf16(__uint_as_float(acc_r[ch][4 * q + 2]) + bq.z, __uint_as_float(acc_r[ch][4 * q + 3]) + bq.w);
+              float v0 = __uint_as_float(acc_r[ch][4 * q]), v1 = __uint_as_float(acc_r[ch][4 * q + 1]);
+              float v2 = __uint_as_float(acc_r[ch][4 * q + 2]), v3 = __uint_as_float(acc_r[ch][4 * q + 3]);
+              if (P.round_first) { v0 = bf16r(v0); v1 = bf16r(v1); v2 = bf16r(v2); v3 = bf16r(v3); }
+              packed[2 * q] = pack_bf16(v0 + bq.x, v1 + bq.y);
+              packed[2 * q + 1] = pack_bf16(v2 + bq.z, v3 + bq.w);
             }
           } else {
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
               float v0 = __uint_as_float(acc_r[ch][j]), v1 = __uint_as_float(acc_r[ch][j + 1]);
+              if (P.round_first) { v0 = bf16r(v0); v1 = bf16r(v1); }
               if (P.bias) {
-                if (fullc || n0 + j < P.n_rows) v0 += bf16r(__ldg(P.bias + n0 + j));
-                if (fullc || n0 + j + 1 < P.n_rows) v1 += bf16r(__ldg(P.bias + n0 + j + 1));
+                if (fullc || n0 + j < lim) v0 += bf16r(__ldg(P.bias + n0 + j));
+                if (fullc || n0 + j + 1 < lim) v1 += bf16r(__ldg(P.bias + n0 + j + 1));
               }
               packed[j >> 1] = pack_bf16(v0, v1);
             }
@@ -260,7 +279,7 @@ linear_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
           if (P.vec && fullc) {
             stg256(orow + n0, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
           } else {
-            for (int j = 0; j < 16 && n0 + j < P.n_rows; ++j) {
+            for (int j = 0; j < 16 && n0 + j < lim; ++j) {
               const uint32_t w = packed[j >> 1];
               reinterpret_cast<uint16_t*>(orow)[n0 + j] = (uint16_t)((j & 1) ? (w >> 16) : (w & 0xffffu));
             }
@@ -463,10 +482,45 @@ extern "C" int m2_linear_fwd(const m2_linear_args* a, void* stream) {
     }
     P.vec = m2_aligned(a->out, 32) && a->out_st % 16 == 0 && a->out_sb % 16 == 0;
   }
+  P.nb = 1; P.p = K; P.q = P.n_rows; P.n_tile = 2 * BNH; P.bh = BNH; P.round_first = 0;
+  P.idesc = tc::make_idesc_major(2 * BM, P.n_tile, 1, x_time ? 1 : 0, 0);
   P.m_pairs = (P.m_rows + 2 * BM - 1) / (2 * BM);
-  P.n_tiles = (P.n_rows + 2 * BNH - 1) / (2 * BNH);
+  P.n_tiles = (P.n_rows + P.n_tile - 1) / P.n_tile;
   P.total_tiles = P.m_pairs * P.n_tiles;
   if (x_rows && o_time) return launch<CHANNELS>(tmA, tmB, P, st);
   if (x_rows) return launch<ROWS>(tmA, tmB, P, st);
   return launch<TIMEIN>(tmA, tmB, P, st);
 }
+
+namespace m2 {
+// BlockdiagLinear on the CTA-pair kernel: out[:, k q + n] = x[:, k p : (k+1) p] . w[k][n, :] (+ bias), the product
+// rounded to bf16 before the (bf16-rounded) bias is added, as BlockdiagMultiply + StructuredLinear do under autocast
+// (bert/src/mm/blockdiag_multiply.py:49-60, bert/src/mm/structured_linear.py:67-70).
+bool blockdiag_pair_supported(const m2_blockdiag_args* a) {
+  return a->dtype == M2_BF16 && a->p % 64 == 0 && a->q % 16 == 0 && a->in_features == a->nblocks * a->p &&
+         a->out_features == a->nblocks * a->q && a->out_features <= lin::BIAS_MAX && a->ldx % 8 == 0 && a->ldo % 8 == 0 &&
+         m2_aligned(a->x, 16) && m2_aligned(a->w, 16) && m2_aligned(a->out, 16) && a->m >= 1;
+}
+
+int blockdiag_pair_launch(const m2_blockdiag_args* a, cudaStream_t st) {
+  using namespace lin;
+  Params P;
+  memset(&P, 0, sizeof(P));
+  P.L = a->m; P.batch = 1; P.ksteps = a->p / BK;
+  P.out = (__nv_bfloat16*)a->out; P.osb = 0; P.ost = a->ldo; P.osc = 1; P.bias = a->bias;
+  P.m_rows = a->m; P.n_rows = a->out_features;
+  P.nb = a->nblocks; P.p = a->p; P.q = a->q; P.round_first = 1;
+  P.n_tile = a->q >= 2 * BNH ? 2 * BNH : ((a->q + 31) / 32) * 32;
+  P.bh = P.n_tile / 2;
+  P.idesc = tc::make_idesc_major(2 * BM, P.n_tile, 1, 0, 0);
+  P.vec = m2_aligned(a->out, 32) && a->ldo % 16 == 0;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if ((rc = m2_make_tmap_bf16_2d(&tmA, a->x, (uint64_t)a->m, (uint64_t)a->in_features, (uint64_t)a->ldx, BM))) return rc;
+  if ((rc = m2_make_tmap_bf16_2d(&tmB, a->w, (uint64_t)a->nblocks * a->q, (uint64_t)a->p, (uint64_t)a->p, (uint32_t)P.bh))) return rc;
+  P.m_pairs = (P.m_rows + 2 * BM - 1) / (2 * BM);
+  P.n_tiles = (a->q + P.n_tile - 1) / P.n_tile;
+  P.total_tiles = P.m_pairs * P.nb * P.n_tiles;
+  return launch<ROWS>(tmA, tmB, P, st);
+}
+}  // namespace m2

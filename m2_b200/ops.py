@@ -230,8 +230,9 @@ def linear_fwd(x, w, bias, out=None, *, force_simt=False):
     return out
 
 
-def blockdiag_fwd(x2d, w, bias, in_features, out_features):
-    """x2d (m, in_features) @ blockdiag(w)^T (+ bias) -> (m, out_features), dtype of x2d."""
+def blockdiag_fwd(x2d, w, bias, in_features, out_features, variant=0):
+    """x2d (m, in_features) @ blockdiag(w)^T (+ bias) -> (m, out_features), dtype of x2d.  variant=2 asks for
+    the CTA-pair kernel (bit-identical results; for cross-checks)."""
     _need_cuda(x2d, w)
     nb, q, p = w.shape
     if x2d.stride(-1) != 1:
@@ -244,7 +245,7 @@ def blockdiag_fwd(x2d, w, bias, in_features, out_features):
     a.in_features, a.out_features, a.dtype = int(in_features), int(out_features), _dt(x2d)
     a.x, a.ldx, a.w = x2d.data_ptr(), x2d.stride(0) if m > 1 else max(x2d.stride(0), in_features), w.data_ptr()
     a.bias = b.data_ptr() if b is not None else None
-    a.out, a.ldo = out.data_ptr(), out.stride(0)
+    a.out, a.ldo, a.variant = out.data_ptr(), out.stride(0), int(variant)
     assert w.dtype == x2d.dtype and w.is_contiguous()
     _launch("m2_blockdiag_fwd", x2d, _lib.lib().m2_blockdiag_fwd, C.byref(a))
     return out

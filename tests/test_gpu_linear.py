@@ -110,3 +110,24 @@ def test_float32_mode():
     yt = torch.empty((3, 40, 50), device=DEV)
     ops.linear_fwd(x, w, b, out=yt.permute(0, 2, 1))
     assert torch.equal(yt.permute(0, 2, 1), y)
+
+
+@pytest.mark.parametrize("M,nb,p,q", [(32768, 4, 768, 192), (1000, 4, 768, 192), (257, 4, 1536, 384), (5000, 4, 64, 1536),
+                                      (128, 2, 128, 48), (3000, 1, 256, 272), (20000, 4, 192, 1536)])
+@pytest.mark.parametrize("with_bias", [True, False])
+def test_blockdiag_pair_kernel_matches_single_cta_kernel(M, nb, p, q, with_bias):
+    """BlockdiagLinear shapes on CTA-pair tiles (narrow blocks use a narrower pair tile, wide blocks several tiles
+    with a ragged last one) against the single-CTA tensor-core kernel (bit for bit where that one applies) and
+    against float32 arithmetic with the reference's two roundings."""
+    g = torch.Generator(device="cpu").manual_seed(M + q)
+    x = torch.randn((M, nb * p), generator=g).to(DEV).bfloat16()
+    w = (torch.randn((nb, q, p), generator=g) / p ** 0.5).to(DEV).bfloat16()
+    b = torch.randn((nb * q,), generator=g).to(DEV) if with_bias else None
+    y = ops.blockdiag_fwd(x, w, b, nb * p, nb * q, variant=2)
+    if q % 64 == 0:
+        assert torch.equal(y, ops.blockdiag_fwd(x, w, b, nb * p, nb * q))
+    rows = torch.tensor(sorted({0, 127, 128, 255, 256, M // 2, M - 1} & set(range(M))), device=DEV)
+    ref = torch.einsum("mkp,kqp->mkq", x[rows].float().view(len(rows), nb, p), w.float()).reshape(len(rows), nb * q).bfloat16()
+    if b is not None:
+        ref = (ref + b.bfloat16()).float()
+    assert O.parity_error(npy(y[rows]), npy(ref.float())) < TOL
