@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(os.path.dirname(HERE), "libm2b200.so")
 SOURCES = ["m2_b200.cu"]   # single translation unit that includes the other .cu parts
 PARTS = ["abi.cu", "filter.cu", "longconv_simt.cu", "longconv_tc.cu", "longconv_tcl.cu", "longconv_tz.cu", "longconv.cu",
-         "gemm_tc.cu", "linear_tc.cu", "gemm_simt.cu", "selftest.cu", "common.cuh", "tc_common.cuh", "m2_b200.cu",
+         "gemm_tc.cu", "linear_tc.cu", "glu_pair.cu", "gemm_simt.cu", "selftest.cu", "common.cuh", "tc_common.cuh", "m2_b200.cu",
          os.path.join("..", "..", "include", "m2_b200.h")]
 
 

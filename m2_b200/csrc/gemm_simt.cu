@@ -313,6 +313,8 @@ int blockdiag_tc_launch(const m2_blockdiag_args* a, cudaStream_t st);   // gemm_
 int glu_tc_launch(const m2_glu_args* a, cudaStream_t st);
 bool blockdiag_tc_supported(const m2_blockdiag_args* a);
 bool glu_tc_supported(const m2_glu_args* a);
+bool glu_pair_supported(const m2_glu_args* a);                            // glu_pair.cu
+int glu_pair_launch(const m2_glu_args* a, cudaStream_t st);
 bool blockdiag_pair_supported(const m2_blockdiag_args* a);               // linear_tc.cu
 int blockdiag_pair_launch(const m2_blockdiag_args* a, cudaStream_t st);
 
@@ -366,6 +368,7 @@ extern "C" int m2_blockdiag_glu_fwd(const m2_glu_args* a, void* stream) {
   M2_REQUIRE(a->ldx >= a->d_model && a->ldh >= a->inter, M2_ERR_ARG,
              "m2_blockdiag_glu_fwd: row stride smaller than the row");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->variant == 0 && glu_pair_supported(a)) return glu_pair_launch(a, st);
   if (glu_tc_supported(a)) return glu_tc_launch(a, st);
   const int p = a->d_model / a->nblocks, q = 2 * a->inter / a->nblocks;
   dim3 grid((q + GT - 1) / GT, (a->m + GT - 1) / GT, a->nblocks / 2);

@@ -9,5 +9,6 @@
 #include "longconv.cu"
 #include "gemm_tc.cu"
 #include "linear_tc.cu"
+#include "glu_pair.cu"
 #include "gemm_simt.cu"
 #include "selftest.cu"
