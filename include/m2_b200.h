@@ -246,10 +246,10 @@ typedef struct {
   const void* x; long long ldx;
   const void* wg;
   void* h; long long ldh;
-  int variant;   /* 0: the library picks the kernel (CTA pairs with resident x slices when d_model / nblocks <= 192);
-                    1: always the single-CTA kernel that streams x and wg tiles through shared memory (the general
-                    one); 2: the single-CTA kernel with resident x slices where it applies.  Results are
-                    bit-identical; the variants are selectable for cross-checks */
+  int variant;   /* 0: the library picks the kernel (x slices resident in shared memory when d_model / nblocks <= 192);
+                    1: always the kernel that streams x and wg tiles through shared memory (the general one);
+                    3: CTA pairs with resident x slices where they apply.  Results are bit-identical; the variants are
+                    selectable for cross-checks */
 } m2_glu_args;
 
 int m2_blockdiag_glu_fwd(const m2_glu_args* args, void* stream);

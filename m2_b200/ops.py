@@ -253,7 +253,7 @@ def blockdiag_fwd(x2d, w, bias, in_features, out_features, variant=0):
 
 def blockdiag_glu_fwd(x2d, wg, inter, variant=0):
     """h = gelu(G[:, :inter]) * G[:, inter:], G = x2d @ blockdiag(wg)^T, without writing G.  variant=1 forces
-    the general streaming kernel (bit-identical results; for cross-checks)."""
+    the general streaming kernel, variant=3 the CTA-pair kernel (bit-identical results; for cross-checks)."""
     _need_cuda(x2d, wg)
     nb, q, p = wg.shape
     if x2d.stride(-1) != 1:

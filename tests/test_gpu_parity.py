@@ -389,9 +389,9 @@ def test_glu_mlp_tile_edges_bf16(M, D, I):
 def test_glu_resident_slices_match_streaming_kernel(M, D, I):
     x = torch.from_numpy(C.randn(70 + D, "x", (M, D))).to(DEV).bfloat16()
     wg = (torch.from_numpy(C.randn(71 + D, "w", (4, 2 * I // 4, D // 4))).to(DEV) / (D // 4) ** 0.5).bfloat16()
-    h = ops.blockdiag_glu_fwd(x, wg, I)                   # CTA pairs, x slices resident
-    h2 = ops.blockdiag_glu_fwd(x, wg, I, variant=1)       # single CTA, everything streamed
-    assert torch.equal(h, ops.blockdiag_glu_fwd(x, wg, I, variant=2))   # single CTA, x slices resident
+    h = ops.blockdiag_glu_fwd(x, wg, I)                   # x slices resident
+    h2 = ops.blockdiag_glu_fwd(x, wg, I, variant=1)       # everything streamed
+    assert torch.equal(h, ops.blockdiag_glu_fwd(x, wg, I, variant=3))   # CTA pairs, x slices resident
     torch.cuda.synchronize()
     assert torch.equal(h, h2)
     rows = torch.tensor([0, 127, 128, M // 2, M - 1], device=DEV)
