@@ -597,6 +597,15 @@ def test_embedder_chunks_match_direct_calls():
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
         _, pooled = model(ids.to(DEV), attention_mask=mask.to(DEV))
     assert np.array_equal(got[:64], pooled.float().cpu().numpy())
+    # ... and against the stock-op path: its encoder, then the reference pooler's masked mean + dense + tanh
+    # (bert/src/bert_layers.py:851-858) written out with torch ops
+    sdt = {k: v.detach() for k, v in model.state_dict().items()}
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        h = T.encoder_forward(sdt, T.embeddings_forward(sdt, ids.to(DEV)), 2)
+        m = mask.to(DEV)
+        mean = torch.sum(h * m.unsqueeze(-1), dim=1) / torch.sum(m, dim=1, keepdim=True)
+        ref = torch.tanh(torch.nn.functional.linear(mean, sdt["pooler.dense.weight"], sdt["pooler.dense.bias"]))
+    assert O.parity_error(got[:64].astype(np.float64), npy(ref)) < TOL_BF16
 
 
 @pytest.mark.parametrize("with_types,with_pos,explicit_pos", [(False, True, False), (True, True, True), (True, False, False)])
