@@ -453,7 +453,7 @@ static int add_layernorm_core(const m2_add_layernorm_args* a, const m2::LnGather
     // channel's run of them is one 32-byte sector
     int rows = 8, threads = 256, rpw = 1;
     if (a->out_tm_f16) {
-      rows = a->seq_len % 16 == 0 ? 16 : 8;
+      rows = a->seq_len % 32 == 0 && a->n <= 768 ? 32 : a->seq_len % 16 == 0 ? 16 : 8;   // 32 rows: 64-byte runs per channel
       threads = rows >= 16 ? 512 : 256;
       rpw = rows / (threads / 32);
     }
