@@ -12,6 +12,7 @@ from ._lib import M2_BF16, M2_F16, M2_F32
 
 LAUNCHES = 0          # kernels of this library launched since the counter was last reset
 PROFILE = None        # a LaunchProfile while a benchmark wants per-kernel device times
+NVTX = False          # True: every launch sits in an NVTX range named after its entry point (timeline tools)
 
 
 class LaunchProfile:
@@ -43,7 +44,11 @@ def _launch(name, tensor, fn, *args):
         if prof is not None:
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record(st)
+        if NVTX:
+            torch.cuda.nvtx.range_push(name)
         rc = fn(*args, C.c_void_p(st.cuda_stream))
+        if NVTX:
+            torch.cuda.nvtx.range_pop()
         if prof is not None:
             e.record(st)
             prof.events.setdefault(name, []).append((s, e))
