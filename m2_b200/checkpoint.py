@@ -14,8 +14,11 @@ and reproduce the same three operations on any state dict of the m2_b200 / refer
 * `pos_emb.t` and `embeddings.position_ids` are dropped, so the longer model keeps the time axis and ids
   its own constructor built (the reference deletes them and loads with strict=False).
 
-The reference's functions cannot be imported for a value comparison (they pull in sentence_transformers,
-rank_bm25 and a `breakpoint()`), so these adapters are tested against the semantics stated above.
+As committed, `from_composer` stops at its own shape assertions for every checkpoint (it tiles the position table
+five times and then asserts 32768 rows) and `expand_8k_model_to_32k` opens with a `breakpoint()`.  With `assert`
+statements switched off (python -O) `from_composer` runs through: tests/golden/checkpoint_expand.npz holds what it
+loads into a model from a fabricated short checkpoint -- five copies of the position table, `pos_emb.z` sixteen
+times as long with copies in slots 1, 2, 3 -- and the adapters here are held to those tensors bit for bit.
 """
 from __future__ import annotations
 
@@ -40,24 +43,28 @@ def strip_prefix(state_dict, prefixes=("model.bert.", "model.", "bert.")):
     return out
 
 
-def expand_sequence_length(state_dict, new_len, *, z_first_slot=1, z_copies=3):
+def expand_sequence_length(state_dict, new_len, *, position_len=None, z_first_slot=1, z_copies=3):
     """A copy of `state_dict` stretched to sequences of `new_len` positions (see the module docstring).
+
+    position_len: rows of the tiled position table when they differ from `new_len` (the reference tiles the table
+    five times while it stretches the filters sixteen-fold); default `new_len`.
 
     z_first_slot / z_copies: which slots of the old length receive a copy of `pos_emb.z`; copies that
     would fall outside the new length are dropped.  Tensors that already have `new_len` positions are
     left alone; a `new_len` that is not a multiple of the old length raises ValueError.
     """
     new_len = int(new_len)
+    position_len = new_len if position_len is None else int(position_len)
     out = {}
     for k, v in state_dict.items():
         if _T_KEY.search(k) or k.endswith("embeddings.position_ids"):
             continue                                           # rebuilt by the longer model's constructor
         if k.endswith("embeddings.position_embeddings.weight"):
             l0 = v.shape[0]
-            if l0 != new_len:
-                if new_len % l0:
-                    raise ValueError(f"{k}: new length {new_len} is not a multiple of {l0}")
-                v = v.repeat(new_len // l0, 1)
+            if l0 != position_len:
+                if position_len % l0:
+                    raise ValueError(f"{k}: new length {position_len} is not a multiple of {l0}")
+                v = v.repeat(position_len // l0, 1)
         elif _Z_KEY.search(k):
             l0 = v.shape[1]
             if l0 != new_len:

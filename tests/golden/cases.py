@@ -158,3 +158,23 @@ def pooler_inputs():
     w = randn(c["seed"], "w", (c["D"], c["D"])) * 0.2
     bias = randn(c["seed"], "b", (c["D"],)) * 0.1
     return h, mask, w.astype(np.float32), bias.astype(np.float32)
+
+
+# Checkpoint of a short model as the reference's `BertForMaskedLM.from_composer` expects it (bert/src/bert_layers.py:
+# 1087-1209) when `expand_positional_embeddings` is set: 12 layers, keys under `model.bert.`.  The function tiles the
+# position table five times and stretches every `pos_emb.z` sixteen-fold, so the receiving model has 5 L0 positions
+# and filters of 16 L0 steps.  Generated by make_golden.py into checkpoint_expand.npz.
+CKPT = dict(seed=61, L0=16, D=8, emb=5, layers=12, pos_copies=5, z_factor=16)
+
+
+def checkpoint_expand_inputs():
+    """name -> array of the short model's entries the expansion touches."""
+    c = CKPT
+    sd = {"model.bert.embeddings.position_embeddings.weight": randn(c["seed"], "pe", (c["L0"], c["D"])),
+          "model.bert.embeddings.position_ids": np.arange(c["L0"], dtype=np.int64)[None, :]}
+    for i in range(c["layers"]):
+        for fn in ("filter_fn", "filter_fn2"):
+            p = f"model.bert.encoder.layer.{i}.attention.{fn}.pos_emb."
+            sd[p + "z"] = randn(c["seed"], p + "z", (1, c["L0"], c["emb"]))
+            sd[p + "t"] = np.linspace(0.0, 1.0, c["L0"], dtype=np.float32)[None, :, None]
+    return sd

@@ -4,6 +4,9 @@ Usage (only where the reference checkout is mounted):
 
     python -m tests.golden.make_golden /path/to/reference
 
+(the checkpoint-expansion fixture is made by a child interpreter this command starts, see
+``run_checkpoint_expand``)
+
 The reference's modules are imported in place with two shims (a stub ``opt_einsum``,
 whose ``contract`` the path binds but never calls, and a bare ``src`` package so that
 ``bert/src/__init__.py`` -- which needs MosaicML Composer -- is skipped).  Weights and
@@ -204,7 +207,54 @@ def run_pooler(ref):
     return store
 
 
+def run_checkpoint_expand(ref):
+    """The reference's `BertForMaskedLM.from_composer` with `expand_positional_embeddings` on the fabricated short
+    checkpoint of cases.checkpoint_expand_inputs().  As committed the function stops at its own shape assertions for
+    every input (five copies of a position table never make the 32768 rows it asserts), so this runs in a child
+    interpreter started with -O, which drops `assert` statements and leaves the rest of the reference untouched."""
+    import tempfile
+    _, _, bert_layers, BertConfig = ref
+    c = C.CKPT
+    sd = {k: torch.from_numpy(np.asarray(v)).clone() for k, v in C.checkpoint_expand_inputs().items()}
+    conf = BertConfig(vocab_size=64, hidden_size=c["D"], intermediate_size=16, num_hidden_layers=c["layers"],
+                      num_attention_heads=4, max_position_embeddings=c["pos_copies"] * c["L0"],
+                      use_glu_mlp=True, use_monarch_mlp=True, monarch_mlp_nblocks=4,
+                      monarch_mixer_sequence_mixing=True, residual_long_conv=True,
+                      bidirectional=True, use_positional_encodings=True,
+                      hyena_filter_order=16, hyena_emb_dim=c["emb"], hyena_w=10,
+                      hyena_wd=0.1, hyena_lr_pos_emb=1e-5, long_conv_l_max=c["z_factor"] * c["L0"],
+                      long_conv_kernel_learning_rate=1e-3, hyena_filter_dropout=0.0,
+                      hyena_training_additions=False, expand_positional_embeddings=True)
+    with tempfile.TemporaryDirectory() as d:
+        path = os.path.join(d, "short_model.pt")
+        torch.save({"state": {"model": sd}}, path)
+        with contextlib.redirect_stdout(io.StringIO()):
+            torch.manual_seed(0)
+            fresh = bert_layers.BertForMaskedLM(conf).state_dict()
+            model = bert_layers.BertForMaskedLM.from_composer(path, config=conf)
+    loaded = model.state_dict()
+    store = {}
+    for k, v in loaded.items():
+        if k.endswith("position_embeddings.weight") or k.endswith("pos_emb.z"):
+            store[k] = v.numpy()
+    # the time axis and the position ids stay the longer model's own: the same as a freshly built model has
+    for k in ("bert.encoder.layer.0.attention.filter_fn.pos_emb.t", "bert.encoder.layer.11.attention.filter_fn2.pos_emb.t",
+              "bert.embeddings.position_ids"):
+        if not torch.equal(loaded[k], fresh[k]):               # (`assert` is off in this interpreter)
+            raise RuntimeError(k + ": differs from the freshly built model's")
+        store[k] = loaded[k].numpy()
+    return store
+
+
 def main():
+    if len(sys.argv) >= 3 and sys.argv[1] == "--checkpoint-expand":
+        if __debug__:
+            sys.exit("--checkpoint-expand needs an interpreter started with -O")
+        here = os.path.dirname(os.path.abspath(__file__))
+        store = run_checkpoint_expand(import_reference(sys.argv[2]))
+        np.savez_compressed(os.path.join(here, "checkpoint_expand.npz"), **store)
+        print("checkpoint_expand", len(store), "arrays")
+        return
     if len(sys.argv) < 2:
         sys.exit("usage: python tests/golden/make_golden.py <path to a checkout of HazyResearch/m2>")
     ref_root = sys.argv[1]
@@ -219,6 +269,8 @@ def main():
     store = run_pooler(ref)
     np.savez_compressed(os.path.join(here, "pooler.npz"), **store)
     print("pooler", {k: v.shape for k, v in store.items()})
+    import subprocess
+    subprocess.run([sys.executable, "-O", "-m", "tests.golden.make_golden", "--checkpoint-expand", ref_root], check=True)
 
 
 if __name__ == "__main__":

@@ -195,6 +195,38 @@ def test_expand_sequence_length_roundtrip_into_longer_model():
         checkpoint.load_expanded(dst, big)
 
 
+def test_expand_sequence_length_matches_the_reference_loader():
+    """Bit-for-bit against what the reference's `BertForMaskedLM.from_composer` (bert/src/bert_layers.py:1087-1209,
+    `expand_positional_embeddings`) loaded from the same fabricated short checkpoint
+    (tests/golden/checkpoint_expand.npz, made by tests/golden/make_golden.py)."""
+    import torch
+    from m2_b200 import checkpoint
+    from m2_b200.encoder import M2BertConfig, M2BertModel
+    from tests.golden import cases as C
+    c = C.CKPT
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "checkpoint_expand.npz"))
+    sd = {k: torch.from_numpy(np.asarray(v)).clone() for k, v in C.checkpoint_expand_inputs().items()}
+    big = checkpoint.expand_sequence_length(checkpoint.strip_prefix(sd, prefixes=("model.",)),
+                                            c["z_factor"] * c["L0"], position_len=c["pos_copies"] * c["L0"])
+    touched = [k for k in gold.files if k.endswith("position_embeddings.weight") or k.endswith("pos_emb.z")]
+    assert len(touched) == 1 + 2 * c["layers"] and set(touched) == set(big)   # t and position_ids are dropped
+    for k in touched:
+        assert big[k].dtype == torch.float32 and big[k].shape == gold[k].shape, k
+        assert np.array_equal(big[k].numpy(), gold[k]), k
+    # loaded into the longer drop-in model, the untouched entries are the constructor's own, as in the reference
+    torch.manual_seed(0)
+    dst = M2BertModel(M2BertConfig(vocab_size=64, hidden_size=c["D"], intermediate_size=16, num_hidden_layers=c["layers"],
+                                   hyena_filter_order=16, hyena_emb_dim=c["emb"], monarch_mlp_nblocks=4,
+                                   max_position_embeddings=c["pos_copies"] * c["L0"],
+                                   long_conv_l_max=c["z_factor"] * c["L0"]))
+    part = {k[len("bert."):]: v for k, v in big.items()}
+    res = dst.load_state_dict(part, strict=False)
+    assert not res.unexpected_keys
+    got = dst.state_dict()
+    for k in gold.files:
+        assert np.array_equal(got[k[len("bert."):]].numpy(), gold[k]), k
+
+
 def test_flash_fft_attribute_protocol_is_accepted():
     """The reference's encoder pokes `flashfft` / `use_flash_fft` onto the filters
     (bert/src/bert_layers.py:616-626); the drop-in filters accept and ignore them."""
