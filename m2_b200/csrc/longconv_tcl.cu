@@ -69,6 +69,16 @@ struct Geo {
   static constexpr int DATA_BYTES =
       ((cmax(cmax(cmax(R * 32, 2 * N3 * SBO2), cmax(2 * N2 * SBO3, T3T * TILE3)),
              cmax(cmax(2 * N3 * SBO4, (R / 8) * SBO5), 4 * YF)) + 127) / 128) * 128;
+  // Variant with asynchronous staging of the global rows (see the kernel): per slot
+  //   [0, A_RA)        the operand regions' first part / the bf16 output buffer (16-byte pad after every 128 bytes)
+  //   [A_RA, +32 R)    one raw row (x1, then u): overlaps the operand regions, used only between passes
+  //   [A_SB, +32 R)    one raw row beyond every operand region (v; x2 and the gated result during the passes)
+  static constexpr int DEXT =
+      ((cmax(cmax(cmax(R * 32, 2 * N3 * SBO2), cmax(2 * N2 * SBO3, T3T * TILE3)),
+             cmax(2 * N3 * SBO4, (R / 8) * SBO5)) + 127) / 128) * 128;
+  static constexpr int A_RA = 36 * R;
+  static constexpr int A_SB = cmax(DEXT, A_RA + 32 * R);
+  static constexpr int A_SLOT = A_SB + 32 * R;
   static constexpr int COLS = cmax(T1T * 32, cmax(T2T * K2, T3T * K3));
   static constexpr int TCOLS = (SLOTS * COLS <= 32) ? 32 : (SLOTS * COLS <= 64) ? 64 : (SLOTS * COLS <= 128) ? 128
                                : (SLOTS * COLS <= 256) ? 256 : 512;
@@ -91,6 +101,8 @@ struct Geo {
   static constexpr int HDR_BYTES = T2B_OFF + N2 * T2B_PITCH;
   static constexpr int HDR_FLOATS = HDR_BYTES / 4;
   static constexpr int SMEM = SLOTS * DATA_BYTES + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
+  static constexpr int SMEM_A = SLOTS * A_SLOT + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
+  static constexpr bool CAN_ASYNC = TS == 1 && SMEM_A <= 227 * 1024;
   static_assert(R % 128 == 0 && N3 % 8 == 0 && N2 % 8 == 0, "row tiles must be full");
   static_assert(SLOTS * COLS <= 512, "accumulators exceed tensor memory");
   static_assert(T1T % TS == 0 && T2T % TS == 0 && T3T % TS == 0, "tile split must divide every stage");
@@ -466,7 +478,16 @@ __device__ __forceinline__ void hop_rows(uint32_t tml, int tile_cols, int ts, F&
     }
   }
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+// 16-byte asynchronous copy global -> shared (L2 only), and the group bookkeeping of the issuing thread
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void sts16(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
+}
 
 // depthwise 3-tap conv taps of one channel, rounded to bf16 as autocast rounds the conv's parameters
 struct Taps { float w0, w1, w2, b; };
@@ -594,9 +615,17 @@ __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t dat
   }
 }
 
-template <typename G, typename TU>
+// ASYNC (geometries with room for it; 2-byte u, 16-byte aligned rows, L % 8 == 0, residual conv rounded to bf16):
+// no thread ever waits for a global load it has just issued.  Every row this slot reads is copied into the slot's
+// shared memory with cp.async one phase ahead -- x2 while the first filter's transform runs, u during the first
+// epilogue, the next sequence's x1 / v during and after the second epilogue -- the output buffer holds bf16, and the
+// first filter's gated result stays in shared memory until the second epilogue adds the residual conv and writes
+// the output once.
+template <typename G, typename TU, bool ASYNC>
 __global__ void __launch_bounds__(G::THREADS, 1)
 longconv_tcl_kernel(const Params P) {
+  static_assert(!ASYNC || (G::CAN_ASYNC && sizeof(TU) == 2), "asynchronous staging: geometry / element size");
+  constexpr int SLOT_BYTES = ASYNC ? G::A_SLOT : G::DATA_BYTES;
   constexpr int N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3, TS = G::TS, TPS = G::TPS;
   constexpr int LIT = 2 * R / TPS;                 // 8-step chunks per thread in the load phase
   constexpr int LB = LIT < 4 ? LIT : 4;            // ... of which this many have their global loads in flight together
@@ -605,7 +634,7 @@ longconv_tcl_kernel(const Params P) {
   static_assert(LIT % LB == 0 && EIT % EB == 0, "batching of the memory phases");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~(uintptr_t)127);
-  unsigned char* hdrb = smem + G::SLOTS * G::DATA_BYTES;
+  unsigned char* hdrb = smem + G::SLOTS * SLOT_BYTES;
   uint64_t* bars = reinterpret_cast<uint64_t*>(hdrb + G::HDR_BYTES);       // per slot: ops, mma, w
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * G::SLOTS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -642,8 +671,10 @@ longconv_tcl_kernel(const Params P) {
   uint64_t* bar_w = bar_ops + 2;
   const uint32_t tm = *tmem_slot + slot * G::COLS;
   const uint32_t tml = tm + ((uint32_t)((warp & 3) * 32) << 16);
-  const uint32_t data = tc::smem_u32(smem + slot * G::DATA_BYTES);
-  float* Y = reinterpret_cast<float*>(smem + slot * G::DATA_BYTES);
+  const uint32_t data = tc::smem_u32(smem + slot * SLOT_BYTES);
+  float* Y = reinterpret_cast<float*>(smem + slot * SLOT_BYTES);
+  const uint32_t RA = data + G::A_RA, SB = data + G::A_SB;     // raw-row regions of the asynchronous variant
+  const int lane = tid & 31;
   const uint32_t hdr = tc::smem_u32(hdrb);
   uint32_t ph_ops = 0, ph_mma = 0, ph_w = 0;
   bool ok = true;
@@ -674,6 +705,26 @@ longconv_tcl_kernel(const Params P) {
     rg = (q >> 6) * 4 + ((q >> 3) & 3);
   };
   const int stride = gridDim.x * G::SLOTS;
+  constexpr int CPN = R / 8;                       // 16-byte chunks per n1 of a raw 2-byte row
+  // ASYNC: copies of the steps below L of a raw row.  Swizzled: chunk c = (R / 8) n1 + rg lands at chunk
+  // c ^ (n1 & 7), so that a quarter warp of the load phase (8 values of n1, one rg) reads 8 different bank groups.
+  auto stage_swz = [&](uint32_t dst, const void* row) {
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(row);
+    for (int c = sl; 8 * c < P.L; c += TPS) cp_async16(dst + 16 * (c ^ ((c / CPN) & 7)), src + 16 * c);
+  };
+  auto stage_lin = [&](uint32_t dst, const void* row) {
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(row);
+    for (int c = sl; 8 * c < P.L; c += TPS) cp_async16(dst + 16 * c, src + 16 * c);
+  };
+  auto x1_of = [&](int rid) { return P.xin + (long long)(rid % P.B) * P.xsb + (long long)(rid / P.B) * P.xsc; };
+  if constexpr (ASYNC) {
+    const int r0 = blockIdx.x * G::SLOTS + slot;
+    if (r0 < P.rows) {
+      stage_swz(RA, x1_of(r0));
+      stage_swz(SB, x1_of(r0) + 2 * (long long)P.D * P.xsc);
+    }
+    cp_async_commit();
+  }
   // rows of one channel are neighbours in the walk (batch index fastest): the slots working at the same time share
   // a few channels' spectrum tables, which then come from L2
   for (int rowid = blockIdx.x * G::SLOTS + slot; rowid < P.rows && ok; rowid += stride) {
@@ -683,23 +734,59 @@ longconv_tcl_kernel(const Params P) {
     const __nv_bfloat16* vrow = x2row + (long long)P.D * P.xsc;
     __nv_bfloat16* orow = P.out + (long long)b * P.osb + (long long)ch * P.osc;
     const TU* urow = reinterpret_cast<const TU*>(P.u) + (long long)b * P.usb + (long long)ch * P.usc;
-    if (rowid + stride < P.rows) {
-      // the next sequence of this slot: ask for its rows now, they are in L2 when its turn comes
-      const int nr = rowid + stride, nch = nr / P.B, nb = nr % P.B;
-      const __nv_bfloat16* nx = P.xin + (long long)nb * P.xsb + (long long)nch * P.xsc;
-      const unsigned char* nu = reinterpret_cast<const unsigned char*>(reinterpret_cast<const TU*>(P.u) + (long long)nb * P.usb + (long long)nch * P.usc);
-      for (int o = sl * 64; o < P.L; o += TPS * 64) {                      // 128-byte lines of the bf16 rows
-        prefetch_l2(nx + o);
-        prefetch_l2(nx + (long long)P.D * P.xsc + o);
-        prefetch_l2(nx + 2 * (long long)P.D * P.xsc + o);
-      }
-      if (P.nf == 2)
-        for (int o = sl * 128; o < P.L * (int)sizeof(TU); o += TPS * 128) prefetch_l2(nu + o);
+    if constexpr (ASYNC) {
+      cp_async_wait<0>();                          // this sequence's x1 (RA) and v (SB)
+      LCL_BARRIER()
     }
 
     for (int f = 0; f < P.nf && ok; ++f) {
+      const float ig = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);          // 2^-e of this channel
       // ---------------- F1 operand: a[R n1 + r] as fp16, one 16-byte chunk = 8 consecutive r of one n1 ----------------
-      if (f == 0) {
+      if (ASYNC && f == 0) {
+        const Taps2 Tx = load_taps2(P.sw, P.sb, ch), Tv = load_taps2(P.sw, P.sb, 2 * P.D + ch);
+#pragma unroll 2
+        for (int it = 0; it < LIT; ++it) {
+          int n1, rg;
+          chunk_of(it * TPS + sl, n1, rg);
+          const int t0 = R * n1 + 8 * rg, c = t0 >> 3;
+          const bool in = t0 < P.L;
+          uint4 x = make_uint4(0u, 0u, 0u, 0u), v = x;
+          if (in) {
+            const uint32_t o = 16 * (c ^ (n1 & 7));
+            x = lds128(RA + o); v = lds128(SB + o);
+          }
+          // the two steps before the chunk: the lane 8 below holds chunk (n1, rg - 1); the first quarter warp reads them
+          uint32_t hx = __shfl_up_sync(0xffffffffu, x.w, 8), hv = __shfl_up_sync(0xffffffffu, v.w, 8);
+          if (lane < 8) {
+            hx = hv = 0u;
+            if (in && c > 0) {
+              const int pc = c - 1;
+              const uint32_t o = 16 * (pc ^ ((pc / CPN) & 7)) + 12;
+              hx = lds32(RA + o); hv = lds32(SB + o);
+            }
+          }
+          const uint32_t wx[5] = {hx, x.x, x.y, x.z, x.w}, wv[5] = {hv, v.x, v.y, v.z, v.w};
+          uint32_t cx[4], cv[4], h[4];
+          conv_packed<8>(Tx, wx, cx);
+          conv_packed<8>(Tv, wv, cv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) h[j] = in ? bf2_to_h2(bf2_mul(cv[j], cx[j])) : 0u;   // steps from L on are zero padding
+          sts128(data + rg * G::SBO1 + n1 * 16, h[0], h[1], h[2], h[3]);
+        }
+      } else if (ASYNC) {
+#pragma unroll 2
+        for (int it = 0; it < LIT; ++it) {
+          int n1, rg;
+          chunk_of(it * TPS + sl, n1, rg);
+          const int t0 = R * n1 + 8 * rg, c = t0 >> 3;
+          uint4 w = make_uint4(0u, 0u, 0u, 0u);
+          if (t0 < P.L) w = lds128(RA + 16 * (c ^ (n1 & 7)));
+          if (!P.u_f16) {
+            w.x = bf2_to_h2(w.x); w.y = bf2_to_h2(w.y); w.z = bf2_to_h2(w.z); w.w = bf2_to_h2(w.w);
+          }
+          sts128(data + rg * G::SBO1 + n1 * 16, w.x, w.y, w.z, w.w);
+        }
+      } else if (f == 0) {
         const Taps2 Tx = load_taps2(P.sw, P.sb, ch), Tv = load_taps2(P.sw, P.sb, 2 * P.D + ch);
 #pragma unroll 1
         for (int it0 = 0; it0 < LIT; it0 += LB) {
@@ -776,6 +863,12 @@ longconv_tcl_kernel(const Params P) {
         }
       }
       LCL_STAGE(0)
+      if constexpr (ASYNC) {
+        if (f == 0) {                              // every thread of the slot is done with the raw x1 / v rows
+          stage_lin(SB, x2row);
+          cp_async_commit();
+        }
+      }
 
       // ---------------- hop 1: x w^{r (k1 + 1/2)}; rows r = (n2, n3) -> operand rows (k1, n3), K = (ri, n2) ----------------
       hop_rows<16, G::T1T / TS, TS>(tml, 32, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k1 = 8 g ..
@@ -899,6 +992,84 @@ longconv_tcl_kernel(const Params P) {
       tc::tc_fence_before();
       LCL_STAGE(5)
 
+      if constexpr (ASYNC) {
+        const bool last = f + 1 == P.nf;
+        // the operand regions are free: the next raw row goes into RA while this pass finishes
+        if (!last) stage_swz(RA, urow);
+        else if (rowid + stride < P.rows) stage_swz(RA, x1_of(rowid + stride));
+        cp_async_commit();
+        // x2's two steps before each chunk come from the lane below; lane 0 fetches its own (L2: the row was just copied)
+        uint32_t hh[LIT];
+#pragma unroll
+        for (int it = 0; it < LIT; ++it) {
+          const int c = it * TPS + sl;
+          hh[it] = 0u;
+          if (f == 0 && lane == 0 && c > 0 && 8 * c < P.L) hh[it] = __ldg(reinterpret_cast<const uint32_t*>(x2row + 8 * c - 2));
+        }
+        if (f == 0) cp_async_wait<1>();            // this thread's pieces of x2 (all but the newest group)
+        // ---- hop 6: bf16(y 2^-e) at time R n1 + r; step t lives at element t + 8 (t / 64): neither these 2-byte
+        // scattered stores nor the epilogue's 16-byte reads meet bank conflicts
+#pragma unroll 1
+        for (int t = ts; t < G::T1T; t += TS) {
+          uint32_t z[16];
+          tc::tmem_ld16(tml + 16 * t, z);
+          tc::tmem_ld_wait();
+          const int j5 = 16 * t + (l >> 3), n2 = 8 * (j5 / N3) + (l & 7), n3 = j5 % N3;
+          const int r = N3 * n2 + n3;
+          const uint32_t yp = data + 2 * (r + 8 * (r >> 6));
+#pragma unroll
+          for (int n1 = 0; n1 < 16; n1 += 2) {
+            const uint32_t pk = pack_bf2(__uint_as_float(z[n1]) * ig, __uint_as_float(z[n1 + 1]) * ig);
+            sts16(yp + n1 * (2 * (R + R / 8)), pk & 0xffffu);
+            sts16(yp + (n1 + 1) * (2 * (R + R / 8)), pk >> 16);
+          }
+        }
+        tc::tc_fence_before();
+        LCL_BARRIER()
+        if (f == 0) {
+          // ---- first epilogue: (conv + bias term as bf16) x short conv of x2; kept in SB when a residual pass follows
+          const Taps2 T2 = load_taps2(P.sw, P.sb, P.D + ch);
+#pragma unroll
+          for (int it = 0; it < LIT; ++it) {
+            const int c = it * TPS + sl, t0 = 8 * c;
+            const bool in = t0 < P.L;
+            uint4 x = make_uint4(0u, 0u, 0u, 0u);
+            if (in) x = lds128(SB + 16 * c);
+            uint32_t h = __shfl_up_sync(0xffffffffu, x.w, 1);
+            if (lane == 0) h = hh[it];
+            if (in) {
+              const uint32_t wx[5] = {h, x.x, x.y, x.z, x.w};
+              uint32_t c2[4];
+              conv_packed<8>(T2, wx, c2);
+              const uint4 y = lds128(data + 16 * c + 16 * (c >> 3));
+              const uint4 o = make_uint4(bf2_mul(y.x, c2[0]), bf2_mul(y.y, c2[1]), bf2_mul(y.z, c2[2]), bf2_mul(y.w, c2[3]));
+              if (last) *reinterpret_cast<uint4*>(orow + t0) = o;
+              else sts128(SB + 16 * c, o.x, o.y, o.z, o.w);
+            }
+          }
+        } else {
+          // ---- second epilogue: gated result (SB) + residual conv (bf16), one 16-byte store per 8 steps
+#pragma unroll
+          for (int it = 0; it < LIT; ++it) {
+            const int c = it * TPS + sl, t0 = 8 * c;
+            if (t0 < P.L) {
+              const uint4 y = lds128(data + 16 * c + 16 * (c >> 3));
+              const uint4 pv = lds128(SB + 16 * c);
+              *reinterpret_cast<uint4*>(orow + t0) =
+                  make_uint4(pack_bf2(bf_lo(pv.x) + bf_lo(y.x), bf_hi(pv.x) + bf_hi(y.x)),
+                             pack_bf2(bf_lo(pv.y) + bf_lo(y.y), bf_hi(pv.y) + bf_hi(y.y)),
+                             pack_bf2(bf_lo(pv.z) + bf_lo(y.z), bf_hi(pv.z) + bf_hi(y.z)),
+                             pack_bf2(bf_lo(pv.w) + bf_lo(y.w), bf_hi(pv.w) + bf_hi(y.w)));
+            }
+          }
+        }
+        if (!last) cp_async_wait<0>();             // u has had the whole epilogue to arrive
+        LCL_BARRIER()                              // output buffer, SB (after the last pass) and RA's copy are settled
+        if (last) {
+          if (rowid + stride < P.rows) stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
+          cp_async_commit();
+        }
+      } else {
       // ---------------- hop 6: y[R n1 + r] (float32) into shared memory in time order, 4 floats of padding after every 32
       // (position t lives at t + 4 (t / 32): the scattered writes below and the float4 reads of the epilogue are both
       // free of bank conflicts) ----------------
@@ -971,11 +1142,13 @@ longconv_tcl_kernel(const Params P) {
         }
       }
       LCL_BARRIER()                                          // the y buffer is free again
+      }
     }
   }
 #undef LCL_STAGE
 #undef LCL_BARRIER
 
+  if constexpr (ASYNC) cp_async_wait<0>();         // nothing may still be landing when the block gives its memory back
   __syncthreads();
   if (warp == 0) {
     tc::tc_fence_after();
@@ -1004,16 +1177,17 @@ static int launch_spectrum(int D, int R, const float* k, float* spec, cudaStream
   return M2_OK;
 }
 
-template <typename G, typename TU>
+template <typename G, typename TU, bool ASYNC = false>
 static int launch_conv(const Params& P, cudaStream_t st) {
-  auto kern = longconv_tcl_kernel<G, TU>;
-  M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G::SMEM));
+  auto kern = longconv_tcl_kernel<G, TU, ASYNC>;
+  constexpr int SMEM = ASYNC ? G::SMEM_A : G::SMEM;
+  M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int need = (P.rows + G::SLOTS - 1) / G::SLOTS;
   const int grid = need < sms ? need : sms;
-  kern<<<grid, G::THREADS, G::SMEM, st>>>(P);
+  kern<<<grid, G::THREADS, SMEM, st>>>(P);
   M2_LAUNCH_CHECK("longconv_tcl_kernel");
   return M2_OK;
 }
@@ -1074,8 +1248,17 @@ int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
     M2_REQUIRE(m2_aligned(a->u, ua) && a->u_sc % 4 == 0 && a->u_sb % 4 == 0, M2_ERR_ALIGN,
                "m2_longconv_fwd: kind 2 needs rows of u aligned to four elements");
   }
-  if (a->seq_len <= 2048) return ubf ? launch_conv<Geo4k, __nv_bfloat16>(P, st) : launch_conv<Geo4k, float>(P, st);
-  if (a->seq_len <= 8192) return ubf ? launch_conv<Geo16k, __nv_bfloat16>(P, st) : launch_conv<Geo16k, float>(P, st);
+  // rows staged through shared memory ahead of their use: 16-byte pieces of every row, bf16 output buffer
+  const bool staged = P.al16 && a->seq_len % 8 == 0 && a->out_sc % 8 == 0 && a->out_sb % 8 == 0 && m2_aligned(a->out, 16) &&
+                      (a->n_filters == 1 || (ubf && P.yu_bf16));
+  if (a->seq_len <= 2048) {
+    if (staged) return launch_conv<Geo4k, __nv_bfloat16, true>(P, st);
+    return ubf ? launch_conv<Geo4k, __nv_bfloat16>(P, st) : launch_conv<Geo4k, float>(P, st);
+  }
+  if (a->seq_len <= 8192) {
+    if (staged) return launch_conv<Geo16k, __nv_bfloat16, true>(P, st);
+    return ubf ? launch_conv<Geo16k, __nv_bfloat16>(P, st) : launch_conv<Geo16k, float>(P, st);
+  }
   return ubf ? launch_conv<Geo64k, __nv_bfloat16>(P, st) : launch_conv<Geo64k, float>(P, st);
 }
 

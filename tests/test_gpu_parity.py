@@ -484,6 +484,32 @@ def test_longconv_long_row_family(L, D, B, residual, u_bf16):
     assert max(errs) < TOL_BF16, errs
 
 
+@pytest.mark.parametrize("L,D,B", [(8192, 40, 16), (4104, 24, 5), (2048, 96, 9), (1000, 16, 3), (136, 8, 2)])
+@pytest.mark.parametrize("residual", [True, False])
+def test_longconv_long_rows_staged_and_direct_paths_agree(L, D, B, residual):
+    """Rows on 16-byte boundaries take the variant that stages every global row in shared memory ahead of its use;
+    an output whose rows start 8 bytes off takes the variant with direct loads.  Same arithmetic, same bits; enough
+    rows that every slot of every block walks several sequences."""
+    cfg = dict(C.CASES["mixer_small"], L=L, l_max=L, D=D, B=B, order=32, residual=residual, seed=72)
+    m, sd = build_mixer(cfg, DEV)
+    g = torch.Generator().manual_seed(L + 1)
+    xin = (0.6 * torch.randn((B, 3 * D, L), generator=g)).to(DEV).bfloat16().transpose(1, 2)
+    u = torch.randn((B, D, L), generator=g).to(DEV).bfloat16().transpose(1, 2) if residual else None
+    filters = [m.filter_fn] + ([m.filter_fn2] if residual else [])
+    specs = [f.spectrum(L, True, 2) for f in filters]
+    outs = []
+    for off in (0, 4):
+        flat = torch.full((B * D * L + 8,), float("nan"), dtype=torch.bfloat16, device=DEV)
+        out = flat[off:off + B * D * L].view(B, D, L).transpose(1, 2)
+        ops.longconv_fwd(xin, u, m.short_filter.weight, m.short_filter.bias, specs,
+                         [f.conv_bias() for f in filters], kind=2, bf16_rounding=True, out=out, yu_bf16=True)
+        assert torch.isnan(flat[:off].float()).all() and torch.isnan(flat[off + B * D * L:].float()).all()
+        outs.append(out)
+    assert ops.device_status() == 0
+    assert torch.isfinite(outs[0].float()).all()
+    assert torch.equal(outs[0], outs[1])
+
+
 # ---- Toeplitz-GEMM family (batch as the M dimension, channel-major rows) against the CUDA-core family ----
 @pytest.mark.parametrize("L,D,B", [(128, 16, 130), (128, 8, 256), (104, 16, 64), (72, 8, 200), (64, 8, 128),
                                    (16, 8, 64), (40, 8, 100)])
