@@ -101,7 +101,7 @@ struct Geo {
   static constexpr int HDR_BYTES = T2B_OFF + N2 * T2B_PITCH;
   static constexpr int HDR_FLOATS = HDR_BYTES / 4;
   static constexpr int SMEM = SLOTS * DATA_BYTES + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
-  static constexpr int SMEM_A = SLOTS * A_SLOT + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
+  static constexpr int SMEM_A = SLOTS * A_SLOT + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128 + SLOTS * 64;   // + per-slot scalars
   static constexpr bool CAN_ASYNC = TS == 1 && SMEM_A <= 227 * 1024;
   static_assert(R % 128 == 0 && N3 % 8 == 0 && N2 % 8 == 0, "row tiles must be full");
   static_assert(SLOTS * COLS <= 512, "accumulators exceed tensor memory");
@@ -482,6 +482,9 @@ __device__ __forceinline__ void hop_rows(uint32_t tml, int tile_cols, int ts, F&
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -675,6 +678,9 @@ longconv_tcl_kernel(const Params P) {
   float* Y = reinterpret_cast<float*>(smem + slot * SLOT_BYTES);
   const uint32_t RA = data + G::A_RA, SB = data + G::A_SB;     // raw-row regions of the asynchronous variant
   const int lane = tid & 31;
+  // ASYNC: the sequence's scalars, copied ahead like its rows: [4 g + k] short-conv taps w0 w1 w2 b of x1, x2, v
+  // (g = 0, 1, 2); [12 + f] 2^-e of filter f's channel; [14 + f] its bias
+  volatile float* prm = reinterpret_cast<volatile float*>(tmem_slot + 4) + 16 * slot;
   const uint32_t hdr = tc::smem_u32(hdrb);
   uint32_t ph_ops = 0, ph_mma = 0, ph_w = 0;
   bool ok = true;
@@ -716,10 +722,25 @@ longconv_tcl_kernel(const Params P) {
     const unsigned char* src = reinterpret_cast<const unsigned char*>(row);
     for (int c = sl; 8 * c < P.L; c += TPS) cp_async16(dst + 16 * c, src + 16 * c);
   };
+  auto stage_scalars = [&](int rid) {
+    if (sl < 16) {
+      const int c = rid / P.B, g = sl >> 2, k = sl & 3, f = sl & 1;
+      const float* src = sl < 12 ? (k < 3 ? P.sw + 3 * (g * P.D + c) + k : P.sb + g * P.D + c)
+                       : sl < 14 ? P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + c : P.bias[f] + c;
+      if (sl < 12 || f < P.nf) cp_async4(tc::smem_u32(const_cast<float*>(prm + sl)), src);
+    }
+  };
+  auto taps_of = [&](int g) {
+    Taps2 T;
+    T.w0 = f2_splat(bf16r(prm[4 * g])); T.w1 = f2_splat(bf16r(prm[4 * g + 1])); T.w2 = f2_splat(bf16r(prm[4 * g + 2]));
+    T.b = f2_splat(bf16r(prm[4 * g + 3]));
+    return T;
+  };
   auto x1_of = [&](int rid) { return P.xin + (long long)(rid % P.B) * P.xsb + (long long)(rid / P.B) * P.xsc; };
   if constexpr (ASYNC) {
     const int r0 = blockIdx.x * G::SLOTS + slot;
     if (r0 < P.rows) {
+      stage_scalars(r0);
       stage_swz(RA, x1_of(r0));
       stage_swz(SB, x1_of(r0) + 2 * (long long)P.D * P.xsc);
     }
@@ -740,10 +761,12 @@ longconv_tcl_kernel(const Params P) {
     }
 
     for (int f = 0; f < P.nf && ok; ++f) {
-      const float ig = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);          // 2^-e of this channel
+      // 2^-e of this channel and the bias term of the spectrum product
+      const float ig = ASYNC ? prm[12 + f] : __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);
+      const float bkf = (ASYNC ? prm[14 + f] : __ldg(P.bias[f] + ch)) * G::KAPPA / ig;
       // ---------------- F1 operand: a[R n1 + r] as fp16, one 16-byte chunk = 8 consecutive r of one n1 ----------------
       if (ASYNC && f == 0) {
-        const Taps2 Tx = load_taps2(P.sw, P.sb, ch), Tv = load_taps2(P.sw, P.sb, 2 * P.D + ch);
+        const Taps2 Tx = taps_of(0), Tv = taps_of(2);
 #pragma unroll 2
         for (int it = 0; it < LIT; ++it) {
           int n1, rg;
@@ -923,8 +946,6 @@ longconv_tcl_kernel(const Params P) {
 
       // ---------------- hop 3: conj(Z (G + bias)); rows (k1, k2) keep their place (K-major), K = (ri, k3) ----------------
       {
-        const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);   // 2^-e of this channel
-        const float bkf = __ldg(P.bias[f] + ch) * G::KAPPA / inv_gain;
         const uint32_t bk = pack_h2(bkf, bkf);
         hop_rows<N3, G::T3T / TS, TS>(tml, K3, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k3 = 8 g ..
           if (g == 0 && t + TS < G::T3T) {
@@ -1028,7 +1049,7 @@ longconv_tcl_kernel(const Params P) {
         LCL_BARRIER()
         if (f == 0) {
           // ---- first epilogue: (conv + bias term as bf16) x short conv of x2; kept in SB when a residual pass follows
-          const Taps2 T2 = load_taps2(P.sw, P.sb, P.D + ch);
+          const Taps2 T2 = taps_of(1);
 #pragma unroll
           for (int it = 0; it < LIT; ++it) {
             const int c = it * TPS + sl, t0 = 8 * c;
@@ -1066,7 +1087,10 @@ longconv_tcl_kernel(const Params P) {
         if (!last) cp_async_wait<0>();             // u has had the whole epilogue to arrive
         LCL_BARRIER()                              // output buffer, SB (after the last pass) and RA's copy are settled
         if (last) {
-          if (rowid + stride < P.rows) stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
+          if (rowid + stride < P.rows) {
+            stage_scalars(rowid + stride);
+            stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
+          }
           cp_async_commit();
         }
       } else {
@@ -1088,8 +1112,7 @@ longconv_tcl_kernel(const Params P) {
       LCL_BARRIER()
 
       // ---------------- epilogue: gate / residual add; 8-byte stores along time ----------------
-      const float inv_gain = __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);     // undo the table's 2^e
-      const f32x2 gain2 = f2_splat(inv_gain);
+      const f32x2 gain2 = f2_splat(ig);                                                             // undo the table's 2^e
       if (f == 0) {
         const Taps2 T2 = load_taps2(P.sw, P.sb, P.D + ch);
 #pragma unroll 1
