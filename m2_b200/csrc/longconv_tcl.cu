@@ -119,8 +119,10 @@ __host__ __device__ constexpr int mat_off(int row, int k) {
 
 // ---------------------------------------------------------------------------------------
 // Spectrum table (kind 2): [HDR_FLOATS floats: matrices + twiddles], then per channel N fp16 values -- for
-// row tile t3 = k2 / 8 and row m = 8 k1 + (k2 % 8): [Re G[k3] x N3 | Im G[k3] x N3], bins
-// k = k1 + 32 k2 + 32 N2 k3, multiplied by KAPPA * 2^e -- then one float 2^-e per channel.
+// row tile t3 = k2 / 8: 16-byte chunks [j][m], j = 0 .. K3 / 8 - 1, row m = 8 k1 + (k2 % 8) of the tile; chunk j
+// of a row holds Re G[k3] for k3 = 8 j .. 8 j + 7 (j < N3 / 8), then Im G[k3] the same way; bins
+// k = k1 + 32 k2 + 32 N2 k3, multiplied by KAPPA * 2^e -- then one float 2^-e per channel.  Chunk-major tiles:
+// the 32 lanes of a warp (32 consecutive rows) read one chunk each from 512 contiguous bytes.
 // ---------------------------------------------------------------------------------------
 template <typename G>
 __device__ void write_header(float* spec, int tid, int nt) {
@@ -217,9 +219,14 @@ __device__ __forceinline__ int table_bin(int idx) {
   const int k3 = idx % G::N3, m = (idx / G::N3) % 128, t3 = idx / (G::N3 * 128);
   return (m >> 3) + 32 * (8 * t3 + (m & 7)) + 32 * G::N2 * k3;
 }
-// where its real part goes, in fp16 units from the channel's start (the imaginary part follows N3 entries on)
+// where its real part goes, in fp16 units from the channel's start (the imaginary part follows TABLE_IM entries on)
 template <typename G>
-__device__ __forceinline__ int table_pos(int idx) { return (idx / G::N3) * G::K3 + idx % G::N3; }
+__device__ __forceinline__ int table_pos(int idx) {
+  const int k3 = idx % G::N3, m = (idx / G::N3) % 128, t3 = idx / (G::N3 * 128);
+  return t3 * (128 * G::K3) + (k3 >> 3) * (128 * 8) + m * 8 + (k3 & 7);
+}
+template <typename G>
+constexpr int TABLE_IM = (G::N3 / 8) * 128 * 8;
 
 // One CTA per channel: N-point complex FFT (decimation in frequency) in shared memory of
 // g[n] w^{n/2}, g = the filter with its wrapped half negated; bins gathered in table order.
@@ -271,7 +278,7 @@ spectrum_kind2_kernel(const float* __restrict__ kfilt, float* __restrict__ spec,
     const int p = (int)(__brev((unsigned)table_bin<G>(idx)) >> (32 - G::LG));
     const int o = table_pos<G>(idx);
     Gt[o] = __float2half_rn(s[p].x * (G::KAPPA * sc));
-    Gt[o + G::N3] = __float2half_rn(s[p].y * (G::KAPPA * sc));
+    Gt[o + TABLE_IM<G>] = __float2half_rn(s[p].y * (G::KAPPA * sc));
   }
 }
 
@@ -371,7 +378,7 @@ spectrum_kind2_cluster_kernel(const float* __restrict__ kfilt, float* __restrict
       } else {
         const int o = table_pos<G>(idx);
         Gt[o] = __float2half_rn(gr * (G::KAPPA * sc));
-        Gt[o + G::N3] = __float2half_rn(gi * (G::KAPPA * sc));
+        Gt[o + TABLE_IM<G>] = __float2half_rn(gi * (G::KAPPA * sc));
       }
     }
     if (pass == 0) {
@@ -937,9 +944,9 @@ longconv_tcl_kernel(const Params P) {
       const __half* Gc = reinterpret_cast<const __half*>(P.spec[f] + G::HDR_FLOATS) + (size_t)ch * G::N;
       uint4 gv[NG], gn[NG];
       {
-        const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)(ts * 128 + l) * K3);
+        const uint4* gp = reinterpret_cast<const uint4*>(Gc) + (size_t)ts * NG * 128 + l;   // chunk i of row l of tile ts
 #pragma unroll
-        for (int i = 0; i < NG; ++i) gv[i] = __ldg(gp + i);
+        for (int i = 0; i < NG; ++i) gv[i] = __ldg(gp + i * 128);
       }
       tc::tc_fence_before();
       LCL_STAGE(2)
@@ -949,9 +956,9 @@ longconv_tcl_kernel(const Params P) {
         const uint32_t bk = pack_h2(bkf, bkf);
         hop_rows<N3, G::T3T / TS, TS>(tml, K3, ts, [&](int t, int g, const uint32_t (&re)[4], const uint32_t (&im)[4]) {   // k3 = 8 g ..
           if (g == 0 && t + TS < G::T3T) {
-            const uint4* gp = reinterpret_cast<const uint4*>(Gc + (size_t)((t + TS) * 128 + l) * K3);
+            const uint4* gp = reinterpret_cast<const uint4*>(Gc) + (size_t)(t + TS) * NG * 128 + l;
 #pragma unroll
-            for (int i = 0; i < NG; ++i) gn[i] = __ldg(gp + i);
+            for (int i = 0; i < NG; ++i) gn[i] = __ldg(gp + i * 128);
           }
           const uint32_t gr[4] = {gv[g].x, gv[g].y, gv[g].z, gv[g].w};
           const uint32_t gi[4] = {gv[N3 / 8 + g].x, gv[N3 / 8 + g].y, gv[N3 / 8 + g].z, gv[N3 / 8 + g].w};
