@@ -495,6 +495,11 @@ __device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  unsigned short v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ void sts16(uint32_t addr, uint32_t v) {
   asm volatile("st.shared.b16 [%0], %1;" ::"r"(addr), "h"((unsigned short)v) : "memory");
 }
@@ -625,12 +630,12 @@ __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t dat
   }
 }
 
-// ASYNC (geometries with room for it; 2-byte u, 16-byte aligned rows, L % 8 == 0, residual conv rounded to bf16):
+// ASYNC (geometries with room for it; 2-byte u, 16-byte aligned rows, L % 8 == 0):
 // no thread ever waits for a global load it has just issued.  Every row this slot reads is copied into the slot's
 // shared memory with cp.async one phase ahead -- x2 while the first filter's transform runs, u during the first
 // epilogue, the next sequence's x1 / v during and after the second epilogue -- the output buffer holds bf16, and the
-// first filter's gated result stays in shared memory until the second epilogue adds the residual conv and writes
-// the output once.
+// first filter's gated result stays in shared memory until the residual pass's last re-layout adds its conv to it;
+// the output is written once.
 template <typename G, typename TU, bool ASYNC>
 __global__ void __launch_bounds__(G::THREADS, 1)
 longconv_tcl_kernel(const Params P) {
@@ -725,9 +730,11 @@ longconv_tcl_kernel(const Params P) {
     const unsigned char* src = reinterpret_cast<const unsigned char*>(row);
     for (int c = sl; 8 * c < P.L; c += TPS) cp_async16(dst + 16 * (c ^ ((c / CPN) & 7)), src + 16 * c);
   };
+  // ... in time order, chunk c at c ^ ((c >> 3) & 1): the epilogue's quarter warps (8 consecutive chunks) and the
+  // last re-layout's 2-byte reads (lanes 32 bytes apart, 8 of them) both find 8 different bank groups
   auto stage_lin = [&](uint32_t dst, const void* row) {
     const unsigned char* src = reinterpret_cast<const unsigned char*>(row);
-    for (int c = sl; 8 * c < P.L; c += TPS) cp_async16(dst + 16 * c, src + 16 * c);
+    for (int c = sl; 8 * c < P.L; c += TPS) cp_async16(dst + 16 * (c ^ ((c >> 3) & 1)), src + 16 * c);
   };
   auto stage_scalars = [&](int rid) {
     if (sl < 16) {
@@ -1035,8 +1042,9 @@ longconv_tcl_kernel(const Params P) {
           if (f == 0 && lane == 0 && c > 0 && 8 * c < P.L) hh[it] = __ldg(reinterpret_cast<const uint32_t*>(x2row + 8 * c - 2));
         }
         if (f == 0) cp_async_wait<1>();            // this thread's pieces of x2 (all but the newest group)
-        // ---- hop 6: bf16(y 2^-e) at time R n1 + r; step t lives at element t + 8 (t / 64): neither these 2-byte
-        // scattered stores nor the epilogue's 16-byte reads meet bank conflicts
+        // ---- hop 6: time R n1 + r gets bf16(y 2^-e) -- in the residual pass added to the first pass's gated result,
+        // which waits in SB -- at element t + 8 (t / 64) of the output buffer: neither these 2-byte scattered
+        // accesses nor the epilogue's 16-byte reads meet bank conflicts
 #pragma unroll 1
         for (int t = ts; t < G::T1T; t += TS) {
           uint32_t z[16];
@@ -1045,9 +1053,20 @@ longconv_tcl_kernel(const Params P) {
           const int j5 = 16 * t + (l >> 3), n2 = 8 * (j5 / N3) + (l & 7), n3 = j5 % N3;
           const int r = N3 * n2 + n3;
           const uint32_t yp = data + 2 * (r + 8 * (r >> 6));
+          float y[16];
+#pragma unroll
+          for (int n1 = 0; n1 < 16; ++n1) y[n1] = __uint_as_float(z[n1]) * ig;
+          if (f == 1) {
+            const uint32_t op = SB + 16 * ((r >> 3) ^ ((r >> 6) & 1)) + 2 * (r & 7);     // (R / 8) n1 is a multiple of 16 chunks
+#pragma unroll
+            for (int n1 = 0; n1 < 16; ++n1) {
+              const float o = __uint_as_float(lds16(op + n1 * 2 * R) << 16);
+              y[n1] = o + (P.yu_bf16 ? bf16r(y[n1]) : y[n1]);
+            }
+          }
 #pragma unroll
           for (int n1 = 0; n1 < 16; n1 += 2) {
-            const uint32_t pk = pack_bf2(__uint_as_float(z[n1]) * ig, __uint_as_float(z[n1 + 1]) * ig);
+            const uint32_t pk = pack_bf2(y[n1], y[n1 + 1]);
             sts16(yp + n1 * (2 * (R + R / 8)), pk & 0xffffu);
             sts16(yp + (n1 + 1) * (2 * (R + R / 8)), pk >> 16);
           }
@@ -1062,7 +1081,8 @@ longconv_tcl_kernel(const Params P) {
             const int c = it * TPS + sl, t0 = 8 * c;
             const bool in = t0 < P.L;
             uint4 x = make_uint4(0u, 0u, 0u, 0u);
-            if (in) x = lds128(SB + 16 * c);
+            const uint32_t sbc = SB + 16 * (c ^ ((c >> 3) & 1));
+            if (in) x = lds128(sbc);
             uint32_t h = __shfl_up_sync(0xffffffffu, x.w, 1);
             if (lane == 0) h = hh[it];
             if (in) {
@@ -1072,23 +1092,15 @@ longconv_tcl_kernel(const Params P) {
               const uint4 y = lds128(data + 16 * c + 16 * (c >> 3));
               const uint4 o = make_uint4(bf2_mul(y.x, c2[0]), bf2_mul(y.y, c2[1]), bf2_mul(y.z, c2[2]), bf2_mul(y.w, c2[3]));
               if (last) *reinterpret_cast<uint4*>(orow + t0) = o;
-              else sts128(SB + 16 * c, o.x, o.y, o.z, o.w);
+              else sts128(sbc, o.x, o.y, o.z, o.w);
             }
           }
         } else {
-          // ---- second epilogue: gated result (SB) + residual conv (bf16), one 16-byte store per 8 steps
+          // ---- second epilogue: the sums are in the output buffer; one 16-byte store per 8 steps
 #pragma unroll
           for (int it = 0; it < LIT; ++it) {
             const int c = it * TPS + sl, t0 = 8 * c;
-            if (t0 < P.L) {
-              const uint4 y = lds128(data + 16 * c + 16 * (c >> 3));
-              const uint4 pv = lds128(SB + 16 * c);
-              *reinterpret_cast<uint4*>(orow + t0) =
-                  make_uint4(pack_bf2(bf_lo(pv.x) + bf_lo(y.x), bf_hi(pv.x) + bf_hi(y.x)),
-                             pack_bf2(bf_lo(pv.y) + bf_lo(y.y), bf_hi(pv.y) + bf_hi(y.y)),
-                             pack_bf2(bf_lo(pv.z) + bf_lo(y.z), bf_hi(pv.z) + bf_hi(y.z)),
-                             pack_bf2(bf_lo(pv.w) + bf_lo(y.w), bf_hi(pv.w) + bf_hi(y.w)));
-            }
+            if (t0 < P.L) *reinterpret_cast<uint4*>(orow + t0) = lds128(data + 16 * c + 16 * (c >> 3));
           }
         }
         if (!last) cp_async_wait<0>();             // u has had the whole epilogue to arrive
@@ -1280,7 +1292,7 @@ int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
   }
   // rows staged through shared memory ahead of their use: 16-byte pieces of every row, bf16 output buffer
   const bool staged = P.al16 && a->seq_len % 8 == 0 && a->out_sc % 8 == 0 && a->out_sb % 8 == 0 && m2_aligned(a->out, 16) &&
-                      (a->n_filters == 1 || (ubf && P.yu_bf16));
+                      (a->n_filters == 1 || ubf);
   if (a->seq_len <= 2048) {
     if (staged) return launch_conv<Geo4k, __nv_bfloat16, true>(P, st);
     return ubf ? launch_conv<Geo4k, __nv_bfloat16>(P, st) : launch_conv<Geo4k, float>(P, st);

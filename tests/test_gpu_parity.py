@@ -485,7 +485,7 @@ def test_longconv_long_row_family(L, D, B, residual, u_bf16):
 
 
 @pytest.mark.parametrize("L,D,B", [(8192, 40, 16), (4104, 24, 5), (2048, 96, 9), (1000, 16, 3), (136, 8, 2)])
-@pytest.mark.parametrize("residual", [True, False])
+@pytest.mark.parametrize("residual", ["bf16", "f16_of_f32", False])
 def test_longconv_long_rows_staged_and_direct_paths_agree(L, D, B, residual):
     """Rows on 16-byte boundaries take the variant that stages every global row in shared memory ahead of its use;
     an output whose rows start 8 bytes off takes the variant with direct loads.  Same arithmetic, same bits; enough
@@ -494,7 +494,11 @@ def test_longconv_long_rows_staged_and_direct_paths_agree(L, D, B, residual):
     m, sd = build_mixer(cfg, DEV)
     g = torch.Generator().manual_seed(L + 1)
     xin = (0.6 * torch.randn((B, 3 * D, L), generator=g)).to(DEV).bfloat16().transpose(1, 2)
-    u = torch.randn((B, D, L), generator=g).to(DEV).bfloat16().transpose(1, 2) if residual else None
+    u = None
+    if residual == "bf16":           # bf16 layer input: the residual conv is rounded to bf16 before the sum
+        u = torch.randn((B, D, L), generator=g).to(DEV).bfloat16().transpose(1, 2)
+    elif residual:                   # float32 layer input handed over as the fp16 time-major copy: float32 sum
+        u = ops.time_major_f16(torch.randn((B, D, L), generator=g).to(DEV).transpose(1, 2)).permute(1, 2, 0)
     filters = [m.filter_fn] + ([m.filter_fn2] if residual else [])
     specs = [f.spectrum(L, True, 2) for f in filters]
     outs = []
@@ -502,7 +506,8 @@ def test_longconv_long_rows_staged_and_direct_paths_agree(L, D, B, residual):
         flat = torch.full((B * D * L + 8,), float("nan"), dtype=torch.bfloat16, device=DEV)
         out = flat[off:off + B * D * L].view(B, D, L).transpose(1, 2)
         ops.longconv_fwd(xin, u, m.short_filter.weight, m.short_filter.bias, specs,
-                         [f.conv_bias() for f in filters], kind=2, bf16_rounding=True, out=out, yu_bf16=True)
+                         [f.conv_bias() for f in filters], kind=2, bf16_rounding=True, out=out,
+                         yu_bf16=residual == "bf16")
         assert torch.isnan(flat[:off].float()).all() and torch.isnan(flat[off + B * D * L:].float()).all()
         outs.append(out)
     assert ops.device_status() == 0
