@@ -1073,6 +1073,16 @@ longconv_tcl_kernel(const Params P) {
         }
         tc::tc_fence_before();
         LCL_BARRIER()
+        // after a residual pass SB (the gated result) and the scalars are done with: the next sequence's v and scalars
+        // start their way here; after a single-filter pass SB holds x2 for the epilogue below and they start after it
+        auto stage_next_v = [&]() {
+          if (rowid + stride < P.rows) {
+            stage_scalars(rowid + stride);
+            stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
+          }
+          cp_async_commit();
+        };
+        if (last && f == 1) stage_next_v();
         if (f == 0) {
           // ---- first epilogue: (conv + bias term as bf16) x short conv of x2; kept in SB when a residual pass follows
           const Taps2 T2 = taps_of(1);
@@ -1105,13 +1115,7 @@ longconv_tcl_kernel(const Params P) {
         }
         if (!last) cp_async_wait<0>();             // u has had the whole epilogue to arrive
         LCL_BARRIER()                              // output buffer, SB (after the last pass) and RA's copy are settled
-        if (last) {
-          if (rowid + stride < P.rows) {
-            stage_scalars(rowid + stride);
-            stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
-          }
-          cp_async_commit();
-        }
+        if (last && f == 0) stage_next_v();
       } else {
       // ---------------- hop 6: y[R n1 + r] (float32) into shared memory in time order, 4 floats of padding after every 32
       // (position t lives at t + 4 (t / 32): the scattered writes below and the float4 reads of the epilogue are both
