@@ -103,6 +103,14 @@ struct Geo {
   static constexpr int SMEM = SLOTS * DATA_BYTES + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128;
   static constexpr int SMEM_A = SLOTS * A_SLOT + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128 + SLOTS * 64;   // + per-slot scalars
   static constexpr bool CAN_ASYNC = TS == 1 && SMEM_A <= 227 * 1024;
+  // Where that does not fit (N = 65536: one sequence fills the SM) rows are staged inside the phase that uses them:
+  //   [32 R, +32 R)    halves of the raw x1 and v rows, then the raw u row, while the F1 operand [0, 32 R) is built
+  //   [36 R, +32 R)    x2 / the first pass's gated result, copied once the last stage's MMAs are done
+  static constexpr int B_LR = 32 * R;
+  static constexpr int B_SB = 36 * R;
+  static constexpr int B_SLOT = cmax(DEXT, 68 * R);
+  static constexpr int SMEM_B = SLOTS * B_SLOT + HDR_BYTES + 3 * SLOTS * 8 + 64 + 128 + SLOTS * 64;
+  static constexpr bool CAN_STAGE_IN_PHASE = !CAN_ASYNC && SMEM_B <= 227 * 1024 && (2 * R / TPS) % 2 == 0;
   static_assert(R % 128 == 0 && N3 % 8 == 0 && N2 % 8 == 0, "row tiles must be full");
   static_assert(SLOTS * COLS <= 512, "accumulators exceed tensor memory");
   static_assert(T1T % TS == 0 && T2T % TS == 0 && T3T % TS == 0, "tile split must divide every stage");
@@ -639,8 +647,12 @@ __device__ __forceinline__ void issue_stage(int stage, uint32_t tm, uint32_t dat
 template <typename G, typename TU, bool ASYNC>
 __global__ void __launch_bounds__(G::THREADS, 1)
 longconv_tcl_kernel(const Params P) {
-  static_assert(!ASYNC || (G::CAN_ASYNC && sizeof(TU) == 2), "asynchronous staging: geometry / element size");
-  constexpr int SLOT_BYTES = ASYNC ? G::A_SLOT : G::DATA_BYTES;
+  static_assert(!ASYNC || ((G::CAN_ASYNC || G::CAN_STAGE_IN_PHASE) && sizeof(TU) == 2), "asynchronous staging: geometry / element size");
+  // XP: rows cross phases (copied one phase ahead); BIG: one sequence fills the SM, rows are copied inside the phase
+  // that uses them -- still as 512-byte runs with every piece of a phase in flight at once, instead of 64-byte runs
+  // fetched a few registers at a time -- and the first pass's gated result takes the way through global memory
+  constexpr bool XP = ASYNC && G::CAN_ASYNC, BIG = ASYNC && !G::CAN_ASYNC;
+  constexpr int SLOT_BYTES = XP ? G::A_SLOT : BIG ? G::B_SLOT : G::DATA_BYTES;
   constexpr int N2 = G::N2, N3 = G::N3, R = G::R, K2 = G::K2, K3 = G::K3, TS = G::TS, TPS = G::TPS;
   constexpr int LIT = 2 * R / TPS;                 // 8-step chunks per thread in the load phase
   constexpr int LB = LIT < 4 ? LIT : 4;            // ... of which this many have their global loads in flight together
@@ -688,7 +700,8 @@ longconv_tcl_kernel(const Params P) {
   const uint32_t tml = tm + ((uint32_t)((warp & 3) * 32) << 16);
   const uint32_t data = tc::smem_u32(smem + slot * SLOT_BYTES);
   float* Y = reinterpret_cast<float*>(smem + slot * SLOT_BYTES);
-  const uint32_t RA = data + G::A_RA, SB = data + G::A_SB;     // raw-row regions of the asynchronous variant
+  const uint32_t RA = data + G::A_RA, SB = data + (BIG ? G::B_SB : G::A_SB);     // raw-row regions of the asynchronous variants
+  const uint32_t LR = data + G::B_LR;
   const int lane = tid & 31;
   // ASYNC: the sequence's scalars, copied ahead like its rows: [4 g + k] short-conv taps w0 w1 w2 b of x1, x2, v
   // (g = 0, 1, 2); [12 + f] 2^-e of filter f's channel; [14 + f] its bias
@@ -755,8 +768,10 @@ longconv_tcl_kernel(const Params P) {
     const int r0 = blockIdx.x * G::SLOTS + slot;
     if (r0 < P.rows) {
       stage_scalars(r0);
-      stage_swz(RA, x1_of(r0));
-      stage_swz(SB, x1_of(r0) + 2 * (long long)P.D * P.xsc);
+      if (XP) {
+        stage_swz(RA, x1_of(r0));
+        stage_swz(SB, x1_of(r0) + 2 * (long long)P.D * P.xsc);
+      }
     }
     cp_async_commit();
   }
@@ -779,7 +794,77 @@ longconv_tcl_kernel(const Params P) {
       const float ig = ASYNC ? prm[12 + f] : __ldg(P.spec[f] + G::HDR_FLOATS + (size_t)P.D * (G::N / 2) + ch);
       const float bkf = (ASYNC ? prm[14 + f] : __ldg(P.bias[f] + ch)) * G::KAPPA / ig;
       // ---------------- F1 operand: a[R n1 + r] as fp16, one 16-byte chunk = 8 consecutive r of one n1 ----------------
-      if (ASYNC && f == 0) {
+      if (BIG && f == 0) {
+        const Taps2 Tx = taps_of(0), Tv = taps_of(2);
+        constexpr int HI = LIT / 2, HC = CPN / 2;          // iterations / chunks per n1 of one half
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          // this half's chunks of x1 (LR) and v (LR + 16 R): chunk (n1, rg) at index HC n1 + rg - HC half, low bits ^ n1
+          for (int j = sl; j < 16 * HC; j += TPS) {
+            const int n1 = j / HC, c = n1 * CPN + half * HC + j % HC;
+            if (8 * c < P.L) {
+              cp_async16(LR + 16 * (j ^ (n1 & 7)), x1row + 8 * c);
+              cp_async16(LR + 16 * R + 16 * (j ^ (n1 & 7)), vrow + 8 * c);
+            }
+          }
+          cp_async_commit();
+          // the two steps before a chunk: by shuffle from the lane 8 below; the first quarter warp asks global memory
+          uint32_t gx[HI], gw[HI];
+#pragma unroll
+          for (int i = 0; i < HI; ++i) {
+            int n1, rg;
+            chunk_of((half * HI + i) * TPS + sl, n1, rg);
+            const int t0 = R * n1 + 8 * rg;
+            gx[i] = gw[i] = 0u;
+            if (lane < 8 && t0 >= 2 && t0 < P.L) {
+              gx[i] = __ldg(reinterpret_cast<const uint32_t*>(x1row + t0 - 2));
+              gw[i] = __ldg(reinterpret_cast<const uint32_t*>(vrow + t0 - 2));
+            }
+          }
+          cp_async_wait<0>();
+          LCL_BARRIER()
+#pragma unroll
+          for (int i = 0; i < HI; ++i) {
+            int n1, rg;
+            chunk_of((half * HI + i) * TPS + sl, n1, rg);
+            const int t0 = R * n1 + 8 * rg;
+            const bool in = t0 < P.L;
+            uint4 x = make_uint4(0u, 0u, 0u, 0u), v = x;
+            if (in) {
+              const uint32_t o = 16 * ((n1 * HC + rg - half * HC) ^ (n1 & 7));
+              x = lds128(LR + o); v = lds128(LR + 16 * R + o);
+            }
+            uint32_t hx = __shfl_up_sync(0xffffffffu, x.w, 8), hv = __shfl_up_sync(0xffffffffu, v.w, 8);
+            if (lane < 8) { hx = gx[i]; hv = gw[i]; }
+            const uint32_t wx[5] = {hx, x.x, x.y, x.z, x.w}, wv[5] = {hv, v.x, v.y, v.z, v.w};
+            uint32_t cx[4], cv[4], h[4];
+            conv_packed<8>(Tx, wx, cx);
+            conv_packed<8>(Tv, wv, cv);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = in ? bf2_to_h2(bf2_mul(cv[j], cx[j])) : 0u;
+            sts128(data + rg * G::SBO1 + n1 * 16, h[0], h[1], h[2], h[3]);
+          }
+          if (half == 0) { LCL_BARRIER() }                 // every thread is done with this half before the next lands
+        }
+      } else if (BIG) {
+        // the raw u row (LR, swizzled like the cross-phase variant's rows), all of it in flight at once
+        stage_swz(LR, urow);
+        cp_async_commit();
+        cp_async_wait<0>();
+        LCL_BARRIER()
+#pragma unroll 2
+        for (int it = 0; it < LIT; ++it) {
+          int n1, rg;
+          chunk_of(it * TPS + sl, n1, rg);
+          const int t0 = R * n1 + 8 * rg, c = t0 >> 3;
+          uint4 w = make_uint4(0u, 0u, 0u, 0u);
+          if (t0 < P.L) w = lds128(LR + 16 * (c ^ (n1 & 7)));
+          if (!P.u_f16) {
+            w.x = bf2_to_h2(w.x); w.y = bf2_to_h2(w.y); w.z = bf2_to_h2(w.z); w.w = bf2_to_h2(w.w);
+          }
+          sts128(data + rg * G::SBO1 + n1 * 16, w.x, w.y, w.z, w.w);
+        }
+      } else if (ASYNC && f == 0) {
         const Taps2 Tx = taps_of(0), Tv = taps_of(2);
 #pragma unroll 2
         for (int it = 0; it < LIT; ++it) {
@@ -900,7 +985,7 @@ longconv_tcl_kernel(const Params P) {
         }
       }
       LCL_STAGE(0)
-      if constexpr (ASYNC) {
+      if constexpr (XP) {
         if (f == 0) {                              // every thread of the slot is done with the raw x1 / v rows
           stage_lin(SB, x2row);
           cp_async_commit();
@@ -1029,9 +1114,14 @@ longconv_tcl_kernel(const Params P) {
 
       if constexpr (ASYNC) {
         const bool last = f + 1 == P.nf;
-        // the operand regions are free: the next raw row goes into RA while this pass finishes
-        if (!last) stage_swz(RA, urow);
-        else if (rowid + stride < P.rows) stage_swz(RA, x1_of(rowid + stride));
+        if (XP) {
+          // the operand regions are free: the next raw row goes into RA while this pass finishes
+          if (!last) stage_swz(RA, urow);
+          else if (rowid + stride < P.rows) stage_swz(RA, x1_of(rowid + stride));
+        } else {
+          // ... x2, or the gated result this slot's threads wrote to the output a pass ago, goes into SB
+          stage_lin(SB, f == 0 ? (const void*)x2row : (const void*)orow);
+        }
         cp_async_commit();
         // x2's two steps before each chunk come from the lane below; lane 0 fetches its own (L2: the row was just copied)
         uint32_t hh[LIT];
@@ -1041,7 +1131,11 @@ longconv_tcl_kernel(const Params P) {
           hh[it] = 0u;
           if (f == 0 && lane == 0 && c > 0 && 8 * c < P.L) hh[it] = __ldg(reinterpret_cast<const uint32_t*>(x2row + 8 * c - 2));
         }
-        if (f == 0) cp_async_wait<1>();            // this thread's pieces of x2 (all but the newest group)
+        if (XP && f == 0) cp_async_wait<1>();      // this thread's pieces of x2 (all but the newest group)
+        if (BIG && f == 1) {                       // the last re-layout adds to the gated result: it has to be there
+          cp_async_wait<0>();
+          LCL_BARRIER()
+        }
         // ---- hop 6: time R n1 + r gets bf16(y 2^-e) -- in the residual pass added to the first pass's gated result,
         // which waits in SB -- at element t + 8 (t / 64) of the output buffer: neither these 2-byte scattered
         // accesses nor the epilogue's 16-byte reads meet bank conflicts
@@ -1071,6 +1165,7 @@ longconv_tcl_kernel(const Params P) {
             sts16(yp + (n1 + 1) * (2 * (R + R / 8)), pk >> 16);
           }
         }
+        if (BIG && f == 0) cp_async_wait<0>();     // x2 came in behind the re-layout
         tc::tc_fence_before();
         LCL_BARRIER()
         // after a residual pass SB (the gated result) and the scalars are done with: the next sequence's v and scalars
@@ -1078,7 +1173,7 @@ longconv_tcl_kernel(const Params P) {
         auto stage_next_v = [&]() {
           if (rowid + stride < P.rows) {
             stage_scalars(rowid + stride);
-            stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
+            if (XP) stage_swz(SB, x1_of(rowid + stride) + 2 * (long long)P.D * P.xsc);
           }
           cp_async_commit();
         };
@@ -1101,7 +1196,7 @@ longconv_tcl_kernel(const Params P) {
               conv_packed<8>(T2, wx, c2);
               const uint4 y = lds128(data + 16 * c + 16 * (c >> 3));
               const uint4 o = make_uint4(bf2_mul(y.x, c2[0]), bf2_mul(y.y, c2[1]), bf2_mul(y.z, c2[2]), bf2_mul(y.w, c2[3]));
-              if (last) *reinterpret_cast<uint4*>(orow + t0) = o;
+              if (last || BIG) *reinterpret_cast<uint4*>(orow + t0) = o;
               else sts128(sbc, o.x, o.y, o.z, o.w);
             }
           }
@@ -1113,7 +1208,7 @@ longconv_tcl_kernel(const Params P) {
             if (t0 < P.L) *reinterpret_cast<uint4*>(orow + t0) = lds128(data + 16 * c + 16 * (c >> 3));
           }
         }
-        if (!last) cp_async_wait<0>();             // u has had the whole epilogue to arrive
+        if (XP && !last) cp_async_wait<0>();       // u has had the whole epilogue to arrive
         LCL_BARRIER()                              // output buffer, SB (after the last pass) and RA's copy are settled
         if (last && f == 0) stage_next_v();
       } else {
@@ -1226,7 +1321,7 @@ static int launch_spectrum(int D, int R, const float* k, float* spec, cudaStream
 template <typename G, typename TU, bool ASYNC = false>
 static int launch_conv(const Params& P, cudaStream_t st) {
   auto kern = longconv_tcl_kernel<G, TU, ASYNC>;
-  constexpr int SMEM = ASYNC ? G::SMEM_A : G::SMEM;
+  constexpr int SMEM = !ASYNC ? G::SMEM : G::CAN_ASYNC ? G::SMEM_A : G::SMEM_B;
   M2_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -1305,6 +1400,7 @@ int longconv_tcl_launch(const m2_longconv_args* a, cudaStream_t st) {
     if (staged) return launch_conv<Geo16k, __nv_bfloat16, true>(P, st);
     return ubf ? launch_conv<Geo16k, __nv_bfloat16>(P, st) : launch_conv<Geo16k, float>(P, st);
   }
+  if (staged) return launch_conv<Geo64k, __nv_bfloat16, true>(P, st);
   return ubf ? launch_conv<Geo64k, __nv_bfloat16>(P, st) : launch_conv<Geo64k, float>(P, st);
 }
 

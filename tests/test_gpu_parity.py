@@ -484,7 +484,8 @@ def test_longconv_long_row_family(L, D, B, residual, u_bf16):
     assert max(errs) < TOL_BF16, errs
 
 
-@pytest.mark.parametrize("L,D,B", [(8192, 40, 16), (4104, 24, 5), (2048, 96, 9), (1000, 16, 3), (136, 8, 2)])
+@pytest.mark.parametrize("L,D,B", [(8192, 40, 16), (4104, 24, 5), (2048, 96, 9), (1000, 16, 3), (136, 8, 2),
+                                   (32768, 40, 8), (16392, 24, 2)])
 @pytest.mark.parametrize("residual", ["bf16", "f16_of_f32", False])
 def test_longconv_long_rows_staged_and_direct_paths_agree(L, D, B, residual):
     """Rows on 16-byte boundaries take the variant that stages every global row in shared memory ahead of its use;
