@@ -57,6 +57,8 @@ HEADLINE = "m2bert80m-L128"
 TRAFFIC = {
     "m2bert80m-L128": (247.2e6, "profiles/longconv_tz_m2bert80m-L128.md"),
     "m2bert80m-L8192": (1990e6, "profiles/longconv_tcl_m2bert80m-L8192.md (batch-8 capture scaled to batch 32)"),
+    "m2bert80m-L32768": (2169e6, "profiles/longconv_tcl_m2bert80m-L32768.md (batch-2 capture scaled to batch 8)"),
+    "m2bert-large-L2048": (1973e6, "profiles/longconv_tcl_m2bert-large-L2048.md (batch-16 capture scaled to batch 64)"),
 }
 VOCAB = 30528
 METRIC = "M2-BERT-80M fwd sequences/sec"
