@@ -785,7 +785,7 @@ longconv_tcl_kernel(const Params P) {
     __nv_bfloat16* orow = P.out + (long long)b * P.osb + (long long)ch * P.osc;
     const TU* urow = reinterpret_cast<const TU*>(P.u) + (long long)b * P.usb + (long long)ch * P.usc;
     if constexpr (ASYNC) {
-      cp_async_wait<0>();                          // this sequence's x1 (RA) and v (SB)
+      cp_async_wait<0>();                          // this sequence's scalars; XP: its x1 (RA) and v (SB) as well
       LCL_BARRIER()
     }
 
